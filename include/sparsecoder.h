@@ -1,0 +1,171 @@
+/*
+ * sparsecoder.h — C ABI of libsparsecoder.so: sm_100a kernels for the TopK
+ * sparse-coder (SAE / transcoder) training step.
+ *
+ * Conventions for every entry point:
+ *   - returns an int status, SC_OK (0) on success; sc_last_error() holds a
+ *     message for the most recent failure in this process;
+ *   - never allocates, frees or synchronises: all pointers are device
+ *     pointers to caller-owned memory (the single exception is the
+ *     *_noalloc entry point, which owns a fixed static device array);
+ *   - the caller passes the CUDA stream as an opaque pointer
+ *     (cudaStream_t) and must have made the right device current;
+ *   - matrices are row-major and contiguous: x[N,D], W[M,D], out[N,D],
+ *     idx[N,k] (int64), acts[N,k];
+ *   - "dtype" arguments take SC_F32 or SC_BF16.
+ *
+ * Each declaration cites the routine of EleutherAI/sparsify v1.3.0 whose
+ * arithmetic it replaces (file:line inside that project).
+ */
+#ifndef SPARSECODER_H_
+#define SPARSECODER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  SC_OK = 0,
+  SC_ERR_INVALID = 1,     /* bad argument (shape, dtype, null pointer, alignment) */
+  SC_ERR_UNSUPPORTED = 2, /* valid request this build has no kernel for */
+  SC_ERR_WORKSPACE = 3,   /* workspace smaller than sc_*_workspace_bytes() */
+  SC_ERR_CUDA = 4,        /* a CUDA runtime/driver call failed */
+  SC_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+  SC_ERR_TOO_LARGE = 6    /* size beyond a fixed maximum of the entry point */
+};
+
+enum { SC_F32 = 0, SC_BF16 = 1 };
+
+enum { SC_ACT_TOPK = 0, SC_ACT_GROUPMAX = 1 };
+
+/* ---- diagnostics ------------------------------------------------------- */
+int sc_version(void);
+/* Copies the last error message (NUL-terminated) into buf; returns its length. */
+size_t sc_last_error(char* buf, size_t cap);
+const char* sc_status_string(int status);
+
+/* ---- encoder forward ---------------------------------------------------
+ * sparsify/fused_encoder.py:19-50 (FusedEncoder.forward):
+ *   preacts = relu(x @ W^T + b); top-k (or groupmax) per row.
+ */
+
+/* x' = x - b_dec (b_dec may be NULL), cast to out_dtype.
+ * sparsify/sparse_coder.py:191-192 (the subtraction in SparseCoder.encode). */
+int sc_prep_input(const void* x, int x_dtype, const float* b_dec, int64_t N,
+                  int64_t D, void* out, int out_dtype, void* stream);
+
+/* Dense pre-activations relu(x W^T + b) written to pre[N,M] (pre_dtype).
+ * Any shape; fp32 FMA kernel (x, W given in x_dtype / w_dtype).
+ * sparsify/fused_encoder.py:29. */
+int sc_preacts_dense(const void* x, int x_dtype, const void* W, int w_dtype,
+                     const float* bias, int64_t N, int64_t D, int64_t M,
+                     void* pre, int pre_dtype, void* stream);
+
+/* Per-row top-k over a dense [N,M] fp32 matrix, optionally restricted to the
+ * columns where col_mask[m] != 0 (others count as -inf). Unsorted output.
+ * If fewer than k columns are eligible the call fails with SC_ERR_INVALID.
+ * sparsify/fused_encoder.py:33 (torch.topk, sorted=False) and
+ * sparsify/sparse_coder.py:240-243 (AuxK: where(dead_mask, pre_acts, -inf).topk). */
+int sc_topk_rows(const float* pre, int64_t N, int64_t M, int k,
+                 const uint8_t* col_mask, float* top_vals, int64_t* top_idx,
+                 void* stream);
+
+/* groupmax: max and argmax inside each of k contiguous groups of M/k columns.
+ * sparsify/fused_encoder.py:34-43. */
+int sc_groupmax_rows(const float* pre, int64_t N, int64_t M, int k,
+                     float* top_vals, int64_t* top_idx, void* stream);
+
+/* Fused tcgen05 path: bf16 x[N,D] and W[M,D], fp32 bias, fp32 TMEM
+ * accumulation; bias + ReLU + running per-row top-k in the epilogue so the
+ * N x M matrix never reaches HBM; then a merge picks the final k per row.
+ * Requirements: D % 64 == 0, M % 8 == 0, k <= 128, M >= k.
+ * ws must hold sc_encode_topk_workspace_bytes(N, D, M, k) bytes, 256-aligned.
+ * status_word (device int32, may be NULL) receives a non-zero code if a
+ * bounded wait inside the kernel gave up.
+ * sparsify/fused_encoder.py:29-33. */
+size_t sc_encode_topk_workspace_bytes(int64_t N, int64_t D, int64_t M, int k);
+int sc_encode_topk(const void* x_bf16, const void* W_bf16, const float* bias,
+                   int64_t N, int64_t D, int64_t M, int k, float* top_vals,
+                   int64_t* top_idx, void* ws, size_t ws_bytes,
+                   int32_t* status_word, void* stream);
+
+/* ---- sparse decode (embedding bag) --------------------------------------
+ * out[n,:] = (bias ? bias : 0) + sum_j acts[n,j] * W[idx[n,j],:]
+ * sparsify/xformers.py:9-53 (embedding_bag_k), sparsify/utils.py:81-90,
+ * sparsify/sparse_coder.py:198-202 (decode, with bias = b_dec) and
+ * sparsify/fused_encoder.py:58-64 (grad-x of the encoder, bias = NULL).
+ * out is fp32. */
+int sc_embedding_bag_fwd(const int64_t* idx, const float* acts, const void* W,
+                         int w_dtype, const float* bias, int64_t N, int64_t D,
+                         int64_t M, int k, float* out, void* stream);
+
+/* grad_acts[n,j] = dot(grad_out[n,:], W[idx[n,j],:])
+ * sparsify/xformers.py:125-131 (per_sample_weights_grad). */
+int sc_embedding_bag_bwd_acts(const int64_t* idx, const float* grad_out,
+                              const void* W, int w_dtype, int64_t N, int64_t D,
+                              int64_t M, int k, float* grad_acts, void* stream);
+
+/* Latent-major CSR of the [N,k] index matrix: row_ptr[M+1], entries[N*k]
+ * (flat position n*k+j, ascending inside each latent).
+ * ws: sc_csr_workspace_bytes(M) bytes.
+ * sparsify/xformers.py:56-85,146-163 (count, cumsum, reverse mapping). */
+size_t sc_csr_workspace_bytes(int64_t M);
+int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M,
+                 int32_t* row_ptr, int32_t* entries, void* ws, size_t ws_bytes,
+                 void* stream);
+
+/* Per-latent row accumulate over latents [lat_begin, lat_end):
+ *   gradA[m,:] = sum_e coefA[e] * vecA[e / k, :]        (always)
+ *   gradB[m,:] = sum_e coefB[e] * vecB[e / k, :]        (if gradB != NULL)
+ *   grad_bias[m] = sum_e coefB[e]                        (if grad_bias != NULL)
+ * e runs over the CSR entries of latent m; rows with no entries are zeroed.
+ * vecA/vecB are [N,D] in their dtypes; coefA/coefB are fp32 [N*k]; grads fp32.
+ * A = decoder (coef = acts, vec = grad_out): sparsify/xformers.py:88-136.
+ * B = encoder (coef = grad_acts, vec = x'):   sparsify/fused_encoder.py:66-84. */
+int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries, int k,
+                       const float* coefA, const void* vecA, int vecA_dtype,
+                       float* gradA, const float* coefB, const void* vecB,
+                       int vecB_dtype, float* gradB, float* grad_bias,
+                       int64_t M, int64_t D, int64_t lat_begin, int64_t lat_end,
+                       void* stream);
+
+/* ---- losses -------------------------------------------------------------
+ * sparsify/sparse_coder.py:225-228,253-254:
+ *   total_variance = sum((y - mean_0(y))^2);  e = y - out;  l2 = sum(e^2).
+ * sc_total_variance writes *tv (device fp32); ws holds
+ * sc_loss_workspace_bytes(D) bytes. */
+size_t sc_loss_workspace_bytes(int64_t D);
+int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv, void* ws,
+                      size_t ws_bytes, void* stream);
+/* sse[0] = sum((a - b)^2) over n elements (device fp32 scalar);
+ * if diff != NULL also writes diff = a - b. */
+int sc_sq_err(const float* a, const float* b, int64_t n, float* diff,
+              float* sse, void* ws, size_t ws_bytes, void* stream);
+
+/* ---- weight update ------------------------------------------------------
+ * sparsify/sparse_coder.py:273-279: W[m,:] /= (||W[m,:]||_2 + eps), in place;
+ * optionally refreshes a bf16 shadow copy in the same pass. */
+int sc_normalize_rows(float* W, int64_t M, int64_t D, float eps,
+                      void* shadow_bf16, void* stream);
+
+/* torch.optim.Adam (betas, eps, no weight decay, no amsgrad) on rows of a
+ * [M,D] matrix; when project != 0 the gradient row first loses its component
+ * parallel to the parameter row (sparsify/sparse_coder.py:281-295, in place on
+ * g, as the reference does). step is the 1-based step count. bc = bias
+ * corrections computed on the host. Optionally refreshes a bf16 shadow.
+ * sparsify/trainer.py:99-116,513-519. A vector is a [1,D] matrix. */
+int sc_adam_rows(float* p, float* g, float* m, float* v, int64_t M, int64_t D,
+                 float lr, float beta1, float beta2, float eps, int64_t step,
+                 int project, void* shadow_bf16, void* stream);
+
+/* fp32 -> bf16 copy (shadow refresh). */
+int sc_cast_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSECODER_H_ */

@@ -1,0 +1,163 @@
+// Latent-major CSR of the [N,k] top-k index matrix.
+//
+// count (atomic histogram) -> exclusive scan -> slot fill (atomic cursors) ->
+// per-latent sort of the claimed slots, so that the entries of each latent
+// come out in ascending flat position n*k+j whatever order the atomics ran in.
+// Latents with more than kSortMax entries keep the arrival order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kSortMax = 2048;
+
+__global__ void csr_count_kernel(const int64_t* __restrict__ idx, int64_t total, int64_t M,
+                                 int32_t* __restrict__ counts) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t m = idx[e];
+    if (m >= 0 && m < M) atomicAdd(&counts[m], 1);
+  }
+}
+
+// Exclusive scan of counts[0..M) into row_ptr[0..M]; also seeds cursor = row_ptr.
+// One CTA; each thread owns a contiguous slice.
+__global__ void __launch_bounds__(1024)
+csr_scan_kernel(const int32_t* __restrict__ counts, int64_t M, int32_t* __restrict__ row_ptr,
+                int32_t* __restrict__ cursor) {
+  __shared__ int32_t s_warp[32];
+  const int t = threadIdx.x;
+  const int64_t per = (M + blockDim.x - 1) / blockDim.x;
+  const int64_t lo = (int64_t)t * per;
+  const int64_t hi = lo + per < M ? lo + per : M;
+  int32_t local = 0;
+  for (int64_t i = lo; i < hi; ++i) local += counts[i];
+  // inclusive scan of `local` over the block
+  int32_t incl = local;
+  const int lane = t & 31, warp = t >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = s_warp[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int32_t y = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += y;
+    }
+    s_warp[lane] = w;
+  }
+  __syncthreads();
+  int32_t run = incl - local + (warp > 0 ? s_warp[warp - 1] : 0);
+  for (int64_t i = lo; i < hi; ++i) {
+    row_ptr[i] = run;
+    cursor[i] = run;
+    run += counts[i];
+  }
+  if (t == blockDim.x - 1) row_ptr[M] = s_warp[31];
+}
+
+__global__ void csr_fill_kernel(const int64_t* __restrict__ idx, int64_t total, int64_t M,
+                                int32_t* __restrict__ cursor, int32_t* __restrict__ entries) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t m = idx[e];
+    if (m >= 0 && m < M) {
+      int32_t pos = atomicAdd(&cursor[m], 1);
+      entries[pos] = (int32_t)e;
+    }
+  }
+}
+
+// One warp per latent; segments of 2..32 entries sort in registers, segments up
+// to kSortMax in a per-warp shared-memory buffer (bitonic network).
+constexpr int kSortWarps = 4;
+__global__ void __launch_bounds__(kSortWarps * 32)
+csr_sort_kernel(const int32_t* __restrict__ row_ptr, int64_t M, int32_t* __restrict__ entries) {
+  __shared__ int32_t s_buf[kSortWarps][kSortMax];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t m = (int64_t)blockIdx.x * kSortWarps + warp;
+  if (m >= M) return;
+  const int32_t lo = row_ptr[m], len = row_ptr[m + 1] - lo;
+  if (len <= 1 || len > kSortMax) return;
+  if (len <= 32) {
+    int32_t v = lane < len ? entries[lo + lane] : 0x7fffffff;
+    for (int size = 2; size <= 32; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        int32_t o = __shfl_xor_sync(0xffffffffu, v, stride);
+        bool up = (lane & size) == 0;          // ascending block?
+        bool lower = (lane & stride) == 0;     // lower partner keeps min when ascending
+        bool keep_min = (up == lower);
+        v = keep_min ? min(v, o) : max(v, o);
+      }
+    }
+    if (lane < len) entries[lo + lane] = v;
+    return;
+  }
+  int32_t* buf = s_buf[warp];
+  int n2 = 64;
+  while (n2 < len) n2 <<= 1;
+  for (int i = lane; i < n2; i += 32) buf[i] = i < len ? entries[lo + i] : 0x7fffffff;
+  __syncwarp();
+  for (int size = 2; size <= n2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = lane; i < n2 / 2; i += 32) {
+        int a = 2 * i - (i & (stride - 1));  // index with bit `stride` clear
+        int b = a + stride;
+        bool up = (a & size) == 0;
+        int32_t x = buf[a], y = buf[b];
+        if ((x > y) == up) { buf[a] = y; buf[b] = x; }
+      }
+      __syncwarp();
+    }
+  }
+  for (int i = lane; i < len; i += 32) entries[lo + i] = buf[i];
+}
+
+}  // namespace
+
+extern "C" size_t sc_csr_workspace_bytes(int64_t M) {
+  if (M < 0) return 0;
+  // counts[M] + cursor[M], each padded to 256 bytes
+  size_t one = (((size_t)M * sizeof(int32_t)) + 255) & ~size_t(255);
+  return 2 * one;
+}
+
+extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int32_t* row_ptr,
+                            int32_t* entries, void* ws, size_t ws_bytes, void* stream) {
+  SC_REQUIRE(N >= 0 && k > 0 && M > 0, "sc_csr_build: bad shape N=%lld k=%d M=%lld",
+             (long long)N, k, (long long)M);
+  SC_REQUIRE(row_ptr && ws, "sc_csr_build: null pointer");
+  // Flat positions are stored as int32 (sparsify/xformers.py:156 has the same bound).
+  SC_REQUIRE(N * (int64_t)k < (int64_t(1) << 31), "sc_csr_build: N*k must be below 2^31");
+  if (ws_bytes < sc_csr_workspace_bytes(M))
+    return sc::fail(SC_ERR_WORKSPACE, "sc_csr_build: workspace %zu < %zu", ws_bytes,
+                    sc_csr_workspace_bytes(M));
+  cudaStream_t st = sc::as_stream(stream);
+  const size_t one = (((size_t)M * sizeof(int32_t)) + 255) & ~size_t(255);
+  int32_t* counts = static_cast<int32_t*>(ws);
+  int32_t* cursor = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + one);
+  const int64_t total = N * k;
+  SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
+  if (total > 0) {
+    SC_REQUIRE(idx && entries, "sc_csr_build: null pointer");
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
+    SC_CHECK_LAUNCH("csr_count");
+    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
+    SC_CHECK_LAUNCH("csr_scan");
+    csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
+    SC_CHECK_LAUNCH("csr_fill");
+    csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(
+        row_ptr, M, entries);
+    SC_CHECK_LAUNCH("csr_sort");
+  } else {
+    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
+    SC_CHECK_LAUNCH("csr_scan");
+  }
+  return SC_OK;
+}

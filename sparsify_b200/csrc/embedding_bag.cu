@@ -1,0 +1,198 @@
+// Sparse decode as a weighted row gather (embedding bag) and its gradient
+// with respect to the per-entry weights.
+//
+// Forward: one CTA per token; every thread owns a few 4-element column groups
+// of the output row and walks the k selected rows of W, so each gathered row is
+// read once with fully coalesced 8/16-byte loads and accumulated in fp32 in
+// ascending j order (the order of sparsify/xformers.py:22-29).
+//
+// Backward w.r.t. acts: one CTA per token; the incoming gradient row is staged
+// in shared memory once and dotted against each of the k gathered rows.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBagThreads = 256;
+
+template <typename WT, int VEC>
+__global__ void __launch_bounds__(kBagThreads)
+bag_fwd_kernel(const int64_t* __restrict__ idx, const float* __restrict__ acts,
+               const WT* __restrict__ W, const float* __restrict__ bias, int64_t N,
+               int64_t D, int64_t M, int k, float* __restrict__ out) {
+  extern __shared__ unsigned char smem_raw[];
+  int64_t* s_idx = reinterpret_cast<int64_t*>(smem_raw);
+  float* s_act = reinterpret_cast<float*>(s_idx + k);
+  const int64_t n = blockIdx.x;
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    int64_t r = idx[n * k + j];
+    float a = acts[n * k + j];
+    if (r < 0 || r >= M) { r = 0; a = 0.f; }  // out-of-range ids contribute nothing
+    s_idx[j] = r;
+    s_act[j] = a;
+  }
+  __syncthreads();
+
+  constexpr int NCH = 4;  // column groups per thread per sweep
+  const int64_t sweep = (int64_t)blockDim.x * VEC * NCH;
+  for (int64_t base = 0; base < D; base += sweep) {
+    float acc[NCH][VEC];
+    int64_t col[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      col[c] = base + ((int64_t)c * blockDim.x + threadIdx.x) * VEC;
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        acc[c][v] = (bias != nullptr && col[c] + v < D) ? __ldg(bias + col[c] + v) : 0.f;
+    }
+#pragma unroll 4
+    for (int j = 0; j < k; ++j) {
+      const WT* row = W + s_idx[j] * D;
+      const float a = s_act[j];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        if (col[c] < D) {
+          if constexpr (VEC == 4) {
+            float4 w = sc::load4<WT>(row + col[c]);
+            acc[c][0] = fmaf(a, w.x, acc[c][0]);
+            acc[c][1] = fmaf(a, w.y, acc[c][1]);
+            acc[c][2] = fmaf(a, w.z, acc[c][2]);
+            acc[c][3] = fmaf(a, w.w, acc[c][3]);
+          } else {
+            acc[c][0] = fmaf(a, sc::load1<WT>(row + col[c]), acc[c][0]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (col[c] < D) {
+        if constexpr (VEC == 4) {
+          *reinterpret_cast<float4*>(out + n * D + col[c]) =
+              make_float4(acc[c][0], acc[c][1], acc[c][2], acc[c][3]);
+        } else {
+          out[n * D + col[c]] = acc[c][0];
+        }
+      }
+    }
+  }
+}
+
+template <typename WT, int VEC>
+__global__ void __launch_bounds__(kBagThreads)
+bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const float* __restrict__ gout,
+                    const WT* __restrict__ W, int64_t N, int64_t D, int64_t M, int k,
+                    float* __restrict__ gacts) {
+  extern __shared__ unsigned char smem_raw[];
+  float* s_g = reinterpret_cast<float*>(smem_raw);                 // [Dpad]
+  const int64_t Dpad = (D + 3) & ~int64_t(3);
+  float* s_part = s_g + Dpad;                                      // [k][nwarps]
+  const int nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t n = blockIdx.x;
+
+  for (int64_t c = threadIdx.x; c < Dpad; c += blockDim.x)
+    s_g[c] = c < D ? __ldg(gout + n * D + c) : 0.f;
+  __syncthreads();
+
+  constexpr int JB = 4;  // rows in flight per iteration
+  for (int j0 = 0; j0 < k; j0 += JB) {
+    float part[JB];
+    const WT* rows[JB];
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj) {
+      part[jj] = 0.f;
+      int64_t r = (j0 + jj < k) ? idx[n * k + j0 + jj] : -1;
+      rows[jj] = (r >= 0 && r < M) ? W + r * D : nullptr;
+    }
+    for (int64_t c = (int64_t)threadIdx.x * VEC; c < D; c += (int64_t)blockDim.x * VEC) {
+#pragma unroll
+      for (int jj = 0; jj < JB; ++jj) {
+        if (rows[jj] != nullptr) {
+          if constexpr (VEC == 4) {
+            float4 w = sc::load4<WT>(rows[jj] + c);
+            float4 g = *reinterpret_cast<const float4*>(s_g + c);
+            part[jj] = fmaf(w.x, g.x, part[jj]);
+            part[jj] = fmaf(w.y, g.y, part[jj]);
+            part[jj] = fmaf(w.z, g.z, part[jj]);
+            part[jj] = fmaf(w.w, g.w, part[jj]);
+          } else {
+            part[jj] = fmaf(sc::load1<WT>(rows[jj] + c), s_g[c], part[jj]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj) {
+      float s = sc::warp_sum(part[jj]);
+      if (lane == 0 && j0 + jj < k) s_part[(j0 + jj) * nwarps + warp] = s;
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += s_part[j * nwarps + w];
+    gacts[n * k + j] = s;
+  }
+}
+
+}  // namespace
+
+extern "C" int sc_embedding_bag_fwd(const int64_t* idx, const float* acts, const void* W,
+                                    int w_dtype, const float* bias, int64_t N, int64_t D,
+                                    int64_t M, int k, float* out, void* stream) {
+  SC_REQUIRE(sc::valid_dtype(w_dtype), "sc_embedding_bag_fwd: bad w_dtype %d", w_dtype);
+  SC_REQUIRE(N >= 0 && D > 0 && M > 0 && k > 0, "sc_embedding_bag_fwd: bad shape N=%lld D=%lld M=%lld k=%d",
+             (long long)N, (long long)D, (long long)M, k);
+  if (N == 0) return SC_OK;
+  SC_REQUIRE(idx && acts && W && out, "sc_embedding_bag_fwd: null pointer");
+  SC_REQUIRE(N <= 0x7fffffffLL, "sc_embedding_bag_fwd: N too large");
+  const size_t smem = (size_t)k * (sizeof(int64_t) + sizeof(float));
+  SC_REQUIRE(smem <= 48 * 1024, "sc_embedding_bag_fwd: k=%d too large", k);
+  const bool vec = (D % 4 == 0) && sc::aligned(W, 16) && sc::aligned(out, 16) &&
+                   (bias == nullptr || sc::aligned(bias, 16));
+  dim3 grid((unsigned)N), block(kBagThreads);
+  cudaStream_t st = sc::as_stream(stream);
+  if (w_dtype == SC_F32) {
+    const float* w = static_cast<const float*>(W);
+    if (vec) bag_fwd_kernel<float, 4><<<grid, block, smem, st>>>(idx, acts, w, bias, N, D, M, k, out);
+    else     bag_fwd_kernel<float, 1><<<grid, block, smem, st>>>(idx, acts, w, bias, N, D, M, k, out);
+  } else {
+    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
+    if (vec) bag_fwd_kernel<__nv_bfloat16, 4><<<grid, block, smem, st>>>(idx, acts, w, bias, N, D, M, k, out);
+    else     bag_fwd_kernel<__nv_bfloat16, 1><<<grid, block, smem, st>>>(idx, acts, w, bias, N, D, M, k, out);
+  }
+  SC_CHECK_LAUNCH("sc_embedding_bag_fwd");
+  return SC_OK;
+}
+
+extern "C" int sc_embedding_bag_bwd_acts(const int64_t* idx, const float* grad_out,
+                                         const void* W, int w_dtype, int64_t N, int64_t D,
+                                         int64_t M, int k, float* grad_acts, void* stream) {
+  SC_REQUIRE(sc::valid_dtype(w_dtype), "sc_embedding_bag_bwd_acts: bad w_dtype %d", w_dtype);
+  SC_REQUIRE(N >= 0 && D > 0 && M > 0 && k > 0, "sc_embedding_bag_bwd_acts: bad shape");
+  if (N == 0) return SC_OK;
+  SC_REQUIRE(idx && grad_out && W && grad_acts, "sc_embedding_bag_bwd_acts: null pointer");
+  SC_REQUIRE(N <= 0x7fffffffLL, "sc_embedding_bag_bwd_acts: N too large");
+  const int nwarps = kBagThreads / 32;
+  const size_t smem = (size_t)(((D + 3) & ~int64_t(3)) + (int64_t)k * nwarps) * sizeof(float);
+  SC_REQUIRE(smem <= 200 * 1024, "sc_embedding_bag_bwd_acts: D=%lld, k=%d need %zu B of shared memory",
+             (long long)D, k, smem);
+  const bool vec = (D % 4 == 0) && sc::aligned(W, 16);
+  dim3 grid((unsigned)N), block(kBagThreads);
+  cudaStream_t st = sc::as_stream(stream);
+#define SC_LAUNCH_BWD(WT, VEC)                                                              \
+  do {                                                                                      \
+    auto kern = bag_bwd_acts_kernel<WT, VEC>;                                               \
+    if (smem > 48 * 1024)                                                                   \
+      SC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    kern<<<grid, block, smem, st>>>(idx, grad_out, static_cast<const WT*>(W), N, D, M, k, grad_acts); \
+  } while (0)
+  if (w_dtype == SC_F32) {
+    if (vec) SC_LAUNCH_BWD(float, 4); else SC_LAUNCH_BWD(float, 1);
+  } else {
+    if (vec) SC_LAUNCH_BWD(__nv_bfloat16, 4); else SC_LAUNCH_BWD(__nv_bfloat16, 1);
+  }
+#undef SC_LAUNCH_BWD
+  SC_CHECK_LAUNCH("sc_embedding_bag_bwd_acts");
+  return SC_OK;
+}

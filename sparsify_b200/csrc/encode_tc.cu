@@ -1,0 +1,422 @@
+// Fused encoder forward on the 5th-generation tensor cores.
+//
+//   pre[n,m] = relu(sum_d x[n,d] W[m,d] + b[m]),   top-k per row
+//
+// A persistent CTA per SM walks work units (128-token row block x strip of
+// consecutive 256-latent tiles). Warp 0 streams 128x64 / 256x64 bf16 tiles of x
+// and W into a shared-memory ring with TMA, warp 1 issues tcgen05.mma into one
+// of two 128x256 fp32 accumulators in tensor memory, and warps 2-5 drain the
+// other accumulator: bias, ReLU and a running top-k list per row held in shared
+// memory, so the epilogue of tile t overlaps the MMAs of tile t+1 and the N x M
+// matrix never reaches HBM. Each (row, strip) emits k candidates; a second
+// kernel merges the strips of a row into the final k.
+//
+// A per-row lower bound on the k-th largest value (`tau`) is published after
+// every finished strip and read at the start of later strips of the same rows:
+// values not above it cannot be among the row's top k, which removes most list
+// insertions after the first wave of units.
+#include "tc.cuh"
+
+namespace {
+
+using namespace sc::tc;
+
+constexpr int BM = 128;   // tokens per tile (TMEM lanes)
+constexpr int BN = 256;   // latents per tile (TMEM columns per accumulator)
+constexpr int BK = 64;    // bf16 per 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kStageBytes = (BM + BN) * BK * 2;  // 48 KiB
+constexpr int kMaxK = 128;
+constexpr int kRowGroup = 32;  // row blocks whose units run together (L2 footprint of x)
+
+struct Plan {
+  int n_rb;       // row blocks
+  int n_ct;       // column tiles
+  int n_strips;   // strips per row block
+  int stages;     // smem ring depth
+  int units;      // n_rb * n_strips
+  size_t smem;    // dynamic shared memory bytes
+  size_t off_lists_val, off_lists_idx, off_bias, off_bars;
+};
+
+// Status codes written to the device status word by a wait that gave up.
+enum { kWaitEmpty = 101, kWaitFull = 102, kWaitTmemEmpty = 103, kWaitTmemFull = 104 };
+
+struct Params {
+  const float* bias;
+  float* cand_vals;     // [N][n_strips][k]
+  int32_t* cand_idx;    // [N][n_strips][k]
+  float* tau;           // [N]
+  int32_t* status;
+  int64_t N, D, M;
+  int k, n_rb, n_ct, n_strips, stages, units;
+  uint32_t off_lists_val, off_lists_idx, off_bias, off_bars;
+};
+
+__device__ __forceinline__ void decode_unit(const Params& p, int u, int& rb, int& strip, int& t0, int& t1) {
+  const int per_group = kRowGroup * p.n_strips;
+  const int g = u / per_group, rem = u % per_group;
+  const int rg = min(kRowGroup, p.n_rb - g * kRowGroup);
+  strip = rem / rg;
+  rb = g * kRowGroup + rem % rg;
+  t0 = (int)(((int64_t)strip * p.n_ct) / p.n_strips);
+  t1 = (int)(((int64_t)(strip + 1) * p.n_ct) / p.n_strips);
+}
+
+__global__ void init_tau_kernel(float* tau, int64_t n, int32_t* status) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) tau[i] = -1.f;
+  if (i == 0 && status != nullptr) *status = 0;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                      const Params p) {
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  float* l_val = reinterpret_cast<float*>(smem + p.off_lists_val);         // [128][k]
+  uint16_t* l_idx = reinterpret_cast<uint16_t*>(smem + p.off_lists_idx);   // [128][k]
+  float* s_bias = reinterpret_cast<float*>(smem + p.off_bias);             // [4 warps][256]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bars);
+  uint64_t* full = bars;                    // [stages]
+  uint64_t* empty = bars + p.stages;        // [stages]
+  uint64_t* tfull = bars + 2 * p.stages;    // [2]
+  uint64_t* tempty = tfull + 2;             // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kc_count = (int)((p.D + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    prefetch_tensor_map(&tmap_x);
+    prefetch_tensor_map(&tmap_w);
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 4); }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        int rb, strip, t0, t1;
+        decode_unit(p, u, rb, strip, t0, t1);
+        for (int t = t0; t < t1 && ok; ++t) {
+          for (int kc = 0; kc < kc_count; ++kc) {
+            if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kWaitEmpty)) { ok = false; break; }
+            unsigned char* sa = smem + (size_t)stage * kStageBytes;
+            unsigned char* sb = sa + BM * BK * 2;
+            mbar_arrive_expect_tx(&full[stage], kStageBytes);
+            tma_load_2d(sa, &tmap_x, kc * BK, rb * BM, &full[stage]);
+            tma_load_2d(sb, &tmap_w, kc * BK, t * BN, &full[stage]);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        int rb, strip, t0, t1;
+        decode_unit(p, u, rb, strip, t0, t1);
+        for (int t = t0; t < t1 && ok; ++t) {
+          if (!mbar_wait(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+          for (int kc = 0; kc < kc_count; ++kc) {
+            if (!mbar_wait(&full[stage], phase, p.status, kWaitFull)) { ok = false; break; }
+            fence_after_sync();
+            const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
+            const uint64_t adesc = make_smem_desc_sw128(sa);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // 32 bytes per K step inside the 128-byte swizzle row
+              mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                       (kc | kk) != 0 ? 1u : 0u);
+            }
+            mma_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          mma_commit(&tfull[buf]);  // accumulator complete
+          buf ^= 1;
+          if (buf == 0) acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue: bias + ReLU + running top-k ----------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;          // row inside the tile
+    const int k = p.k;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      int rb, strip, t0, t1;
+      decode_unit(p, u, rb, strip, t0, t1);
+      const int64_t grow = (int64_t)rb * BM + row;
+      const int64_t strip_col0 = (int64_t)t0 * BN;
+      // reset this row's list
+      for (int j = 0; j < k; ++j) l_val[row * k + j] = -1.f;
+      float thr = -1.f;    // smallest value in the list (-1 while it has free slots)
+      int minpos = 0;
+      // rows past N are padding: an infinite bound keeps them out of the lists
+      const float tau = (grow < p.N) ? __ldcg(p.tau + grow) : INFINITY;
+      float thr_eff = fmaxf(thr, tau);
+      __syncwarp();
+
+      for (int t = t0; t < t1 && ok; ++t) {
+        // stage the bias of this tile (one private copy per warp: no cross-warp barrier)
+        float* sb = s_bias + (warp - 2) * BN;
+        __syncwarp();
+        for (int c = lane; c < BN; c += 32) {
+          const int64_t col = (int64_t)t * BN + c;
+          sb[c] = (col < p.M) ? __ldg(p.bias + col) : 0.f;
+        }
+        __syncwarp();
+
+        ok = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], acc_phase, p.status, kWaitTmemFull));
+        if (!ok) break;
+        fence_after_sync();
+        const int64_t tile_col0 = (int64_t)t * BN;
+        const int ncols = (int)min((int64_t)BN, p.M - tile_col0);
+        const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = fmaxf(__uint_as_float(r[i]) + sb[c * 32 + i], 0.f);
+            bool pr = (v > thr_eff) && (c * 32 + i < ncols);
+            unsigned bal = __ballot_sync(0xffffffffu, pr);
+            while (bal) {
+              const int src = __ffs(bal) - 1;
+              bal &= bal - 1;
+              const float bv = __shfl_sync(0xffffffffu, v, src);
+              const int bp = __shfl_sync(0xffffffffu, minpos, src);
+              const int lrow = q * 32 + src;
+              if (lane == 0) {
+                l_val[lrow * k + bp] = bv;
+                l_idx[lrow * k + bp] = (uint16_t)(tile_col0 - strip_col0 + c * 32 + i);
+              }
+              __syncwarp();
+              int key = 0x7fffffff, pos = 0;
+              for (int j = lane; j < k; j += 32) {
+                const int kk = __float_as_int(l_val[lrow * k + j]);
+                if (kk < key) { key = kk; pos = j; }
+              }
+              const int mn = __reduce_min_sync(0xffffffffu, key);
+              const unsigned who = __ballot_sync(0xffffffffu, key == mn);
+              const int mpos = __shfl_sync(0xffffffffu, pos, __ffs(who) - 1);
+              if (lane == src) {
+                thr = __int_as_float(mn);
+                minpos = mpos;
+                thr_eff = fmaxf(thr, tau);
+              }
+              __syncwarp();
+            }
+          }
+        }
+        // accumulator drained
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+        buf ^= 1;
+        if (buf == 0) acc_phase ^= 1;
+      }
+      if (!ok) break;
+      // write this strip's candidates and publish the row's lower bound
+      __syncwarp();
+      for (int rr = 0; rr < 32; ++rr) {
+        const int lrow = q * 32 + rr;
+        const int64_t gr = (int64_t)rb * BM + lrow;
+        if (gr >= p.N) break;
+        float* cv = p.cand_vals + (gr * p.n_strips + strip) * k;
+        int32_t* ci = p.cand_idx + (gr * p.n_strips + strip) * k;
+        for (int j = lane; j < k; j += 32) {
+          const float v = l_val[lrow * k + j];
+          cv[j] = v;
+          ci[j] = v >= 0.f ? (int32_t)(strip_col0 + l_idx[lrow * k + j]) : -1;
+        }
+      }
+      if (grow < p.N && thr >= 0.f) atomicMax(reinterpret_cast<int*>(p.tau + grow), __float_as_int(thr));
+      __syncwarp();
+    }
+  }
+
+  // teardown
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---- merge: final k of a row from its n_strips*k candidates --------------------
+// One warp per row. Candidates with value < 0 are empty slots. Output is in
+// descending value (ties: ascending index), so it does not depend on the order
+// in which the lists were filled.
+__global__ void __launch_bounds__(128)
+topk_merge_kernel(const float* __restrict__ cand_vals, const int32_t* __restrict__ cand_idx, int64_t N,
+                  int ncand, int k, float* __restrict__ top_vals, int64_t* __restrict__ top_idx) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const float* cv = cand_vals + n * ncand;
+  const int32_t* ci = cand_idx + n * ncand;
+  // 64-bit keys: value bits in the high word (values are >= 0), inverted index
+  // in the low word, so a larger key is the better candidate.
+  unsigned long long last = ~0ull;
+  for (int r = 0; r < k; ++r) {
+    unsigned long long best = 0ull;
+    for (int c = lane; c < ncand; c += 32) {
+      const float v = cv[c];
+      if (v >= 0.f) {
+        const unsigned long long key =
+            ((unsigned long long)__float_as_uint(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)ci[c]);
+        if (key < last && key > best) best = key;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    if (lane == 0) {
+      if (best != 0ull) {
+        top_vals[n * k + r] = __uint_as_float((uint32_t)(best >> 32));
+        top_idx[n * k + r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
+      } else {  // fewer than k candidates: cannot happen when M >= k
+        top_vals[n * k + r] = 0.f;
+        top_idx[n * k + r] = 0;
+      }
+    }
+    last = best;
+  }
+}
+
+int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
+  pl->n_rb = (int)((N + BM - 1) / BM);
+  pl->n_ct = (int)((M + BN - 1) / BN);
+  // Strips per row block: the fewest (longest strips, fewest list insertions)
+  // that keep the persistent grid of 148 CTAs busy; strips hold at most 255
+  // tiles so that a strip-relative column fits 16 bits.
+  const int sms = 148;
+  int min_strips = (pl->n_ct + 254) / 255;
+  int best = -1;
+  double best_eff = -1.0;
+  for (int s = min_strips; s <= pl->n_ct; ++s) {
+    const long units = (long)pl->n_rb * s;
+    const long waves = (units + sms - 1) / sms;
+    const double eff = (double)units / (double)(waves * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    if (eff >= 0.97) { best = s; break; }
+    if (pl->n_ct / s < 4 && best_eff > 0) break;  // do not shred strips below 4 tiles for balance
+  }
+  pl->n_strips = best < 1 ? 1 : best;
+  pl->units = pl->n_rb * pl->n_strips;
+  const size_t lists_val = (size_t)BM * k * sizeof(float);
+  const size_t lists_idx = (size_t)BM * k * sizeof(uint16_t);
+  const size_t fixed = lists_val + lists_idx + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
+  const size_t budget = 227 * 1024;
+  if (fixed + 2 * kStageBytes > budget) return SC_ERR_UNSUPPORTED;
+  int stages = (int)((budget - fixed) / kStageBytes);
+  if (stages > 6) stages = 6;
+  pl->stages = stages;
+  pl->off_lists_val = (size_t)stages * kStageBytes;
+  pl->off_lists_idx = pl->off_lists_val + lists_val;
+  pl->off_bias = pl->off_lists_idx + lists_idx;
+  pl->off_bars = pl->off_bias + 4 * BN * sizeof(float);
+  pl->smem = pl->off_bars + 256 + 1024;
+  return SC_OK;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+
+extern "C" size_t sc_encode_topk_workspace_bytes(int64_t N, int64_t D, int64_t M, int k) {
+  if (N <= 0 || D <= 0 || M <= 0 || k <= 0 || k > kMaxK) return 0;
+  Plan pl;
+  if (make_plan(N, D, M, k, &pl) != SC_OK) return 0;
+  const size_t cand = (size_t)N * pl.n_strips * k;
+  return align256(cand * sizeof(float)) + align256(cand * sizeof(int32_t)) + align256((size_t)N * sizeof(float));
+}
+
+extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const float* bias, int64_t N,
+                              int64_t D, int64_t M, int k, float* top_vals, int64_t* top_idx, void* ws,
+                              size_t ws_bytes, int32_t* status_word, void* stream) {
+  SC_REQUIRE(N >= 0 && D > 0 && M > 0 && k > 0, "sc_encode_topk: bad shape");
+  if (N == 0) return SC_OK;
+  SC_REQUIRE(x_bf16 && W_bf16 && bias && top_vals && top_idx && ws, "sc_encode_topk: null pointer");
+  if (k > kMaxK) return sc::fail(SC_ERR_UNSUPPORTED, "sc_encode_topk: k=%d above %d", k, kMaxK);
+  SC_REQUIRE(k <= M, "sc_encode_topk: k=%d exceeds M=%lld", k, (long long)M);
+  SC_REQUIRE(D % 8 == 0, "sc_encode_topk: D=%lld must be a multiple of 8 (16-byte row stride for TMA)",
+             (long long)D);
+  SC_REQUIRE(sc::aligned(x_bf16, 16) && sc::aligned(W_bf16, 16), "sc_encode_topk: operands must be 16-byte aligned");
+  SC_REQUIRE(N < (int64_t(1) << 31) && M < (int64_t(1) << 31), "sc_encode_topk: N, M must be below 2^31");
+  SC_REQUIRE(sc::aligned(ws, 256), "sc_encode_topk: workspace must be 256-byte aligned");
+  Plan pl;
+  if (make_plan(N, D, M, k, &pl) != SC_OK)
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_encode_topk: k=%d leaves no room for the operand ring", k);
+  const size_t need = sc_encode_topk_workspace_bytes(N, D, M, k);
+  if (ws_bytes < need) return sc::fail(SC_ERR_WORKSPACE, "sc_encode_topk: workspace %zu < %zu", ws_bytes, need);
+
+  const size_t cand = (size_t)N * pl.n_strips * k;
+  char* w = static_cast<char*>(ws);
+  float* cand_vals = reinterpret_cast<float*>(w);
+  int32_t* cand_idx = reinterpret_cast<int32_t*>(w + align256(cand * sizeof(float)));
+  float* tau = reinterpret_cast<float*>(w + align256(cand * sizeof(float)) + align256(cand * sizeof(int32_t)));
+
+  CUtensorMap tmx, tmw;
+  int rc = make_tensor_map_bf16(&tmx, x_bf16, (uint64_t)N, (uint64_t)D, BM);
+  if (rc != SC_OK) return rc;
+  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN);
+  if (rc != SC_OK) return rc;
+
+  Params p;
+  p.bias = bias; p.cand_vals = cand_vals; p.cand_idx = cand_idx; p.tau = tau; p.status = status_word;
+  p.N = N; p.D = D; p.M = M; p.k = k;
+  p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
+  p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
+  p.off_bias = (uint32_t)pl.off_bias; p.off_bars = (uint32_t)pl.off_bars;
+
+  cudaStream_t st = sc::as_stream(stream);
+  init_tau_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(tau, N, status_word);
+  SC_CHECK_LAUNCH("init_tau");
+  SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = pl.units < sms ? pl.units : sms;
+  encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
+  SC_CHECK_LAUNCH("encode_topk_tc");
+  const int ncand = pl.n_strips * k;
+  topk_merge_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(cand_vals, cand_idx, N, ncand, k, top_vals, top_idx);
+  SC_CHECK_LAUNCH("topk_merge");
+  return SC_OK;
+}

@@ -1,0 +1,120 @@
+// Loss reductions of SparseCoder.forward: total variance of the target and
+// squared error, as device scalars (no host synchronisation). All partial sums
+// are reduced in a fixed order, so results are run-to-run reproducible.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kSlices = 64;       // row slices for the column sums
+constexpr int kRedBlocks = 1024;  // partial sums of the flat reductions
+
+// partial[s][d] = sum of y[n][d] over the rows n of slice s
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const float* __restrict__ y, int64_t N, int64_t D,
+                      float* __restrict__ partial) {
+  __shared__ float s_acc[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t d = (int64_t)blockIdx.x * 32 + lane;
+  const int64_t per = (N + kSlices - 1) / kSlices;
+  const int64_t r0 = (int64_t)blockIdx.y * per;
+  const int64_t r1 = r0 + per < N ? r0 + per : N;
+  float acc = 0.f;
+  if (d < D)
+    for (int64_t r = r0 + warp; r < r1; r += 8) acc += __ldg(y + r * D + d);
+  s_acc[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += s_acc[w][lane];
+    if (d < D) partial[(int64_t)blockIdx.y * D + d] = t;
+  }
+}
+
+__global__ void colmean_finish_kernel(const float* __restrict__ partial, int64_t N, int64_t D,
+                                      float* __restrict__ mean) {
+  int64_t d = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float t = 0.f;
+  for (int s = 0; s < kSlices; ++s) t += partial[(int64_t)s * D + d];
+  mean[d] = t / (float)N;
+}
+
+// block partials of sum((a[i] - b[i % D])^2) when BROADCAST, else sum((a[i]-b[i])^2)
+template <bool BROADCAST>
+__global__ void __launch_bounds__(256)
+sqdiff_partial_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t total,
+                      int64_t D, float* __restrict__ diff, float* __restrict__ partial) {
+  __shared__ float scratch[33];
+  float acc = 0.f;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float e = __ldg(a + i) - __ldg(b + (BROADCAST ? i % D : i));
+    if (diff != nullptr) diff[i] = e;
+    acc = fmaf(e, e, acc);
+  }
+  acc = sc::block_sum(acc, scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+__global__ void __launch_bounds__(256)
+final_sum_kernel(const float* __restrict__ partial, int n, float* __restrict__ out) {
+  __shared__ float scratch[33];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
+  acc = sc::block_sum(acc, scratch);
+  if (threadIdx.x == 0) *out = acc;
+}
+
+int flat_blocks(int64_t total) {
+  int64_t b = (total + 255) / 256;
+  return (int)(b < kRedBlocks ? (b > 0 ? b : 1) : kRedBlocks);
+}
+
+}  // namespace
+
+extern "C" size_t sc_loss_workspace_bytes(int64_t D) {
+  if (D < 0) return 0;
+  return ((size_t)kSlices * D + (size_t)D + kRedBlocks) * sizeof(float);
+}
+
+extern "C" int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv, void* ws,
+                                 size_t ws_bytes, void* stream) {
+  SC_REQUIRE(N > 0 && D > 0, "sc_total_variance: bad shape");
+  SC_REQUIRE(y && tv && ws, "sc_total_variance: null pointer");
+  if (ws_bytes < sc_loss_workspace_bytes(D))
+    return sc::fail(SC_ERR_WORKSPACE, "sc_total_variance: workspace %zu < %zu", ws_bytes,
+                    sc_loss_workspace_bytes(D));
+  cudaStream_t st = sc::as_stream(stream);
+  float* partial = static_cast<float*>(ws);
+  float* mean = partial + (size_t)kSlices * D;
+  float* red = mean + D;
+  dim3 grid((unsigned)((D + 31) / 32), kSlices);
+  colsum_partial_kernel<<<grid, 256, 0, st>>>(y, N, D, partial);
+  SC_CHECK_LAUNCH("colsum_partial");
+  colmean_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, N, D, mean);
+  SC_CHECK_LAUNCH("colmean_finish");
+  const int blocks = flat_blocks(N * D);
+  sqdiff_partial_kernel<true><<<blocks, 256, 0, st>>>(y, mean, N * D, D, nullptr, red);
+  SC_CHECK_LAUNCH("sqdiff_partial");
+  final_sum_kernel<<<1, 256, 0, st>>>(red, blocks, tv);
+  SC_CHECK_LAUNCH("final_sum");
+  return SC_OK;
+}
+
+extern "C" int sc_sq_err(const float* a, const float* b, int64_t n, float* diff, float* sse,
+                         void* ws, size_t ws_bytes, void* stream) {
+  SC_REQUIRE(n > 0, "sc_sq_err: bad size");
+  SC_REQUIRE(a && b && sse && ws, "sc_sq_err: null pointer");
+  if (ws_bytes < kRedBlocks * sizeof(float))
+    return sc::fail(SC_ERR_WORKSPACE, "sc_sq_err: workspace %zu < %zu", ws_bytes,
+                    kRedBlocks * sizeof(float));
+  cudaStream_t st = sc::as_stream(stream);
+  float* red = static_cast<float*>(ws);
+  const int blocks = flat_blocks(n);
+  sqdiff_partial_kernel<false><<<blocks, 256, 0, st>>>(a, b, n, 1, diff, red);
+  SC_CHECK_LAUNCH("sqdiff_partial");
+  final_sum_kernel<<<1, 256, 0, st>>>(red, blocks, sse);
+  SC_CHECK_LAUNCH("final_sum");
+  return SC_OK;
+}
