@@ -119,19 +119,20 @@ int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M,
                  void* stream);
 
 /* Per-latent row accumulate over latents [lat_begin, lat_end):
- *   gradA[m,:] = sum_e coefA[e] * vecA[e / k, :]        (always)
- *   gradB[m,:] = sum_e coefB[e] * vecB[e / k, :]        (if gradB != NULL)
- *   grad_bias[m] = sum_e coefB[e]                        (if grad_bias != NULL)
+ *   gradA[m,:] = sum_e coefA[e] * vecA[e / k, :]   gbiasA[m] = sum_e coefA[e]
+ *   gradB[m,:] = sum_e coefB[e] * vecB[e / k, :]   gbiasB[m] = sum_e coefB[e]
  * e runs over the CSR entries of latent m; rows with no entries are zeroed.
- * vecA/vecB are [N,D] in their dtypes; coefA/coefB are fp32 [N*k]; grads fp32.
- * A = decoder (coef = acts, vec = grad_out): sparsify/xformers.py:88-136.
- * B = encoder (coef = grad_acts, vec = x'):   sparsify/fused_encoder.py:66-84. */
+ * The B operands are optional as a group (gradB == NULL), gbiasA / gbiasB are
+ * optional individually. vecA/vecB are [N,D] in their dtypes; coefA/coefB are
+ * fp32 [N*k]; gradients are fp32. D must be a multiple of 4.
+ * Decoder use (coef = acts, vec = grad_out): sparsify/xformers.py:88-136.
+ * Encoder use (coef = grad_acts, vec = x', bias): sparsify/fused_encoder.py:66-84. */
 int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries, int k,
                        const float* coefA, const void* vecA, int vecA_dtype,
-                       float* gradA, const float* coefB, const void* vecB,
-                       int vecB_dtype, float* gradB, float* grad_bias,
-                       int64_t M, int64_t D, int64_t lat_begin, int64_t lat_end,
-                       void* stream);
+                       float* gradA, float* gbiasA, const float* coefB,
+                       const void* vecB, int vecB_dtype, float* gradB,
+                       float* gbiasB, int64_t M, int64_t D, int64_t lat_begin,
+                       int64_t lat_end, void* stream);
 
 /* ---- losses -------------------------------------------------------------
  * sparsify/sparse_coder.py:225-228,253-254:

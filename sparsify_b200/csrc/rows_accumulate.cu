@@ -5,7 +5,7 @@
 // writes the full row of the gradient (zeros when the latent did not fire), so
 // the [M,D] gradient needs no separate zero fill and no atomics, and the sum
 // order is fixed by the CSR. The decoder gradient (A) and the encoder gradient
-// (B) share the segment walk; the bias gradient is the plain sum of coefB.
+// (B) share the segment walk; a bias gradient is the plain sum of the coefficients.
 #include "common.cuh"
 
 namespace {
@@ -17,16 +17,22 @@ template <typename TA, typename TB, bool HAS_B>
 __global__ void __launch_bounds__(kAccThreads)
 rows_accumulate_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ entries,
                        int k, const float* __restrict__ coefA, const TA* __restrict__ vecA,
-                       float* __restrict__ gradA, const float* __restrict__ coefB,
-                       const TB* __restrict__ vecB, float* __restrict__ gradB,
-                       float* __restrict__ grad_bias, int64_t D, int64_t lat_begin) {
+                       float* __restrict__ gradA, float* __restrict__ gbiasA,
+                       const float* __restrict__ coefB, const TB* __restrict__ vecB,
+                       float* __restrict__ gradB, float* __restrict__ gbiasB, int64_t D,
+                       int64_t lat_begin) {
   const int64_t m = lat_begin + blockIdx.x;
   const int32_t lo = row_ptr[m], hi = row_ptr[m + 1];
 
-  if (HAS_B && grad_bias != nullptr && threadIdx.x == 0) {
+  if (gbiasA != nullptr && threadIdx.x == 0) {
+    float s = 0.f;
+    for (int32_t p = lo; p < hi; ++p) s += coefA[entries[p]];
+    gbiasA[m] = s;
+  }
+  if (HAS_B && gbiasB != nullptr && threadIdx.x == 32) {
     float s = 0.f;
     for (int32_t p = lo; p < hi; ++p) s += coefB[entries[p]];
-    grad_bias[m] = s;
+    gbiasB[m] = s;
   }
 
   const int64_t sweep = (int64_t)kAccThreads * 4 * kNch;
@@ -78,16 +84,16 @@ rows_accumulate_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __res
 
 template <typename TA, typename TB>
 int launch(const int32_t* row_ptr, const int32_t* entries, int k, const float* coefA,
-           const void* vecA, float* gradA, const float* coefB, const void* vecB, float* gradB,
-           float* grad_bias, int64_t D, int64_t lat_begin, int64_t nlat, cudaStream_t st) {
+           const void* vecA, float* gradA, float* gbiasA, const float* coefB, const void* vecB,
+           float* gradB, float* gbiasB, int64_t D, int64_t lat_begin, int64_t nlat, cudaStream_t st) {
   dim3 grid((unsigned)nlat), block(kAccThreads);
   if (gradB != nullptr) {
     rows_accumulate_kernel<TA, TB, true><<<grid, block, 0, st>>>(
-        row_ptr, entries, k, coefA, static_cast<const TA*>(vecA), gradA, coefB,
-        static_cast<const TB*>(vecB), gradB, grad_bias, D, lat_begin);
+        row_ptr, entries, k, coefA, static_cast<const TA*>(vecA), gradA, gbiasA, coefB,
+        static_cast<const TB*>(vecB), gradB, gbiasB, D, lat_begin);
   } else {
     rows_accumulate_kernel<TA, TB, false><<<grid, block, 0, st>>>(
-        row_ptr, entries, k, coefA, static_cast<const TA*>(vecA), gradA, nullptr, nullptr,
+        row_ptr, entries, k, coefA, static_cast<const TA*>(vecA), gradA, gbiasA, nullptr, nullptr,
         nullptr, nullptr, D, lat_begin);
   }
   SC_CHECK_LAUNCH("sc_rows_accumulate");
@@ -98,9 +104,10 @@ int launch(const int32_t* row_ptr, const int32_t* entries, int k, const float* c
 
 extern "C" int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries, int k,
                                   const float* coefA, const void* vecA, int vecA_dtype,
-                                  float* gradA, const float* coefB, const void* vecB,
-                                  int vecB_dtype, float* gradB, float* grad_bias, int64_t M,
-                                  int64_t D, int64_t lat_begin, int64_t lat_end, void* stream) {
+                                  float* gradA, float* gbiasA, const float* coefB,
+                                  const void* vecB, int vecB_dtype, float* gradB, float* gbiasB,
+                                  int64_t M, int64_t D, int64_t lat_begin, int64_t lat_end,
+                                  void* stream) {
   SC_REQUIRE(M > 0 && D > 0 && k > 0, "sc_rows_accumulate: bad shape");
   SC_REQUIRE(0 <= lat_begin && lat_begin <= lat_end && lat_end <= M,
              "sc_rows_accumulate: latent range [%lld,%lld) outside [0,%lld)", (long long)lat_begin,
@@ -114,7 +121,7 @@ extern "C" int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries
     SC_REQUIRE(coefB && vecB && sc::valid_dtype(vecB_dtype), "sc_rows_accumulate: B operands missing");
     SC_REQUIRE(sc::aligned(vecB, 16) && sc::aligned(gradB, 16), "sc_rows_accumulate: B pointers must be 16-byte aligned");
   } else {
-    SC_REQUIRE(grad_bias == nullptr, "sc_rows_accumulate: grad_bias needs the B operands");
+    SC_REQUIRE(gbiasB == nullptr, "sc_rows_accumulate: gbiasB needs the B operands");
     vecB_dtype = SC_F32;
   }
   cudaStream_t st = sc::as_stream(stream);
@@ -122,10 +129,10 @@ extern "C" int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries
   SC_REQUIRE(nlat <= 0x7fffffffLL, "sc_rows_accumulate: too many latents in one call");
   using bf16 = __nv_bfloat16;
   if (vecA_dtype == SC_F32 && vecB_dtype == SC_F32)
-    return launch<float, float>(row_ptr, entries, k, coefA, vecA, gradA, coefB, vecB, gradB, grad_bias, D, lat_begin, nlat, st);
+    return launch<float, float>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
   if (vecA_dtype == SC_F32 && vecB_dtype == SC_BF16)
-    return launch<float, bf16>(row_ptr, entries, k, coefA, vecA, gradA, coefB, vecB, gradB, grad_bias, D, lat_begin, nlat, st);
+    return launch<float, bf16>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
   if (vecA_dtype == SC_BF16 && vecB_dtype == SC_F32)
-    return launch<bf16, float>(row_ptr, entries, k, coefA, vecA, gradA, coefB, vecB, gradB, grad_bias, D, lat_begin, nlat, st);
-  return launch<bf16, bf16>(row_ptr, entries, k, coefA, vecA, gradA, coefB, vecB, gradB, grad_bias, D, lat_begin, nlat, st);
+    return launch<bf16, float>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
+  return launch<bf16, bf16>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
 }

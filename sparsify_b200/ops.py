@@ -1,0 +1,262 @@
+"""Thin functional wrappers over the C ABI: allocate outputs and workspaces as
+torch tensors, pass raw device pointers and the current stream. No autograd
+here; see fused_encoder.py and embedding_bag.py for the differentiable ops."""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import call, dtype_code, ptr
+
+
+def _stream(t: Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ws(nbytes: int, device) -> Tensor:
+    # torch's caching allocator returns 512-byte aligned blocks
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _check_cuda(*ts: Tensor | None):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "sparsify_b200 runs on CUDA tensors only; there is no CPU path "
+                f"(got a tensor on {t.device})"
+            )
+
+
+def prep_input(x: Tensor, b_dec: Tensor | None, out_dtype: torch.dtype) -> Tensor:
+    """x - b_dec (row broadcast) cast to out_dtype."""
+    _check_cuda(x, b_dec)
+    x = x.contiguous()
+    N, D = x.shape
+    out = torch.empty(N, D, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        call("sc_prep_input", ptr(x), dtype_code(x), ptr(_f32(b_dec)), N, D, ptr(out),
+             dtype_code(out), _stream(x))
+    return out
+
+
+def _f32(t: Tensor | None) -> Tensor | None:
+    if t is None:
+        return None
+    return t.detach().to(torch.float32).contiguous()
+
+
+def preacts_dense(x: Tensor, W: Tensor, bias: Tensor | None, out_dtype=torch.float32) -> Tensor:
+    _check_cuda(x, W, bias)
+    x, W = x.detach().contiguous(), W.detach().contiguous()
+    N, D = x.shape
+    M = W.shape[0]
+    pre = torch.empty(N, M, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        call("sc_preacts_dense", ptr(x), dtype_code(x), ptr(W), dtype_code(W), ptr(_f32(bias)),
+             N, D, M, ptr(pre), dtype_code(pre), _stream(x))
+    return pre
+
+
+def topk_rows(pre: Tensor, k: int, col_mask: Tensor | None = None) -> tuple[Tensor, Tensor]:
+    _check_cuda(pre, col_mask)
+    pre = pre.detach().to(torch.float32).contiguous()
+    N, M = pre.shape
+    vals = torch.empty(N, k, dtype=torch.float32, device=pre.device)
+    idx = torch.empty(N, k, dtype=torch.int64, device=pre.device)
+    mask = None
+    if col_mask is not None:
+        mask = col_mask.to(torch.uint8).contiguous()
+    with torch.cuda.device(pre.device):
+        call("sc_topk_rows", ptr(pre), N, M, int(k), ptr(mask), ptr(vals), ptr(idx), _stream(pre))
+    return vals, idx
+
+
+def groupmax_rows(pre: Tensor, k: int) -> tuple[Tensor, Tensor]:
+    _check_cuda(pre)
+    pre = pre.detach().to(torch.float32).contiguous()
+    N, M = pre.shape
+    vals = torch.empty(N, k, dtype=torch.float32, device=pre.device)
+    idx = torch.empty(N, k, dtype=torch.int64, device=pre.device)
+    with torch.cuda.device(pre.device):
+        call("sc_groupmax_rows", ptr(pre), N, M, int(k), ptr(vals), ptr(idx), _stream(pre))
+    return vals, idx
+
+
+def tc_encode_supported(D: int, M: int, k: int) -> bool:
+    return D % 8 == 0 and 0 < k <= 128 and k <= M
+
+
+def encode_topk_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tuple[Tensor, Tensor]:
+    """Tensor-core encoder: relu(x W^T + b) and exact per-row top-k, never
+    materialising the [N, M] matrix. Values come out in descending order."""
+    _check_cuda(x_bf16, W_bf16, bias)
+    assert x_bf16.dtype == torch.bfloat16 and W_bf16.dtype == torch.bfloat16
+    x_bf16, W_bf16 = x_bf16.contiguous(), W_bf16.contiguous()
+    N, D = x_bf16.shape
+    M = W_bf16.shape[0]
+    dev = x_bf16.device
+    vals = torch.empty(N, k, dtype=torch.float32, device=dev)
+    idx = torch.empty(N, k, dtype=torch.int64, device=dev)
+    nbytes = _lib.lib().sc_encode_topk_workspace_bytes(N, D, M, int(k))
+    ws = _ws(nbytes, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        call("sc_encode_topk", ptr(x_bf16), ptr(W_bf16), ptr(_f32(bias)), N, D, M, int(k),
+             ptr(vals), ptr(idx), ptr(ws), ws.numel(), ptr(status), _stream(x_bf16))
+    encode_topk_tc.last_status = status
+    return vals, idx
+
+
+def embedding_bag_fwd(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None = None) -> Tensor:
+    """out[n] = bias + sum_j acts[n, j] * W[idx[n, j]], fp32."""
+    _check_cuda(idx, acts, W, bias)
+    idx = idx.contiguous()
+    acts = _f32(acts)
+    W = W.detach().contiguous()
+    N, k = idx.shape
+    M, D = W.shape
+    out = torch.empty(N, D, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        call("sc_embedding_bag_fwd", ptr(idx), ptr(acts), ptr(W), dtype_code(W), ptr(_f32(bias)),
+             N, D, M, int(k), ptr(out), _stream(W))
+    return out
+
+
+def embedding_bag_bwd_acts(idx: Tensor, grad_out: Tensor, W: Tensor) -> Tensor:
+    _check_cuda(idx, grad_out, W)
+    idx = idx.contiguous()
+    grad_out = _f32(grad_out)
+    W = W.detach().contiguous()
+    N, k = idx.shape
+    M, D = W.shape
+    gacts = torch.empty(N, k, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        call("sc_embedding_bag_bwd_acts", ptr(idx), ptr(grad_out), ptr(W), dtype_code(W), N, D, M,
+             int(k), ptr(gacts), _stream(W))
+    return gacts
+
+
+def csr_build(idx: Tensor, M: int) -> tuple[Tensor, Tensor]:
+    """Latent-major CSR (row_ptr[M+1], entries[N*k]) of an [N, k] index matrix."""
+    _check_cuda(idx)
+    idx = idx.contiguous()
+    N, k = idx.shape
+    dev = idx.device
+    row_ptr = torch.empty(M + 1, dtype=torch.int32, device=dev)
+    entries = torch.empty(max(N * k, 1), dtype=torch.int32, device=dev)
+    ws = _ws(_lib.lib().sc_csr_workspace_bytes(M), dev)
+    with torch.cuda.device(dev):
+        call("sc_csr_build", ptr(idx), N, int(k), int(M), ptr(row_ptr), ptr(entries), ptr(ws),
+             ws.numel(), _stream(idx))
+    return row_ptr, entries
+
+
+def rows_accumulate(
+    row_ptr: Tensor,
+    entries: Tensor,
+    k: int,
+    M: int,
+    D: int,
+    coefA: Tensor,
+    vecA: Tensor,
+    *,
+    biasA: bool = False,
+    coefB: Tensor | None = None,
+    vecB: Tensor | None = None,
+    biasB: bool = False,
+    lat_range: tuple[int, int] | None = None,
+    out: dict | None = None,
+) -> dict:
+    """Per-latent sums of coef * vec rows; returns {"gradA", "gbiasA", "gradB", "gbiasB"}.
+    `out` may supply preallocated [M, D] / [M] tensors under the same keys (used
+    when the gradient is produced chunk by chunk over latent ranges)."""
+    _check_cuda(row_ptr, entries, coefA, vecA, coefB, vecB)
+    dev = vecA.device
+    out = dict(out or {})
+    coefA = _f32(coefA).reshape(-1)
+    vecA = vecA.detach().contiguous()
+    has_b = coefB is not None
+    if has_b:
+        coefB = _f32(coefB).reshape(-1)
+        vecB = vecB.detach().contiguous()
+    def buf(name, shape, want):
+        if not want:
+            return None
+        if out.get(name) is None:
+            out[name] = torch.empty(shape, dtype=torch.float32, device=dev)
+        return out[name]
+    gA = buf("gradA", (M, D), True)
+    gbA = buf("gbiasA", (M,), biasA)
+    gB = buf("gradB", (M, D), has_b)
+    gbB = buf("gbiasB", (M,), has_b and biasB)
+    lo, hi = lat_range if lat_range is not None else (0, M)
+    with torch.cuda.device(dev):
+        call("sc_rows_accumulate", ptr(row_ptr), ptr(entries), int(k), ptr(coefA), ptr(vecA),
+             dtype_code(vecA), ptr(gA), ptr(gbA), ptr(coefB), ptr(vecB),
+             dtype_code(vecB) if has_b else 0, ptr(gB), ptr(gbB), int(M), int(D), int(lo), int(hi),
+             _stream(vecA))
+    return out
+
+
+def total_variance(y: Tensor) -> Tensor:
+    """sum((y - y.mean(0))**2) as a 0-d fp32 device tensor."""
+    _check_cuda(y)
+    y = _f32(y)
+    N, D = y.shape
+    tv = torch.empty((), dtype=torch.float32, device=y.device)
+    ws = _ws(_lib.lib().sc_loss_workspace_bytes(D), y.device)
+    with torch.cuda.device(y.device):
+        call("sc_total_variance", ptr(y), N, D, ptr(tv), ptr(ws), ws.numel(), _stream(y))
+    return tv
+
+
+def sq_err(a: Tensor, b: Tensor, want_diff: bool = False) -> tuple[Tensor, Tensor | None]:
+    """(sum((a-b)**2), a-b or None)."""
+    _check_cuda(a, b)
+    a, b = _f32(a), _f32(b)
+    assert a.shape == b.shape
+    sse = torch.empty((), dtype=torch.float32, device=a.device)
+    diff = torch.empty_like(a) if want_diff else None
+    ws = _ws(4096, a.device)
+    with torch.cuda.device(a.device):
+        call("sc_sq_err", ptr(a), ptr(b), a.numel(), ptr(diff), ptr(sse), ptr(ws), ws.numel(),
+             _stream(a))
+    return sse, diff
+
+
+def normalize_rows_(W: Tensor, eps: float, shadow: Tensor | None = None) -> None:
+    """In place W[m] /= ||W[m]|| + eps; optionally refreshes a bf16 shadow."""
+    _check_cuda(W, shadow)
+    assert W.dtype == torch.float32 and W.is_contiguous()
+    M, D = W.shape
+    with torch.cuda.device(W.device):
+        call("sc_normalize_rows", ptr(W), M, D, float(eps), ptr(shadow), _stream(W))
+
+
+def adam_rows_(p: Tensor, g: Tensor, m: Tensor, v: Tensor, *, lr: float, beta1: float, beta2: float,
+               eps: float, step: int, project: bool = False, shadow: Tensor | None = None) -> None:
+    """One Adam step on p (any shape; rows = leading dim) with optional removal of
+    the gradient component parallel to each row of p, optional bf16 shadow refresh."""
+    _check_cuda(p, g, m, v, shadow)
+    for t in (p, g, m, v):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    if p.dim() >= 2:
+        M, D = p.shape[0], p.numel() // p.shape[0]
+    else:
+        M, D = 1, p.numel()
+    with torch.cuda.device(p.device):
+        call("sc_adam_rows", ptr(p), ptr(g), ptr(m), ptr(v), M, D, float(lr), float(beta1),
+             float(beta2), float(eps), int(step), int(bool(project)), ptr(shadow), _stream(p))
+
+
+def cast_bf16(src: Tensor, dst: Tensor | None = None) -> Tensor:
+    _check_cuda(src, dst)
+    src = src.detach()
+    assert src.dtype == torch.float32 and src.is_contiguous()
+    if dst is None:
+        dst = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    with torch.cuda.device(src.device):
+        call("sc_cast_bf16", ptr(src), ptr(dst), src.numel(), _stream(src))
+    return dst

@@ -1,0 +1,293 @@
+"""SparseCoder with the reference's surface (sparsify/sparse_coder.py:38-299):
+same parameters (`encoder.weight`, `encoder.bias`, `W_dec`, `b_dec`, `W_skip`),
+`encode` / `decode` / `forward`, the `sae.safetensors` + `cfg.json` checkpoint
+layout, and the decoder-norm utilities - computed by the CUDA kernels of
+libsparsecoder instead of eager PyTorch / Triton.
+
+Precision. The reference runs `forward` under a CUDA bf16 autocast
+(sparsify/sparse_coder.py:205-209) with fp32 parameters. Here the attribute
+`precision` selects:
+  "bf16"  encoder GEMM on bf16 copies of x and W_enc (tensor cores, fp32
+          accumulate) and bf16 copies of W_dec / W_enc for the row gathers;
+  "mixed" bf16 encoder GEMM, fp32 rows for the gathers (what autocast does);
+  "fp32"  everything in fp32 (what the reference computes on CPU).
+The bf16 copies ("shadows") are cached per parameter and re-cast only when the
+parameter's version counter has moved.
+"""
+
+from __future__ import annotations
+
+import json
+import re
+from fnmatch import fnmatch
+from pathlib import Path
+from typing import NamedTuple
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import load_model, save_model
+from torch import Tensor, nn
+
+from . import ops
+from .config import SparseCoderConfig
+from .fused_encoder import EncoderOutput, fused_encoder
+from .utils import decoder_impl
+
+
+def natsorted(seq, key=None):
+    """Natural sort (digit runs compare as numbers), as natsort.natsorted does
+    for the hookpoint names the reference sorts (sparsify/trainer.py:48)."""
+    def split(s):
+        return [int(t) if t.isdigit() else t for t in re.split(r"(\d+)", str(s))]
+    return sorted(seq, key=(lambda v: split(key(v))) if key else split)
+
+
+class ForwardOutput(NamedTuple):
+    sae_out: Tensor
+
+    latent_acts: Tensor
+    """Activations of the top-k latents."""
+
+    latent_indices: Tensor
+    """Indices of the top-k features."""
+
+    fvu: Tensor
+    """Fraction of variance unexplained."""
+
+    auxk_loss: Tensor
+    """AuxK loss, if applicable."""
+
+    multi_topk_fvu: Tensor
+    """Multi-TopK FVU, if applicable."""
+
+
+class SparseCoder(nn.Module):
+    def __init__(
+        self,
+        d_in: int,
+        cfg: SparseCoderConfig,
+        device: str | torch.device = "cpu",
+        dtype: torch.dtype | None = None,
+        *,
+        decoder: bool = True,
+    ):
+        super().__init__()
+        self.cfg = cfg
+        self.d_in = d_in
+        self.num_latents = cfg.num_latents or d_in * cfg.expansion_factor
+        self.precision = "bf16"
+        self._shadows: dict[str, tuple[int, int, Tensor]] = {}
+
+        self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
+        self.encoder.bias.data.zero_()
+
+        if decoder:
+            if cfg.transcode:
+                # transcoder: decoder starts at zero (sparsify/sparse_coder.py:57-59)
+                self.W_dec = nn.Parameter(torch.zeros_like(self.encoder.weight.data))
+            else:
+                # autoencoder: decoder starts as the (row-normalised) encoder
+                self.W_dec = nn.Parameter(self.encoder.weight.data.clone())
+                if self.cfg.normalize_decoder:
+                    self.set_decoder_norm_to_unit_norm()
+        else:
+            self.W_dec = None
+
+        self.b_dec = nn.Parameter(torch.zeros(d_in, dtype=dtype, device=device))
+        self.W_skip = (
+            nn.Parameter(torch.zeros(d_in, d_in, device=device, dtype=dtype))
+            if cfg.skip_connection
+            else None
+        )
+
+    # ------------------------------------------------------------------ loading
+    @staticmethod
+    def load_many(
+        name: str,
+        local: bool = False,
+        layers: list[str] | None = None,
+        device: str | torch.device = "cpu",
+        *,
+        decoder: bool = True,
+        pattern: str | None = None,
+    ) -> dict[str, "SparseCoder"]:
+        """Load sparse coders for several hookpoints from one directory tree."""
+        pattern = pattern + "/*" if pattern is not None else None
+        if not local:
+            raise NotImplementedError(
+                "Downloading from the HuggingFace Hub is outside this package; "
+                "fetch the repository yourself and pass local=True."
+            )
+        repo_path = Path(name)
+        if layers is not None:
+            return {
+                layer: SparseCoder.load_from_disk(repo_path / layer, device=device, decoder=decoder)
+                for layer in natsorted(layers)
+            }
+        files = [
+            f for f in repo_path.iterdir()
+            if f.is_dir() and (pattern is None or fnmatch(f.name, pattern))
+        ]
+        return {
+            f.name: SparseCoder.load_from_disk(f, device=device, decoder=decoder)
+            for f in natsorted(files, key=lambda f: f.name)
+        }
+
+    @staticmethod
+    def load_from_disk(
+        path: Path | str,
+        device: str | torch.device = "cpu",
+        *,
+        decoder: bool = True,
+    ) -> "SparseCoder":
+        path = Path(path)
+        with open(path / "cfg.json", "r") as f:
+            cfg_dict = json.load(f)
+            d_in = cfg_dict.pop("d_in")
+            cfg = SparseCoderConfig.from_dict(cfg_dict, drop_extra_fields=True)
+
+        safetensors_path = str(path / "sae.safetensors")
+        with safe_open(safetensors_path, framework="pt", device="cpu") as f:
+            first_key = next(iter(f.keys()))
+            reference_dtype = f.get_tensor(first_key).dtype
+
+        sae = SparseCoder(d_in, cfg, device=device, decoder=decoder, dtype=reference_dtype)
+        load_model(model=sae, filename=safetensors_path, device=str(device), strict=decoder)
+        return sae
+
+    def save_to_disk(self, path: Path | str):
+        path = Path(path)
+        path.mkdir(parents=True, exist_ok=True)
+        save_model(self, str(path / "sae.safetensors"))
+        with open(path / "cfg.json", "w") as f:
+            json.dump({**self.cfg.to_dict(), "d_in": self.d_in}, f)
+
+    @property
+    def device(self):
+        return self.encoder.weight.device
+
+    @property
+    def dtype(self):
+        return self.encoder.weight.dtype
+
+    # ------------------------------------------------------------------ shadows
+    def shadow(self, name: str) -> Tensor | None:
+        """bf16 copy of parameter `name` ("encoder.weight" or "W_dec"), re-cast
+        when the parameter was modified in place since the copy was made."""
+        p = self.encoder.weight if name == "encoder.weight" else getattr(self, name)
+        if p is None:
+            return None
+        if p.dtype == torch.bfloat16:
+            return p.detach()
+        hit = self._shadows.get(name)
+        if hit is not None and hit[0] == p.data_ptr() and hit[1] == p._version:
+            return hit[2]
+        buf = hit[2] if hit is not None and hit[2].shape == p.shape and hit[2].device == p.device else None
+        buf = ops.cast_bf16(p.detach().contiguous(), buf)
+        self._shadows[name] = (p.data_ptr(), p._version, buf)
+        return buf
+
+    def mark_shadow_fresh(self, name: str, buf: Tensor) -> None:
+        """Records that `buf` holds the bf16 image of the parameter's current
+        value (a fused update kernel wrote both)."""
+        p = self.encoder.weight if name == "encoder.weight" else getattr(self, name)
+        self._shadows[name] = (p.data_ptr(), p._version, buf)
+
+    def _lowp(self) -> bool:
+        return self.precision in ("bf16", "mixed") and self.dtype == torch.float32 or self.dtype == torch.bfloat16
+
+    # ------------------------------------------------------------------ compute
+    def encode(self, x: Tensor, *, need_pre_acts: bool = True) -> EncoderOutput:
+        """Encode the input and select the top-k latents."""
+        if not self.cfg.transcode:
+            x = x - self.b_dec
+        lowp = self._lowp()
+        if lowp:
+            w_lp = self.shadow("encoder.weight")
+        else:
+            w_lp = None
+            x = x.to(torch.float32)
+        return fused_encoder(
+            x, self.encoder.weight, self.encoder.bias, self.cfg.k, self.cfg.activation,
+            need_pre_acts=need_pre_acts, weight_bf16=w_lp,
+        )
+
+    def decode(self, top_acts: Tensor, top_indices: Tensor) -> Tensor:
+        assert self.W_dec is not None, "Decoder weight was not initialized."
+        w_lp = self.shadow("W_dec") if (self.precision == "bf16" and self.dtype == torch.float32) else None
+        y = decoder_impl(top_indices, top_acts.to(self.dtype), self.W_dec.mT, w_lp)
+        return y + self.b_dec
+
+    def forward(
+        self, x: Tensor, y: Tensor | None = None, *, dead_mask: Tensor | None = None
+    ) -> ForwardOutput:
+        num_dead = int(dead_mask.sum()) if dead_mask is not None else 0
+        need_dense = self.cfg.multi_topk or num_dead > 0
+        top_acts, top_indices, pre_acts = self.encode(x, need_pre_acts=need_dense)
+
+        # If we aren't given a distinct target, we're autoencoding
+        if y is None:
+            y = x
+        y = y.to(torch.float32)
+
+        sae_out = self.decode(top_acts, top_indices)
+        if self.W_skip is not None:
+            sae_out += x.to(self.dtype) @ self.W_skip.mT
+
+        e = y - sae_out
+
+        # Used as a denominator for putting everything on a reasonable scale
+        total_variance = ops.total_variance(y.detach())
+
+        if num_dead > 0:
+            # Heuristic from Appendix B.1 of the TopK SAE paper, as in the reference
+            k_aux = y.shape[-1] // 2
+            scale = min(num_dead / k_aux, 1.0)
+            k_aux = min(k_aux, num_dead)
+
+            # top-k_aux among dead latents only; no gradient reaches the encoder
+            auxk_acts, auxk_indices = ops.topk_rows(pre_acts, k_aux, col_mask=dead_mask)
+
+            e_hat = self.decode(auxk_acts, auxk_indices)
+            auxk_loss = (e_hat - e.detach()).pow(2).sum()
+            auxk_loss = scale * auxk_loss / total_variance
+        else:
+            auxk_loss = sae_out.new_tensor(0.0)
+
+        l2_loss = e.pow(2).sum()
+        fvu = l2_loss / total_variance
+
+        if self.cfg.multi_topk:
+            top_acts, top_indices = ops.topk_rows(pre_acts, 4 * self.cfg.k)
+            sae_out = self.decode(top_acts, top_indices)
+            multi_topk_fvu = (sae_out - y).pow(2).sum() / total_variance
+        else:
+            multi_topk_fvu = sae_out.new_tensor(0.0)
+
+        return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, multi_topk_fvu)
+
+    # ------------------------------------------------------------------ decoder norm
+    @torch.no_grad()
+    def set_decoder_norm_to_unit_norm(self):
+        assert self.W_dec is not None, "Decoder weight was not initialized."
+        eps = torch.finfo(self.W_dec.dtype).eps
+        W = self.W_dec.data
+        if W.is_cuda and W.dtype == torch.float32 and W.is_contiguous():
+            ops.normalize_rows_(W, eps)
+            self.W_dec.add_(0)  # bump the version counter: the kernel wrote through a raw pointer
+        else:
+            # construction / checkpoint handling on the host before .to("cuda")
+            norm = torch.norm(W, dim=1, keepdim=True)
+            self.W_dec.data /= norm + eps
+
+    @torch.no_grad()
+    def remove_gradient_parallel_to_decoder_directions(self):
+        assert self.W_dec is not None, "Decoder weight was not initialized."
+        assert self.W_dec.grad is not None
+        g, w = self.W_dec.grad, self.W_dec.data
+        parallel = (g * w).sum(dim=1, keepdim=True)
+        g -= parallel * w
+
+
+# Allow for alternate naming conventions
+Sae = SparseCoder

@@ -1,0 +1,273 @@
+"""Generates tests/golden/*.safetensors by running the REFERENCE implementation
+(EleutherAI/sparsify v1.3.0, unmodified, imported from its source tree) on CPU
+with seeded inputs. Run once where the reference tree is available:
+
+    SPARSIFY_REF=/path/to/sparsify python tests/golden/make_golden.py
+
+The reference's non-arithmetic dependencies that are not installed here
+(natsort, simple_parsing, accelerate, schedulefree) are replaced by small stub
+modules; none of them takes part in the arithmetic that is frozen. The fixtures
+are what the oracle (oracle/sae_oracle.py) is pinned against.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+import re
+import sys
+import tempfile
+import types
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def import_reference():
+    root = os.environ.get("SPARSIFY_REF", "/root/reference")
+    if not Path(root, "sparsify", "fused_encoder.py").exists():
+        raise SystemExit(f"reference tree not found at {root}; set SPARSIFY_REF")
+    os.environ["SPARSIFY_DISABLE_TRITON"] = "1"
+    import transformers  # noqa: F401  (must precede the accelerate stub)
+
+    def natsorted(seq, key=None):
+        def split(s):
+            return [int(t) if t.isdigit() else t for t in re.split(r"(\d+)", str(s))]
+        return sorted(seq, key=(lambda v: split(key(v))) if key else split)
+
+    natsort = types.ModuleType("natsort")
+    natsort.natsorted = natsorted
+
+    class Serializable:
+        def to_dict(self):
+            return dataclasses.asdict(self)
+
+        @classmethod
+        def from_dict(cls, d, drop_extra_fields=False):
+            names = {f.name for f in dataclasses.fields(cls)}
+            return cls(**{k: v for k, v in d.items() if k in names})
+
+        def save_json(self, path):
+            with open(path, "w") as f:
+                json.dump(self.to_dict(), f)
+
+    sp = types.ModuleType("simple_parsing")
+    sp.Serializable = Serializable
+    sp.list_field = lambda *d: dataclasses.field(default_factory=lambda: list(d))
+    sp.field = dataclasses.field
+    sp.parse = lambda *a, **k: None
+
+    acc = types.ModuleType("accelerate")
+    acc_utils = types.ModuleType("accelerate.utils")
+    acc_utils.send_to_device = lambda obj, device: obj
+    acc.utils = acc_utils
+
+    sf = types.ModuleType("schedulefree")
+    sf.ScheduleFreeWrapper = type("ScheduleFreeWrapper", (), {})
+
+    for name, mod in [("natsort", natsort), ("simple_parsing", sp), ("accelerate", acc),
+                      ("accelerate.utils", acc_utils), ("schedulefree", sf)]:
+        sys.modules.setdefault(name, mod)
+    sys.path.insert(0, root)
+    import sparsify  # noqa: F401
+    return sparsify
+
+
+def save(name: str, tensors: dict, meta: dict | None = None):
+    from safetensors.torch import save_file
+    tensors = {k: v.detach().contiguous().clone() for k, v in tensors.items()}
+    save_file(tensors, str(HERE / f"{name}.safetensors"),
+              metadata={k: json.dumps(v) for k, v in (meta or {}).items()})
+    print(f"wrote {name}.safetensors: {sorted(tensors)}")
+
+
+def sorted_topk(vals, idx):
+    """Canonical order (descending value) so unsorted top-k results compare."""
+    order = torch.argsort(vals, dim=-1, descending=True, stable=True)
+    return vals.gather(-1, order), idx.gather(-1, order)
+
+
+def gen_encoder(sparsify):
+    from sparsify.fused_encoder import fused_encoder
+    for tag, act, (N, D, M, k) in [("topk", "topk", (48, 40, 256, 8)), ("groupmax", "groupmax", (24, 32, 128, 8))]:
+        g = torch.Generator().manual_seed(42)
+        x = torch.randn(N, D, generator=g, requires_grad=True)
+        W = torch.randn(M, D, generator=g, requires_grad=True)
+        b = torch.randn(M, generator=g, requires_grad=True)
+        coef = torch.randn(N, k, generator=g)
+        vals, idx, pre = fused_encoder(x, W, b, k, act)
+        # coefficients follow the canonical order so the gradient is order-free
+        svals, sidx = sorted_topk(vals, idx)
+        order = torch.argsort(vals, dim=-1, descending=True, stable=True)
+        loss = (vals.gather(-1, order) * coef).sum()
+        loss.backward()
+        save(f"encoder_{tag}", dict(x=x, W=W, b=b, coef=coef, vals=svals, idx=sidx, pre=pre,
+                                    gx=x.grad, gW=W.grad, gb=b.grad), dict(k=k, activation=act))
+
+
+def gen_decoder(sparsify):
+    from sparsify.utils import eager_decode
+    for d_in in (48, 64):
+        g = torch.Generator().manual_seed(7 + d_in)
+        batch, d_sae, k = 2, 128, 10
+        latents = torch.rand(batch, d_sae, generator=g)
+        W_dec = torch.randn(d_sae, d_in, generator=g, requires_grad=True)
+        vals, idx = latents.topk(k)
+        vals = vals.clone().requires_grad_(True)
+        out = eager_decode(idx, vals, W_dec.mT)
+        gout = torch.randn(batch, d_in, generator=g)
+        (out * gout).sum().backward()
+        save(f"decoder_d{d_in}", dict(idx=idx, acts=vals, W_dec=W_dec, out=out, gout=gout,
+                                      gW=W_dec.grad, gacts=vals.grad), dict(k=k))
+
+
+def gen_forward(sparsify):
+    from sparsify import SparseCoder, SparseCoderConfig
+    cases = {
+        "sae_plain": dict(cfg=dict(k=4), dead=False),
+        "sae_auxk": dict(cfg=dict(k=4), dead=True),
+        "sae_multitopk": dict(cfg=dict(k=4, multi_topk=True), dead=True),
+        "transcoder_skip": dict(cfg=dict(k=4, transcode=True, skip_connection=True), dead=False),
+    }
+    N, D, M = 80, 32, 256
+    alpha = 1 / 32
+    for name, case in cases.items():
+        torch.manual_seed(0)
+        cfg = SparseCoderConfig(num_latents=M, **case["cfg"])
+        sae = SparseCoder(D, cfg, dtype=torch.float32)
+        g = torch.Generator().manual_seed(11)
+        with torch.no_grad():
+            sae.encoder.bias.copy_(0.1 * torch.randn(M, generator=g))
+            sae.b_dec.copy_(0.1 * torch.randn(D, generator=g))
+            if cfg.transcode:
+                sae.W_dec.copy_(0.2 * torch.randn(M, D, generator=g))
+                sae.W_skip.copy_(0.1 * torch.randn(D, D, generator=g))
+        x = torch.randn(N, D, generator=g)
+        y = torch.randn(N, D, generator=g) if cfg.transcode else None
+        dead_mask = None
+        if case["dead"]:
+            dead_mask = torch.zeros(M, dtype=torch.bool)
+            dead_mask[torch.randperm(M, generator=g)[:40]] = True
+        params = dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec)
+        if sae.W_skip is not None:
+            params["W_skip"] = sae.W_skip
+        init = {k: v.detach().clone() for k, v in params.items()}
+        out = sae(x, y, dead_mask=dead_mask)
+        loss = out.fvu + alpha * out.auxk_loss + out.multi_topk_fvu / 8
+        loss.backward()
+        acts, idx = sorted_topk(out.latent_acts, out.latent_indices)
+        t = dict(x=x, sae_out=out.sae_out, latent_acts=acts, latent_indices=idx, fvu=out.fvu,
+                 auxk_loss=out.auxk_loss, multi_topk_fvu=out.multi_topk_fvu)
+        if y is not None:
+            t["y"] = y
+        if dead_mask is not None:
+            t["dead_mask"] = dead_mask
+        for k_, v in init.items():
+            t[f"param.{k_}"] = v
+        for k_, v in params.items():
+            t[f"grad.{k_}"] = v.grad if v.grad is not None else torch.zeros_like(v)
+        save(f"forward_{name}", t, dict(cfg=dataclasses.asdict(cfg), auxk_alpha=alpha))
+
+
+class FakeLayer(torch.nn.Module):
+    def __init__(self, owner):
+        super().__init__()
+        object.__setattr__(self, "_owner", owner)
+
+    def forward(self, h):
+        return self._owner.next_activation()
+
+
+class FakeModel(torch.nn.Module):
+    """Stands in for the language model: one hooked layer whose output is the
+    next batch of stored activations."""
+
+    def __init__(self, acts):
+        super().__init__()
+        self.config = types.SimpleNamespace(num_hidden_layers=1)
+        self.layers = torch.nn.ModuleList([FakeLayer(self)])
+        self.acts = acts  # [steps, B, T, D]
+        self.cursor = -1  # the width probe consumes one call
+        self.dummy_inputs = {"input_ids": torch.zeros(1, acts.shape[2], dtype=torch.long)}
+
+    @property
+    def base_model(self):
+        return self
+
+    @property
+    def device(self):
+        return torch.device("cpu")
+
+    def next_activation(self):
+        i = max(self.cursor, 0)
+        self.cursor += 1
+        return self.acts[min(i, self.acts.shape[0] - 1)]
+
+    def forward(self, input_ids=None, **kw):
+        return self.layers[0](input_ids)
+
+
+def gen_trainer(sparsify):
+    """A few optimiser steps of the reference Trainer (Adam, FVU + AuxK, decoder
+    normalisation) on stored activations; freezes the per-step FVU and the final
+    parameters."""
+    from sparsify import SparseCoderConfig, TrainConfig, Trainer
+    steps, B, T, D, M, k = 6, 4, 16, 32, 256, 4
+    g = torch.Generator().manual_seed(5)
+    atoms = torch.nn.functional.normalize(torch.randn(512, D, generator=g), dim=1)
+    ids = torch.randint(0, 512, (steps, B, T, 6), generator=g)
+    coef = -torch.log1p(-torch.rand(steps, B, T, 6, generator=g))
+    acts = (atoms[ids] * coef.unsqueeze(-1)).sum(-2) + 0.05 * torch.randn(steps, B, T, D, generator=g)
+    model = FakeModel(acts)
+    dataset = [{"input_ids": torch.zeros(T, dtype=torch.long)} for _ in range(steps * B)]
+    fvus = []
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg = TrainConfig(
+            SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="adam", lr=1e-2,
+            lr_warmup_steps=2, auxk_alpha=1 / 32, dead_feature_threshold=100, hookpoints=["layers.0"],
+            log_to_wandb=False, save_dir=tmp, run_name="golden", save_every=10**9,
+        )
+        trainer = Trainer(cfg, dataset, model)
+        sae = trainer.saes["layers.0"]
+        init = dict(W_enc=sae.encoder.weight.detach().clone(), b_enc=sae.encoder.bias.detach().clone(),
+                    W_dec=sae.W_dec.detach().clone(), b_dec=sae.b_dec.detach().clone())
+        orig_forward = sae.forward
+
+        def recording_forward(*a, **kw):
+            out = orig_forward(*a, **kw)
+            fvus.append(out.fvu.detach().clone())
+            return out
+
+        sae.forward = recording_forward
+        trainer.fit()
+        final = dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec)
+        t = dict(acts=acts, fvu=torch.stack(fvus),
+                 num_tokens_since_fired=trainer.num_tokens_since_fired["layers.0"])
+        for k_, v in init.items():
+            t[f"init.{k_}"] = v
+        for k_, v in final.items():
+            t[f"final.{k_}"] = v
+        save("trainer_adam", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=1e-2, warmup=2,
+                                     auxk_alpha=1 / 32, dead_feature_threshold=100))
+
+
+def gen_muon(sparsify):
+    from sparsify.muon import quintic_newtonschulz
+    g = torch.Generator().manual_seed(3)
+    for name, shape in [("wide", (32, 96)), ("tall", (96, 32))]:
+        G = torch.randn(*shape, generator=g)
+        X = quintic_newtonschulz(G, 5)
+        save(f"newtonschulz_{name}", dict(G=G, X=X.float()))
+
+
+if __name__ == "__main__":
+    ref = import_reference()
+    torch.set_num_threads(1)  # one summation order
+    gen_encoder(ref)
+    gen_decoder(ref)
+    gen_forward(ref)
+    gen_trainer(ref)
+    gen_muon(ref)
