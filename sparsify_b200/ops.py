@@ -11,6 +11,22 @@ from . import _lib
 from ._lib import call, dtype_code, ptr
 
 
+# When set to a dict, selected ops append (start, end) CUDA-event pairs under
+# their name, recorded on the launching stream (used by the benchmark to time
+# the dominant kernel inside the step).
+timers: dict | None = None
+
+
+def _timed(name: str, device):
+    if timers is None:
+        return None
+    s = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    timers.setdefault(name, []).append((s, e))
+    s.record(torch.cuda.current_stream(device))
+    return e
+
+
 def _stream(t: Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -102,9 +118,13 @@ def encode_topk_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tupl
     nbytes = _lib.lib().sc_encode_topk_workspace_bytes(N, D, M, int(k))
     ws = _ws(nbytes, dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
+    bias32 = _f32(bias)
     with torch.cuda.device(dev):
-        call("sc_encode_topk", ptr(x_bf16), ptr(W_bf16), ptr(_f32(bias)), N, D, M, int(k),
+        end = _timed("encode_topk", dev)
+        call("sc_encode_topk", ptr(x_bf16), ptr(W_bf16), ptr(bias32), N, D, M, int(k),
              ptr(vals), ptr(idx), ptr(ws), ws.numel(), ptr(status), _stream(x_bf16))
+        if end is not None:
+            end.record(torch.cuda.current_stream(dev))
     encode_topk_tc.last_status = status
     return vals, idx
 

@@ -273,12 +273,30 @@ class SparseCoder(nn.Module):
         eps = torch.finfo(self.W_dec.dtype).eps
         W = self.W_dec.data
         if W.is_cuda and W.dtype == torch.float32 and W.is_contiguous():
-            ops.normalize_rows_(W, eps)
-            self.W_dec.add_(0)  # bump the version counter: the kernel wrote through a raw pointer
+            # the kernel writes through raw pointers (no version bump): refresh the
+            # cached bf16 copy in the same pass, or drop it
+            hit = self._shadows.pop("W_dec", None)
+            buf = hit[2] if hit is not None and hit[2].shape == W.shape and hit[2].device == W.device else None
+            ops.normalize_rows_(W, eps, buf)
+            if buf is not None:
+                self.mark_shadow_fresh("W_dec", buf)
         else:
             # construction / checkpoint handling on the host before .to("cuda")
             norm = torch.norm(W, dim=1, keepdim=True)
             self.W_dec.data /= norm + eps
+
+    def attach_optimizer(self, opt) -> None:
+        """Lets a FusedAdam keep the bf16 copies current inside its update kernel
+        and fold the decoder-gradient projection into the same pass."""
+        lowp = self._lowp() and self.dtype == torch.float32
+        names = ["encoder.weight"] + (["W_dec"] if self.precision == "bf16" and self.W_dec is not None else [])
+        if lowp and self.device.type == "cuda":
+            for name in names:
+                p = self.encoder.weight if name == "encoder.weight" else self.W_dec
+                buf = self.shadow(name)
+                opt.register_shadow(p, buf, lambda name=name, buf=buf: self.mark_shadow_fresh(name, buf))
+        if self.W_dec is not None and self.cfg.normalize_decoder and not self.cfg.transcode:
+            opt.project_rows(self.W_dec)
 
     @torch.no_grad()
     def remove_gradient_parallel_to_decoder_directions(self):

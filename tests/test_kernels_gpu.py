@@ -1,0 +1,229 @@
+"""Parity of each CUDA entry point with the CPU oracle on the same seeded
+inputs, and with the reference-generated golden fixtures. Integer results
+(indices, CSR) must match exactly; floating point within the stated tolerance.
+"""
+
+import pytest
+import torch
+
+from oracle import sae_oracle as O
+from tests.conftest import load_golden, rel_l2, sort_topk
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 2e-5     # fp32 kernels vs fp32 oracle (summation order differs)
+ACT_TOL = 1e-3     # selected activations / decode output (north-star tolerance)
+GRAD_TOL = 1e-2    # gradients in the bf16 configuration (north-star tolerance)
+
+
+def dev(t):
+    return t.cuda() if t is not None else None
+
+
+def bf16_round(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def check_topk_sets(vals_gpu, idx_gpu, pre_ref, k, rel_gap=1e-3):
+    """Index sets must agree row by row except where the k-th and (k+1)-th
+    reference pre-activations are closer than rel_gap (relative)."""
+    vals_gpu, idx_gpu = vals_gpu.cpu(), idx_gpu.cpu()
+    top = torch.topk(pre_ref, min(k + 1, pre_ref.shape[1]), dim=-1).values
+    bad = 0
+    for n in range(pre_ref.shape[0]):
+        got = set(idx_gpu[n].tolist())
+        assert len(got) == k, f"row {n}: duplicate indices"
+        want = set(torch.topk(pre_ref[n], k).indices.tolist())
+        if got != want:
+            kth = float(top[n, k - 1])
+            nxt = float(top[n, k]) if top.shape[1] > k else kth
+            if abs(kth - nxt) > rel_gap * max(abs(kth), 1e-12):
+                bad += 1
+    assert bad == 0, f"{bad} rows differ beyond the tie rule"
+    # the reported values are the pre-activations at the reported indices
+    picked = pre_ref.gather(1, idx_gpu)
+    assert rel_l2(vals_gpu, picked) < ACT_TOL
+
+
+# ----------------------------------------------------------------------------- decode
+@pytest.mark.parametrize("d_in", [48, 64])
+def test_decode_golden(cuda_lib, d_in):
+    from sparsify_b200 import ops
+    t, _ = load_golden(f"decoder_d{d_in}")
+    out = ops.embedding_bag_fwd(dev(t["idx"]), dev(t["acts"]), dev(t["W_dec"]))
+    assert rel_l2(out, t["out"]) < F32_TOL
+    gacts = ops.embedding_bag_bwd_acts(dev(t["idx"]), dev(t["gout"]), dev(t["W_dec"]))
+    assert rel_l2(gacts, t["gacts"]) < F32_TOL
+    M, D = t["W_dec"].shape
+    row_ptr, entries = ops.csr_build(dev(t["idx"]), M)
+    res = ops.rows_accumulate(row_ptr, entries, t["idx"].shape[1], M, D, dev(t["acts"]), dev(t["gout"]))
+    assert rel_l2(res["gradA"], t["gW"]) < F32_TOL
+
+
+@pytest.mark.parametrize("N,D,M,k,wdtype", [
+    (257, 768, 4096, 32, torch.float32),
+    (300, 4096, 8192, 32, torch.bfloat16),
+    (64, 1024, 2048, 64, torch.bfloat16),
+    (5, 52, 96, 3, torch.float32),
+])
+def test_decode_oracle(cuda_lib, N, D, M, k, wdtype):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    W = torch.randn(M, D, generator=g)
+    if wdtype == torch.bfloat16:
+        W = bf16_round(W)
+    b = torch.randn(D, generator=g)
+    acts = torch.rand(N, k, generator=g)
+    idx = torch.stack([torch.randperm(M, generator=g)[:k] for _ in range(N)])
+    gout = torch.randn(N, D, generator=g)
+    Wd = W.cuda().to(wdtype)
+    out = ops.embedding_bag_fwd(idx.cuda(), acts.cuda(), Wd, b.cuda())
+    assert rel_l2(out, O.decode(idx, acts, W, b)) < F32_TOL
+    gW_ref, gacts_ref = O.decode_backward(idx, acts, W, gout)
+    gacts = ops.embedding_bag_bwd_acts(idx.cuda(), gout.cuda(), Wd)
+    assert rel_l2(gacts, gacts_ref) < F32_TOL
+    row_ptr, entries = ops.csr_build(idx.cuda(), M)
+    res = ops.rows_accumulate(row_ptr, entries, k, M, D, acts.cuda(), gout.cuda(), biasA=True)
+    assert rel_l2(res["gradA"], gW_ref) < F32_TOL
+    gb_ref = torch.zeros(M).index_add_(0, idx.reshape(-1), acts.reshape(-1))
+    assert rel_l2(res["gbiasA"], gb_ref) < F32_TOL
+
+
+def test_csr_exact(cuda_lib):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    N, k, M = 3000, 16, 512
+    idx = torch.stack([torch.randperm(M, generator=g)[:k] for _ in range(N)])
+    idx[:, 0] = 7  # one very hot latent (N entries > the in-kernel sort limit)
+    rest = idx[:, 1:]
+    rest[rest == 7] = 8  # (duplicates inside a row are harmless for the CSR)
+    row_ptr, entries = ops.csr_build(idx.cuda(), M)
+    ref_ptr, ref_order = O.csr_by_latent(idx, M)
+    assert torch.equal(row_ptr.cpu().long(), ref_ptr)
+    entries = entries.cpu().long()
+    for m in range(M):
+        lo, hi = int(ref_ptr[m]), int(ref_ptr[m + 1])
+        seg = entries[lo:hi]
+        if hi - lo <= 2048:
+            assert torch.equal(seg, ref_order[lo:hi]), m  # ascending flat positions
+        else:
+            assert torch.equal(seg.sort().values, ref_order[lo:hi]), m
+
+
+def test_csr_empty_and_ragged(cuda_lib):
+    from sparsify_b200 import ops
+    idx = torch.zeros(0, 4, dtype=torch.int64, device="cuda")
+    row_ptr, _ = ops.csr_build(idx, 16)
+    assert int(row_ptr.abs().sum()) == 0
+    out = ops.embedding_bag_fwd(idx, torch.zeros(0, 4, device="cuda"), torch.randn(16, 8, device="cuda"))
+    assert out.shape == (0, 8)
+
+
+# ----------------------------------------------------------------------------- encoder
+def test_encoder_dense_golden(cuda_lib):
+    from sparsify_b200 import ops
+    t, meta = load_golden("encoder_topk")
+    pre = ops.preacts_dense(dev(t["x"]), dev(t["W"]), dev(t["b"]))
+    assert rel_l2(pre, t["pre"]) < F32_TOL
+    vals, idx = ops.topk_rows(pre, meta["k"])
+    vals, idx = sort_topk(vals.cpu(), idx.cpu())
+    assert torch.equal(idx, t["idx"])
+    assert rel_l2(vals, t["vals"]) < F32_TOL
+    t, meta = load_golden("encoder_groupmax")
+    pre = ops.preacts_dense(dev(t["x"]), dev(t["W"]), dev(t["b"]))
+    vals, idx = ops.groupmax_rows(pre, meta["k"])
+    vals, idx = sort_topk(vals.cpu(), idx.cpu())
+    assert torch.equal(idx, t["idx"])
+
+
+def test_topk_rows_masked(cuda_lib):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    N, M, k = 37, 5000, 200
+    pre = torch.randn(N, M, generator=g).clamp_min(0)  # many exact zeros (ties)
+    mask = torch.rand(M, generator=g) < 0.3
+    vals, idx = ops.topk_rows(pre.cuda(), k, col_mask=mask.cuda())
+    vals, idx = vals.cpu(), idx.cpu()
+    masked = torch.where(mask[None], pre, torch.full_like(pre, -float("inf")))
+    ref_vals = torch.topk(masked, k).values
+    assert torch.equal(vals.sort(-1, descending=True).values, ref_vals)
+    assert bool(mask[idx].all())
+    assert torch.equal(pre.gather(1, idx), vals)
+    for n in range(N):
+        assert len(set(idx[n].tolist())) == k
+
+
+@pytest.mark.parametrize("N,D,M,k", [
+    (128, 64, 256, 8),       # one tile, one k-chunk
+    (200, 256, 1024, 32),    # ragged rows, several tiles
+    (384, 1024, 4352, 32),   # ragged last column tile (4352 = 17 * 256)
+    (130, 72, 520, 64),      # D not a multiple of 64, M not a multiple of 256
+    (1024, 4096, 16384, 32), # config-1 width, reduced N and M
+])
+def test_encoder_tc_vs_oracle(cuda_lib, N, D, M, k):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    x = bf16_round(torch.randn(N, D, generator=g))
+    W = bf16_round(torch.randn(M, D, generator=g) / D ** 0.5)
+    b = 0.1 * torch.randn(M, generator=g)
+    vals, idx = ops.encode_topk_tc(x.cuda().bfloat16(), W.cuda().bfloat16(), b.cuda(), k)
+    torch.cuda.synchronize()
+    assert int(ops.encode_topk_tc.last_status.item()) == 0
+    pre = O.preacts(x.double(), W.double(), b.double()).float()
+    check_topk_sets(vals, idx, pre, k)
+
+
+def test_encoder_tc_few_positive(cuda_lib):
+    """Rows with fewer than k positive pre-activations still return k distinct
+    valid indices (zeros fill the tail), as torch.topk over post-ReLU values does."""
+    from sparsify_b200 import ops
+    N, D, M, k = 128, 64, 512, 16
+    x = torch.ones(N, D)
+    W = -torch.ones(M, D) / D
+    W[:5] = 1.0 / D
+    b = torch.zeros(M)
+    vals, idx = ops.encode_topk_tc(x.cuda().bfloat16(), W.cuda().bfloat16(), b.cuda(), k)
+    vals, idx = vals.cpu(), idx.cpu()
+    for n in range(N):
+        assert len(set(idx[n].tolist())) == k
+        assert set(idx[n, vals[n] > 0].tolist()) == {0, 1, 2, 3, 4}
+    assert bool(((idx >= 0) & (idx < M)).all())
+
+
+# ----------------------------------------------------------------------------- losses / optimiser
+def test_losses(cuda_lib):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    y = torch.randn(1000, 96, generator=g) * torch.rand(96, generator=g) * 5 + 3
+    out = torch.randn(1000, 96, generator=g)
+    tv = ops.total_variance(y.cuda())
+    ref = (y.double() - y.double().mean(0)).pow(2).sum()
+    assert abs(float(tv) - float(ref)) < 1e-5 * float(ref)
+    sse, diff = ops.sq_err(y.cuda(), out.cuda(), want_diff=True)
+    assert abs(float(sse) - float((y.double() - out.double()).pow(2).sum())) < 1e-5 * float(sse)
+    assert torch.equal(diff.cpu(), y - out)
+
+
+def test_normalize_and_adam(cuda_lib):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    M, D = 300, 200
+    W = torch.randn(M, D, generator=g)
+    Wg = W.clone().cuda()
+    shadow = torch.empty(M, D, dtype=torch.bfloat16, device="cuda")
+    ops.normalize_rows_(Wg, torch.finfo(torch.float32).eps, shadow)
+    ref = W.clone()
+    O.normalize_decoder_(ref)
+    assert rel_l2(Wg, ref) < 1e-6
+    assert torch.equal(shadow.cpu(), Wg.cpu().bfloat16())
+    for project in (False, True):
+        p, gr = ref.clone(), torch.randn(M, D, generator=g)
+        m, v = torch.zeros(M, D), torch.zeros(M, D)
+        pg, gg, mg, vg = p.clone().cuda(), gr.clone().cuda(), m.clone().cuda(), v.clone().cuda()
+        for step in (1, 2, 3):
+            if project:
+                O.project_out_parallel_(gr, p)
+            O.adam_step_(p, gr, m, v, step, 1e-3)
+            ops.adam_rows_(pg, gg, mg, vg, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=step,
+                           project=project)
+        assert rel_l2(pg, p) < 1e-6 and rel_l2(mg, m) < 1e-5 and rel_l2(vg, v) < 1e-5

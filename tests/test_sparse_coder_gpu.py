@@ -1,0 +1,138 @@
+"""SparseCoder / fused_encoder / decoder_impl on the GPU against the
+reference-generated fixtures (fp32 mode) and against the oracle evaluated on
+the same bf16-rounded operands (bf16 mode)."""
+
+import pytest
+import torch
+
+from oracle import sae_oracle as O
+from tests.conftest import load_golden, rel_l2, sort_topk
+
+pytestmark = pytest.mark.gpu
+
+
+def build_sae(t, cfg_dict, precision):
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    cfg = SparseCoderConfig(**cfg_dict)
+    D = t["param.b_dec"].numel()
+    sae = SparseCoder(D, cfg, device="cuda", dtype=torch.float32)
+    sae.precision = precision
+    with torch.no_grad():
+        sae.encoder.weight.copy_(t["param.W_enc"])
+        sae.encoder.bias.copy_(t["param.b_enc"])
+        sae.W_dec.copy_(t["param.W_dec"])
+        sae.b_dec.copy_(t["param.b_dec"])
+        if "param.W_skip" in t:
+            sae.W_skip.copy_(t["param.W_skip"])
+    return sae
+
+
+@pytest.mark.parametrize("name", ["sae_plain", "sae_auxk", "sae_multitopk", "transcoder_skip"])
+def test_forward_backward_fp32_golden(cuda_lib, name):
+    t, meta = load_golden(f"forward_{name}")
+    sae = build_sae(t, meta["cfg"], "fp32")
+    x = t["x"].cuda()
+    y = t["y"].cuda() if "y" in t else None
+    dead = t["dead_mask"].cuda() if "dead_mask" in t else None
+    out = sae(x, y, dead_mask=dead)
+    loss = out.fvu + meta["auxk_alpha"] * out.auxk_loss + out.multi_topk_fvu / 8
+    loss.backward()
+    acts, idx = sort_topk(out.latent_acts.detach().cpu(), out.latent_indices.cpu())
+    assert torch.equal(idx, t["latent_indices"])
+    assert rel_l2(acts, t["latent_acts"]) < 2e-5
+    assert rel_l2(out.sae_out.detach(), t["sae_out"]) < 2e-5
+    for key in ("fvu", "auxk_loss", "multi_topk_fvu"):
+        assert abs(float(getattr(out, key)) - float(t[key])) <= 2e-5 * max(1.0, abs(float(t[key]))), key
+    grads = {"W_enc": sae.encoder.weight.grad, "b_enc": sae.encoder.bias.grad,
+             "W_dec": sae.W_dec.grad, "b_dec": sae.b_dec.grad}
+    if sae.W_skip is not None:
+        grads["W_skip"] = sae.W_skip.grad
+    for pname, g in grads.items():
+        ref = t[f"grad.{pname}"]
+        if float(ref.norm()) == 0:
+            assert g is None or float(g.norm()) < 1e-7, pname
+        else:
+            assert rel_l2(g, ref) < 1e-4, (pname, rel_l2(g, ref))
+
+
+def test_fused_encoder_golden(cuda_lib):
+    from sparsify_b200 import fused_encoder
+    for tag in ("topk", "groupmax"):
+        t, meta = load_golden(f"encoder_{tag}")
+        x = t["x"].cuda().requires_grad_(True)
+        W = t["W"].cuda().requires_grad_(True)
+        b = t["b"].cuda().requires_grad_(True)
+        vals, idx, pre = fused_encoder(x, W, b, meta["k"], meta["activation"])
+        assert rel_l2(pre, t["pre"]) < 2e-5
+        order = torch.argsort(vals, dim=-1, descending=True, stable=True)
+        assert torch.equal(idx.gather(-1, order).cpu(), t["idx"])
+        (vals.gather(-1, order) * t["coef"].cuda()).sum().backward()
+        assert rel_l2(x.grad, t["gx"]) < 2e-5
+        assert rel_l2(W.grad, t["gW"]) < 2e-5
+        assert rel_l2(b.grad, t["gb"]) < 2e-5
+    with pytest.raises(ValueError):
+        fused_encoder(x, W, b, 4, "softmax")
+
+
+@pytest.mark.parametrize("d_in", [48, 64])
+def test_decoder_impl_like_reference_test(cuda_lib, d_in):
+    """Shapes of the reference's tests/test_decode.py."""
+    from sparsify_b200.utils import decoder_impl
+    t, _ = load_golden(f"decoder_d{d_in}")
+    W = t["W_dec"].cuda().requires_grad_(True)
+    acts = t["acts"].cuda().requires_grad_(True)
+    out = decoder_impl(t["idx"].cuda(), acts, W.mT)
+    torch.testing.assert_close(out.cpu(), t["out"])
+    (out * t["gout"].cuda()).sum().backward()
+    torch.testing.assert_close(W.grad.cpu(), t["gW"])
+    torch.testing.assert_close(acts.grad.cpu(), t["gacts"])
+
+
+def test_forward_backward_bf16_vs_oracle(cuda_lib):
+    """bf16 configuration: tensor-core encoder and bf16 row gathers, compared
+    with the oracle fed the same bf16-rounded operands."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    torch.manual_seed(0)
+    N, D, M, k = 512, 256, 4096, 32
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+    assert sae.precision == "bf16"
+    g = torch.Generator().manual_seed(9)
+    atoms = torch.nn.functional.normalize(torch.randn(2048, D, generator=g), dim=1)
+    ids = torch.randint(0, 2048, (N, 16), generator=g)
+    x = (atoms[ids] * torch.rand(N, 16, 1, generator=g)).sum(1) + 0.05 * torch.randn(N, D, generator=g)
+    with torch.no_grad():
+        sae.b_dec.copy_(x.mean(0))
+    out = sae(x.cuda())
+    out.fvu.backward()
+    rnd = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    params = dict(W_enc=sae.encoder.weight.detach().cpu(), b_enc=sae.encoder.bias.detach().cpu(),
+                  W_dec=sae.W_dec.detach().cpu(), b_dec=sae.b_dec.detach().cpu())
+    ref = O.sae_forward_backward(params, x, cfg=O.OracleCfg(k=k), round_operands=rnd)
+    acts, idx = sort_topk(out.latent_acts.detach().cpu(), out.latent_indices.cpu())
+    racts, ridx = sort_topk(ref.latent_acts, ref.latent_indices)
+    agree = (idx == ridx).float().mean()
+    assert agree > 0.999, float(agree)
+    assert rel_l2(acts, racts) < 1e-3
+    assert rel_l2(out.sae_out.detach(), ref.sae_out) < 1e-3
+    assert abs(float(out.fvu) - float(ref.fvu)) < 1e-3 * float(ref.fvu)
+    for pname, gt in (("W_enc", sae.encoder.weight.grad), ("b_enc", sae.encoder.bias.grad),
+                      ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad)):
+        assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
+
+
+def test_checkpoint_roundtrip(cuda_lib, tmp_path):
+    from safetensors import safe_open
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    sae = SparseCoder(32, SparseCoderConfig(num_latents=128, k=4, skip_connection=True), device="cuda")
+    sae.save_to_disk(tmp_path / "ckpt")
+    with safe_open(str(tmp_path / "ckpt" / "sae.safetensors"), framework="pt") as f:
+        assert sorted(f.keys()) == ["W_dec", "W_skip", "b_dec", "encoder.bias", "encoder.weight"]
+    back = SparseCoder.load_from_disk(tmp_path / "ckpt", device="cuda")
+    for (n1, p1), (n2, p2) in zip(sae.named_parameters(), back.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2)
+
+
+def test_cpu_tensors_are_rejected():
+    from sparsify_b200 import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.embedding_bag_fwd(torch.zeros(2, 2, dtype=torch.long), torch.zeros(2, 2), torch.zeros(4, 4))
