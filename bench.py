@@ -1,0 +1,338 @@
+"""Benchmark of the TopK sparse-coder training step (SAE train tokens/s).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU arm (oracle port)
+
+Workload (default): d_in=4096, 131072 latents, k=32, 16384 tokens per rank per
+step, bf16 operands with fp32 accumulation, forward + backward + Adam with the
+AuxK branch enabled (inert while no latent is dead), synthetic activations.
+One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "sae_train_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=16384, help="tokens per rank per step")
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--latents", type=int, default=131072)
+    ap.add_argument("--k", type=int, default=32)
+    ap.add_argument("--atoms", type=int, default=262144)
+    ap.add_argument("--active", type=int, default=64)
+    ap.add_argument("--cpu-tokens", type=int, default=1024,
+                    help="tokens per step of the bounded CPU sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a) -> str:
+    return (f"SAE train step d_in={a.d} latents={a.latents} k={a.k} tokens/rank/step={a.tokens} "
+            f"bf16 operands fp32 accumulate, fwd+bwd+Adam, AuxK enabled")
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"tflops": d.get("bf16_tflops_sustained", d.get("bf16_tflops")), "hbm": d.get("hbm_gbs"),
+                "source": "measured"}
+    return {"tflops": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample(a, steps: int, warmup: int) -> dict:
+    """Times the oracle port of the reference's step (CPU, fp32, all host
+    threads) on a bounded sample: the full-width model (d_in x latents of the
+    workload) with `--cpu-tokens` tokens per step."""
+    from oracle import sae_oracle as O
+    from sparsify_b200.synthetic import SyntheticActivations
+
+    D, M, k, n = a.d, a.latents, a.k, a.cpu_tokens
+    cores = torch.get_num_threads()
+    g = torch.Generator().manual_seed(0)
+    bound = 1.0 / D ** 0.5
+    W_enc = (torch.rand(M, D, generator=g) * 2 - 1) * bound
+    params = dict(W_enc=W_enc, b_enc=torch.zeros(M), W_dec=W_enc.clone(), b_dec=torch.zeros(D))
+    O.normalize_decoder_(params["W_dec"])
+    gen = SyntheticActivations(D, min(a.atoms, 65536), a.active, device="cpu")
+    tr = O.OracleTrainer(params, O.OracleCfg(k=k), warmup=1000, total_steps=10**6, auxk_alpha=1 / 32)
+    times = []
+    for s in range(warmup + steps):
+        x = gen.batch(n, seed=s)
+        t0 = time.perf_counter()
+        tr.step(x)
+        dt = time.perf_counter() - t0
+        if s >= warmup:
+            times.append(dt)
+    sec = statistics.median(times)
+    return {"value": n / sec, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} tokens/step at d_in={D}, latents={M}, k={k}, fp32, {steps} timed steps "
+                      f"(median {sec:.2f} s/step)",
+            "ms_per_step": sec * 1e3}
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(a.steps, 3)), max(1, min(a.warmup, 1))
+    base = cpu_sample(a, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "note": "CPU oracle port of the reference step; bounded sample"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+LAUNCHES_PER_CALL = {  # kernels each C-ABI entry point enqueues
+    "sc_encode_topk": 3, "sc_csr_build": 4, "sc_total_variance": 4, "sc_sq_err": 2,
+}
+
+
+class LaunchCounter:
+    """Counts kernel launches of libsparsecoder by wrapping the ABI call helper."""
+
+    def __init__(self):
+        from sparsify_b200 import _lib, ops
+        self.n = 0
+        self._lib, self._ops = _lib, ops
+        self._orig = _lib.call
+
+        def counted(name, *args):
+            self.n += LAUNCHES_PER_CALL.get(name, 1)
+            return self._orig(name, *args)
+
+        _lib.call = counted
+        ops.call = counted
+
+
+def run_ours(a):
+    import torch.distributed as dist
+
+    from sparsify_b200 import SparseCoder, SparseCoderConfig, ops
+    from sparsify_b200.optim import FusedAdam
+    from sparsify_b200.synthetic import SyntheticActivations, batch_seed
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    N, D, M, k = a.tokens, a.d, a.latents, a.k
+    torch.manual_seed(0)  # identical replicas on every rank (sparsify/trainer.py:80-87)
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device=dev, dtype=torch.float32)
+    lr = 2e-4 / (M / 2 ** 14) ** 0.5
+    opt = FusedAdam(sae.parameters(), lr=lr)
+    sae.attach_optimizer(opt)
+    alpha = 1 / 32
+    since_fired = torch.zeros(M, dtype=torch.long, device=dev)
+    dead_threshold = 10_000_000
+
+    gen = SyntheticActivations(D, a.atoms, a.active, device=dev)
+    pool = [gen.batch(N, batch_seed(t, rank, world), torch.bfloat16) for t in range(4)]
+    del gen
+    torch.cuda.empty_cache()
+    host_pool = [b.cpu().pin_memory() for b in pool]
+    with torch.no_grad():
+        mean = pool[0].float().mean(0)
+        if world > 1:
+            dist.all_reduce(mean)
+            mean /= world
+        sae.b_dec.copy_(mean)
+    grads = [p for p in sae.parameters()]
+
+    def step(x):
+        sae.set_decoder_norm_to_unit_norm()
+        out = sae(x, dead_mask=since_fired > dead_threshold)
+        loss = out.fvu + alpha * out.auxk_loss
+        loss.backward()
+        if world > 1:
+            for p in grads:
+                dist.all_reduce(p.grad)
+                p.grad /= world
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        with torch.no_grad():
+            fired = torch.zeros(M, dtype=torch.bool, device=dev)
+            fired[out.latent_indices.flatten()] = True
+            if world > 1:
+                f8 = fired.to(torch.uint8)
+                dist.all_reduce(f8, op=dist.ReduceOp.MAX)
+                fired = f8.bool()
+            since_fired.add_(N)
+            since_fired[fired] = 0
+        return out.fvu.detach()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for t in range(max(a.warmup, 3)):
+        step(pool[t % len(pool)])
+    sync()
+
+    # ---- device-resident timing -------------------------------------------
+    counter = LaunchCounter()
+    ops.timers = {}
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for t in range(a.steps):
+        step(pool[t % len(pool)])
+    e1.record()
+    sync()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    enc_ms = statistics.mean(s.elapsed_time(e) for s, e in ops.timers.get("encode_topk", [])) \
+        if ops.timers.get("encode_topk") else None
+    ops.timers = None
+    launches = counter.n
+
+    # ---- end to end: pinned host input -> device, step, loss back to host ----
+    xbuf = torch.empty_like(pool[0])
+    sync()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for t in range(a.steps):
+        xbuf.copy_(host_pool[t % len(host_pool)], non_blocking=True)
+        fvu = step(xbuf)
+        float(fvu.cpu())
+    f1.record()
+    sync()
+    ms_e2e = torch.tensor([f0.elapsed_time(f1) / a.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(ms), float(ms_e2e)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        flops = 2.0 * N * D * M
+        roof = None
+        if enc_ms:
+            achieved = flops / (enc_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "encode_topk_tc_kernel (+ tau init, merge)",
+                    "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops"], "peak_source": peaks["source"],
+                    "ms_per_launch": enc_ms, "traffic": None}
+        gs_bytes = 3 * (N * k * D * 2) + 3 * N * D * 4 + N * k * 12 + 2 * M * D * 4 + 2 * N * D * 4 + N * k * 12
+        step_roof_ms = max(flops / (peaks["tflops"] * 1e12), gs_bytes / (peaks["hbm"] * 1e9)) * 1e3
+        line = {
+            "metric": METRIC, "value": world * N / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(a), "l2": "inputs and weights per step exceed L2 (x 134 MB, weights > 2 GB)",
+                       "parallelism": f"dp{world}"},
+            "e2e": {"value": world * N / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": N * D * 2,
+                    "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": roof,
+            "step_roofline": {"ms": step_roof_ms, "frac": step_roof_ms / ms,
+                              "def": "max(encoder FLOPs / tensor peak, gather+scatter bytes / HBM peak)"},
+        }
+        if world == 1 and not a.no_cpu_baseline:
+            base = cpu_sample(a, 2, 1)
+            line["cpu_baseline"] = {k_: base[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)

@@ -226,4 +226,4 @@ def test_normalize_and_adam(cuda_lib):
             O.adam_step_(p, gr, m, v, step, 1e-3)
             ops.adam_rows_(pg, gg, mg, vg, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=step,
                            project=project)
-        assert rel_l2(pg, p) < 1e-6 and rel_l2(mg, m) < 1e-5 and rel_l2(vg, v) < 1e-5
+        assert rel_l2(pg, p) < 1e-6 and rel_l2(mg, m) < 1e-5 and rel_l2(vg, v) < 5e-5
