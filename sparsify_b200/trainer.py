@@ -1,0 +1,435 @@
+"""Trainer with the reference's surface (sparsify/trainer.py:28-728):
+``Trainer(cfg, dataset, model)``, ``fit()``, ``save()``, ``load_state(path)``,
+``saes``, ``module_plan``, ``local_hookpoints()`` and the same checkpoint tree.
+
+The step it drives per hookpoint is the reference's (trainer.py:340-447,
+510-538): mask tokens, step-0 bias initialisation, decoder normalisation,
+forward (FVU + AuxK + Multi-TopK), backward, gradient exchange, projection of
+the decoder gradient, optimiser step, dead-latent bookkeeping - with the
+arithmetic done by the CUDA kernels. Differences, all outside the arithmetic:
+
+* data parallel: gradients are averaged by `parallel.GradReducer`
+  (asynchronous all-reduce per parameter, overlapped with backward) instead of
+  a DistributedDataParallel wrapper;
+* `distribute_modules`: activations go to the owning rank only;
+* `loss_fn` "ce"/"kl" (end-to-end through a live language model), the
+  schedule-free "signum" optimiser and Weights & Biases logging are not part of
+  this package; metrics go to `metrics.jsonl` in the run directory under the
+  names the reference logs.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from collections import defaultdict
+from fnmatch import fnmatchcase
+from glob import glob
+from typing import Sized
+
+import torch
+import torch.distributed as dist
+from safetensors.torch import load_model
+from torch import Tensor, nn
+from torch.utils.data import DataLoader
+
+from . import parallel
+from .config import TrainConfig
+from .muon import Muon
+from .optim import FusedAdam
+from .sparse_coder import SparseCoder, natsorted
+from .utils import get_layer_list, resolve_widths
+
+
+def linear_schedule_with_warmup(optimizer, num_warmup_steps: int, num_training_steps: int):
+    """transformers.get_linear_schedule_with_warmup (used at trainer.py:117-121)."""
+    def lr_lambda(step: int):
+        if step < num_warmup_steps:
+            return float(step) / float(max(1, num_warmup_steps))
+        return max(0.0, float(num_training_steps - step) / float(max(1, num_training_steps - num_warmup_steps)))
+    return torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda)
+
+
+class Trainer:
+    def __init__(self, cfg: TrainConfig, dataset, model: nn.Module):
+        self.model = model
+
+        if cfg.hookpoints:
+            assert not cfg.layers, "Cannot specify both `hookpoints` and `layers`."
+            raw = [name for name, _ in model.base_model.named_modules()
+                   if any(fnmatchcase(name, pat) for pat in cfg.hookpoints)]
+            cfg.hookpoints = natsorted(raw)
+        else:
+            if not cfg.layers:
+                cfg.layers = list(range(0, model.config.num_hidden_layers))
+            layers_name, _ = get_layer_list(model)
+            cfg.hookpoints = [f"{layers_name}.{i}" for i in cfg.layers]
+        cfg.hookpoints = cfg.hookpoints[:: cfg.layer_stride]
+
+        self.cfg = cfg
+        self.dataset = dataset
+        self.distribute_modules()
+
+        device = model.device
+        input_widths = resolve_widths(model, cfg.hookpoints)
+        unique_widths = set(input_widths.values())
+        if cfg.distribute_modules and len(unique_widths) > 1:
+            raise ValueError(
+                f"All modules must output tensors of the same shape when using "
+                f"`distribute_modules=True`, got {unique_widths}"
+            )
+        if cfg.loss_fn != "fvu":
+            raise NotImplementedError(
+                f"loss_fn='{cfg.loss_fn}' trains end-to-end through a live language model; "
+                "this package covers the local 'fvu' objective only"
+            )
+
+        print(f"Initializing SAEs with random seed(s) {cfg.init_seeds}")
+        self.saes: dict[str, SparseCoder] = {}
+        for hook in self.local_hookpoints():
+            for seed in cfg.init_seeds:
+                torch.manual_seed(seed)
+                name = f"{hook}/seed{seed}" if len(cfg.init_seeds) > 1 else hook
+                self.saes[name] = SparseCoder(input_widths[hook], cfg.sae, device, dtype=torch.float32)
+
+        assert isinstance(dataset, Sized)
+        num_batches = len(dataset) // cfg.batch_size
+
+        match cfg.optimizer:
+            case "adam":
+                pgs = [dict(params=list(sae.parameters()),
+                            lr=cfg.lr or 2e-4 / (sae.num_latents / (2 ** 14)) ** 0.5)
+                       for sae in self.saes.values()]
+                lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
+                adam = FusedAdam(pgs)
+                for sae in self.saes.values():
+                    sae.attach_optimizer(adam)
+                self.optimizers = [adam]
+                self.lr_schedulers = [linear_schedule_with_warmup(adam, cfg.lr_warmup_steps, num_batches)]
+            case "muon":
+                # name-sorted so that the matrix -> rank assignment is the same in every process
+                named = [(f"{n}.{pn}", p) for n, sae in self.saes.items() for pn, p in sae.named_parameters()]
+                muon_params = [p for _, p in sorted(named, key=lambda t: t[0]) if p.ndim >= 2]
+                other = [p for _, p in named if p.ndim < 2]
+                lrs = [f"{cfg.lr or 2e-3:.2e}"]
+                self.optimizers = [
+                    Muon(muon_params, lr=cfg.lr or 2e-3, ddp=not cfg.distribute_modules),
+                    FusedAdam(other, lr=cfg.lr or 2e-3),
+                ]
+                self.lr_schedulers = [
+                    linear_schedule_with_warmup(self.optimizers[0], 0, num_batches),
+                    linear_schedule_with_warmup(self.optimizers[1], cfg.lr_warmup_steps, num_batches),
+                ]
+            case "signum":
+                raise NotImplementedError(
+                    "optimizer='signum' wraps SignSGD in the third-party schedulefree package, "
+                    "which this package does not provide; use 'adam' or 'muon'"
+                )
+            case other:
+                raise ValueError(f"Unknown optimizer '{other}'")
+
+        print(f"Learning rates: {lrs}" if len(lrs) > 1 else f"Learning rate: {lrs[0]}")
+        self.global_step = 0
+        self.num_tokens_since_fired = {
+            name: torch.zeros(sae.num_latents, device=device, dtype=torch.long)
+            for name, sae in self.saes.items()
+        }
+        self.exclude_tokens = torch.tensor(self.cfg.exclude_tokens, device=device, dtype=torch.long)
+
+        num_latents = list(self.saes.values())[0].num_latents
+        self.initial_k = min(num_latents, round(list(input_widths.values())[0] * 10))
+        self.final_k = self.cfg.sae.k
+        self.best_loss = {name: float("inf") for name in self.local_hookpoints()}
+        self.metrics: list[dict] = []
+
+    # ------------------------------------------------------------------ state
+    def load_state(self, path: str):
+        """Load the trainer state from disk (layout of trainer.py:186-227)."""
+        device = self.model.device
+        train_state = torch.load(f"{path}/state.pt", map_location=device, weights_only=True)
+        self.global_step = train_state["global_step"]
+
+        for file in glob(f"{path}/rank_*_state.pt"):
+            rank_state = torch.load(file, map_location=device, weights_only=True)
+            for k in self.local_hookpoints():
+                if k in rank_state["num_tokens_since_fired"]:
+                    self.num_tokens_since_fired[k] = rank_state["num_tokens_since_fired"][k]
+                if not isinstance(rank_state["best_loss"], dict):
+                    self.best_loss = rank_state["best_loss"]
+                elif k in rank_state["best_loss"]:
+                    self.best_loss[k] = rank_state["best_loss"][k]
+
+        print(f"\033[92mResuming training at step {self.global_step} from '{path}'\033[0m")
+        for i, scheduler in enumerate(self.lr_schedulers):
+            scheduler.load_state_dict(
+                torch.load(f"{path}/lr_scheduler_{i}.pt", map_location=device, weights_only=True))
+        for i, optimizer in enumerate(self.optimizers):
+            optimizer.load_state_dict(
+                torch.load(f"{path}/optimizer_{i}.pt", map_location=device, weights_only=True))
+        for name, sae in self.saes.items():
+            load_model(sae, f"{path}/{name}/sae.safetensors", device=str(device))
+
+    def get_current_k(self) -> int:
+        """Linear decay of k from initial_k to final_k (trainer.py:229-235)."""
+        if self.global_step >= self.cfg.k_decay_steps:
+            return self.final_k
+        progress = self.global_step / self.cfg.k_decay_steps
+        return round(self.initial_k * (1 - progress) + self.final_k * progress)
+
+    # ------------------------------------------------------------------ training
+    def fit(self):
+        self.model.requires_grad_(False)
+        rank_zero = not dist.is_initialized() or dist.get_rank() == 0
+        ddp = dist.is_initialized() and not self.cfg.distribute_modules
+        world = dist.get_world_size() if dist.is_initialized() else 1
+
+        num_sae_params = sum(p.numel() for s in self.saes.values() for p in s.parameters())
+        print(f"Number of SAE parameters: {num_sae_params:_}")
+
+        if self.global_step > 0:
+            assert hasattr(self.dataset, "select"), "Dataset must implement `select`"
+            n = self.global_step * self.cfg.batch_size
+            ds = self.dataset.select(range(n, len(self.dataset)))
+        else:
+            ds = self.dataset
+
+        device = self.model.device
+        dl = DataLoader(ds, batch_size=self.cfg.batch_size, shuffle=False)
+
+        did_fire = {name: torch.zeros(sae.num_latents, device=device, dtype=torch.bool)
+                    for name, sae in self.saes.items()}
+        tokens_mask: Tensor
+
+        acc_steps = self.cfg.grad_acc_steps * self.cfg.micro_acc_steps
+        denom = acc_steps * self.cfg.wandb_log_frequency
+        num_tokens_in_step = 0
+        avg_auxk_loss = defaultdict(float)
+        avg_fvu = defaultdict(float)
+        avg_multi_topk_fvu = defaultdict(float)
+        avg_losses = {name: float("inf") for name in self.local_hookpoints()}
+
+        name_to_module = {name: self.model.base_model.get_submodule(name) for name in self.cfg.hookpoints}
+        module_to_name = {v: k for k, v in name_to_module.items()}
+        reducer: parallel.GradReducer | None = None
+        # loss scalars stay on the device until the step ends: one host sync per step
+        pending_metrics: list[tuple] = []
+
+        def hook(module: nn.Module, inputs, outputs):
+            if isinstance(inputs, tuple):
+                inputs = inputs[0]
+            if isinstance(outputs, tuple):
+                outputs, *_ = outputs
+            mask = tokens_mask
+            hookpoint = module_to_name[module]
+
+            if self.cfg.distribute_modules:
+                owner = parallel.owner_of(self.module_plan, hookpoint)
+                outputs = parallel.gather_to_owner(outputs, owner)
+                if self.cfg.sae.transcode:
+                    inputs = parallel.gather_to_owner(inputs, owner)
+                mask = parallel.gather_to_owner(mask.to(torch.uint8), owner)
+                if dist.get_rank() != owner:
+                    return
+                mask = mask.bool()
+
+            outputs = outputs.flatten(0, 1)
+            inputs = inputs.flatten(0, 1) if self.cfg.sae.transcode else outputs
+            mask = mask.flatten(0, 1)
+            if not bool(mask.all()):
+                outputs = outputs[mask]
+                inputs = inputs[mask] if self.cfg.sae.transcode else outputs
+
+            seeds = self.cfg.init_seeds
+            names = [f"{hookpoint}/seed{s}" for s in seeds] if len(seeds) > 1 else [hookpoint]
+            for name in names:
+                raw = self.saes[name]
+                if self.global_step == 0 and not self.cfg.finetune:
+                    # centre the pre-activations and the reconstruction (trainer.py:393-404)
+                    with torch.no_grad():
+                        if self.cfg.sae.transcode:
+                            mean = self.maybe_all_reduce(inputs.float().mean(0)).to(raw.dtype)
+                            raw.encoder.bias.data = -mean @ raw.encoder.weight.data.T
+                        mean = self.maybe_all_reduce(outputs.float().mean(0))
+                        raw.b_dec.data = mean.to(raw.dtype)
+
+                if raw.cfg.normalize_decoder and not self.cfg.sae.transcode:
+                    raw.set_decoder_norm_to_unit_norm()
+
+                out = raw(
+                    x=inputs,
+                    y=outputs,
+                    dead_mask=(self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold
+                               if self.cfg.auxk_alpha > 0 else None),
+                )
+                did_fire[name][out.latent_indices.flatten()] = True
+                self.maybe_all_reduce(did_fire[name], "max")
+
+                pending_metrics.append((name, out.fvu.detach(), out.auxk_loss.detach(),
+                                        out.multi_topk_fvu.detach()))
+                loss = out.fvu + self.cfg.auxk_alpha * out.auxk_loss + out.multi_topk_fvu / 8
+                loss.div(acc_steps).backward()
+
+        k = self.get_current_k()
+        for sae in self.saes.values():
+            sae.cfg.k = k
+
+        for batch in dl:
+            x = batch["input_ids"].to(device)
+            tokens_mask = torch.isin(x, self.exclude_tokens, invert=True)
+
+            step, substep = divmod(self.global_step + 1, self.cfg.grad_acc_steps)
+            if ddp and reducer is None:
+                reducer = parallel.GradReducer(
+                    [p for sae in self.saes.values() for p in sae.parameters()]).attach()
+            if reducer is not None:
+                reducer.enabled = substep == 0
+
+            N = int(tokens_mask.sum().item())
+            num_tokens_in_step += N
+
+            handles = [mod.register_forward_hook(hook) for mod in name_to_module.values()]
+            try:
+                self.model(x)
+            finally:
+                for handle in handles:
+                    handle.remove()
+
+            # metric reads (one sync for all hookpoints of this batch)
+            for name, fvu, auxk, multi in pending_metrics:
+                avg_fvu[name] += float(self.maybe_all_reduce(fvu) / denom)
+                if self.cfg.auxk_alpha > 0:
+                    avg_auxk_loss[name] += float(self.maybe_all_reduce(auxk) / denom)
+                if self.cfg.sae.multi_topk:
+                    avg_multi_topk_fvu[name] += float(self.maybe_all_reduce(multi) / denom)
+            pending_metrics.clear()
+            avg_losses = dict(avg_fvu)
+
+            if substep == 0:
+                if reducer is not None:
+                    reducer.finish()
+                # the decoder-gradient projection (trainer.py:513-515) runs inside
+                # FusedAdam's update kernel; Muon needs it applied beforehand
+                if self.cfg.optimizer == "muon" and self.cfg.sae.normalize_decoder and not self.cfg.sae.transcode:
+                    for sae in self.saes.values():
+                        sae.remove_gradient_parallel_to_decoder_directions()
+
+                for optimizer in self.optimizers:
+                    optimizer.step()
+                    optimizer.zero_grad()
+                for scheduler in self.lr_schedulers:
+                    scheduler.step()
+
+                k = self.get_current_k()
+                for sae in self.saes.values():
+                    sae.cfg.k = k
+
+                with torch.no_grad():
+                    for name, counts in self.num_tokens_since_fired.items():
+                        counts += num_tokens_in_step
+                        counts[did_fire[name]] = 0
+                    num_tokens_in_step = 0
+                    for mask in did_fire.values():
+                        mask.zero_()
+
+                if (step + 1) % self.cfg.save_every == 0:
+                    self.save()
+                    if self.cfg.save_best:
+                        self.save_best(avg_losses)
+
+                if (step + 1) % self.cfg.wandb_log_frequency == 0:
+                    info = {"step": step, "k": k}
+                    for name in self.saes:
+                        dead = self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold
+                        info[f"dead_pct/{name}"] = dead.mean(dtype=torch.float32).item()
+                        info[f"fvu/{name}"] = avg_fvu[name]
+                        if self.cfg.auxk_alpha > 0:
+                            info[f"auxk/{name}"] = avg_auxk_loss[name]
+                        if self.cfg.sae.multi_topk:
+                            info[f"multi_topk_fvu/{name}"] = avg_multi_topk_fvu[name]
+                    self.metrics.append(info)
+
+                avg_auxk_loss.clear()
+                avg_fvu.clear()
+                avg_multi_topk_fvu.clear()
+
+            self.global_step += 1
+
+        if reducer is not None:
+            reducer.detach()
+        self.save()
+        if self.cfg.save_best:
+            self.save_best(avg_losses)
+
+    # ------------------------------------------------------------------ distribution
+    def local_hookpoints(self) -> list[str]:
+        return self.module_plan[dist.get_rank()] if self.module_plan else self.cfg.hookpoints
+
+    def maybe_all_reduce(self, x: Tensor, op: str = "mean") -> Tensor:
+        if not dist.is_initialized() or self.cfg.distribute_modules:
+            return x
+        return parallel.all_reduce_(x, op)
+
+    def distribute_modules(self):
+        """Prepare a plan for distributing modules across ranks."""
+        if not self.cfg.distribute_modules:
+            self.module_plan = []
+            print(f"Training on modules: {self.cfg.hookpoints}")
+            return
+        self.module_plan = parallel.module_plan(self.cfg.hookpoints, dist.get_world_size())
+        for rank, modules in enumerate(self.module_plan):
+            print(f"Rank {rank} modules: {modules}")
+
+    # ------------------------------------------------------------------ checkpoints
+    def _checkpoint(self, saes: dict[str, SparseCoder], path: str, rank_zero: bool):
+        """Layout of trainer.py:648-686: {path}/{name}/sae.safetensors + cfg.json,
+        and on rank 0 lr_scheduler_i.pt, optimizer_i.pt, state.pt, config.json; every
+        saving rank writes rank_{r}_state.pt."""
+        print("Saving checkpoint")
+        for name, sae in saes.items():
+            assert isinstance(sae, SparseCoder)
+            sae.save_to_disk(f"{path}/{name}")
+
+        if rank_zero:
+            os.makedirs(path, exist_ok=True)
+            for i, scheduler in enumerate(self.lr_schedulers):
+                torch.save(scheduler.state_dict(), f"{path}/lr_scheduler_{i}.pt")
+            for i, optimizer in enumerate(self.optimizers):
+                torch.save(optimizer.state_dict(), f"{path}/optimizer_{i}.pt")
+            torch.save({"global_step": self.global_step}, f"{path}/state.pt")
+            self.cfg.save_json(f"{path}/config.json")
+            if self.metrics:
+                with open(f"{path}/metrics.jsonl", "w") as f:
+                    for row in self.metrics:
+                        f.write(json.dumps(row) + "\n")
+
+        rank = 0 if rank_zero else dist.get_rank()
+        os.makedirs(path, exist_ok=True)
+        torch.save(
+            {"num_tokens_since_fired": self.num_tokens_since_fired, "best_loss": self.best_loss},
+            f"{path}/rank_{rank}_state.pt",
+        )
+
+    def save(self):
+        """Save the SAEs and training state to disk."""
+        path = f'{self.cfg.save_dir}/{self.cfg.run_name or "unnamed"}'
+        rank_zero = not dist.is_initialized() or dist.get_rank() == 0
+        if rank_zero or self.cfg.distribute_modules:
+            self._checkpoint(self.saes, path, rank_zero)
+        if dist.is_initialized():
+            dist.barrier()
+
+    def save_best(self, avg_loss: dict[str, float]):
+        """Save individual sparse coders to disk if they have the lowest loss."""
+        base_path = f'{self.cfg.save_dir}/{self.cfg.run_name or "unnamed"}/best'
+        rank_zero = not dist.is_initialized() or dist.get_rank() == 0
+        for name in self.saes:
+            if avg_loss.get(name, float("inf")) < self.best_loss.get(name, float("inf")):
+                self.best_loss[name] = avg_loss[name]
+                if rank_zero or self.cfg.distribute_modules:
+                    self._checkpoint({name: self.saes[name]}, f"{base_path}/{name}", rank_zero)
+        if dist.is_initialized():
+            dist.barrier()
+
+
+# Support old name for compatibility
+SaeTrainer = Trainer

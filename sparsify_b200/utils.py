@@ -28,3 +28,39 @@ def assert_type(typ, obj):
     if not isinstance(obj, typ):
         raise TypeError(f"Expected {typ.__name__}, got {type(obj).__name__}")
     return obj
+
+
+def get_layer_list(model):
+    """(name, ModuleList) of the model's layer stack (sparsify/utils.py:20-31)."""
+    from torch import nn
+    N = assert_type(int, model.config.num_hidden_layers)
+    candidates = [
+        (name, mod) for (name, mod) in model.base_model.named_modules()
+        if isinstance(mod, nn.ModuleList) and len(mod) == N
+    ]
+    assert len(candidates) == 1, "Could not find the list of layers."
+    return candidates[0]
+
+
+def resolve_widths(model, module_names: list[str], dim: int = -1) -> dict[str, int]:
+    """Output width of each named module, probed with the model's dummy inputs
+    (sparsify/utils.py:34-61)."""
+    import torch
+
+    module_to_name = {model.base_model.get_submodule(name): name for name in module_names}
+    shapes: dict[str, int] = {}
+
+    def hook(module, _, output):
+        if isinstance(output, tuple):
+            output, *_ = output
+        shapes[module_to_name[module]] = output.shape[dim]
+
+    handles = [mod.register_forward_hook(hook) for mod in module_to_name]
+    dummy = {k: (v.to(model.device) if hasattr(v, "to") else v) for k, v in model.dummy_inputs.items()}
+    try:
+        with torch.inference_mode():
+            model(**dummy)
+    finally:
+        for handle in handles:
+            handle.remove()
+    return shapes

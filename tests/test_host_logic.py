@@ -1,0 +1,75 @@
+"""Host-side logic that needs no GPU: configuration round trips, natural sort,
+module plan, learning-rate schedule, checkpoint layout of a CPU-resident coder."""
+
+import json
+
+import pytest
+import torch
+
+from sparsify_b200 import SparseCoder, SparseCoderConfig, TrainConfig, TranscoderConfig
+from sparsify_b200 import parallel
+from sparsify_b200.sparse_coder import natsorted
+
+
+def test_config_roundtrip_and_validation(tmp_path):
+    cfg = TrainConfig(SparseCoderConfig(k=64, transcode=True), batch_size=8, hookpoints=["layers.3"])
+    d = cfg.to_dict()
+    assert d["sae"]["k"] == 64 and d["init_seeds"] == [0]
+    back = TrainConfig.from_dict(json.loads(json.dumps(d)))
+    assert back == cfg
+    cfg.save_json(tmp_path / "config.json")
+    assert TrainConfig.load_json(tmp_path / "config.json") == cfg
+    assert TranscoderConfig().transcode is True
+    assert SparseCoderConfig.from_dict({"k": 5, "unknown": 1}, drop_extra_fields=True).k == 5
+    with pytest.raises(ValueError):
+        TrainConfig(SparseCoderConfig(), layers=[1], layer_stride=2)
+    with pytest.raises(ValueError):
+        TrainConfig(SparseCoderConfig(), distribute_modules=True, loss_fn="ce")
+    with pytest.raises(ValueError):
+        TrainConfig(SparseCoderConfig(), init_seeds=[])
+
+
+def test_natsorted_and_plan():
+    names = ["layers.10", "layers.2", "layers.1", "layers.21"]
+    assert natsorted(names) == ["layers.1", "layers.2", "layers.10", "layers.21"]
+    plan = parallel.module_plan(natsorted(names), 2)
+    assert plan == [["layers.1", "layers.2"], ["layers.10", "layers.21"]]
+    assert parallel.owner_of(plan, "layers.10") == 1
+    with pytest.raises(AssertionError):
+        parallel.module_plan(names, 3)
+
+
+def test_lr_schedule_matches_transformers():
+    from transformers import get_linear_schedule_with_warmup
+    from sparsify_b200.trainer import linear_schedule_with_warmup
+    p1, p2 = torch.nn.Parameter(torch.zeros(1)), torch.nn.Parameter(torch.zeros(1))
+    o1, o2 = torch.optim.SGD([p1], lr=0.3), torch.optim.SGD([p2], lr=0.3)
+    s1, s2 = get_linear_schedule_with_warmup(o1, 5, 20), linear_schedule_with_warmup(o2, 5, 20)
+    for _ in range(25):
+        assert o1.param_groups[0]["lr"] == pytest.approx(o2.param_groups[0]["lr"])
+        o1.step(); o2.step(); s1.step(); s2.step()
+
+
+def test_checkpoint_layout_cpu(tmp_path):
+    """Construction, save and load work on the host (no kernels involved); the
+    files carry the reference's tensor names and cfg.json fields."""
+    from safetensors import safe_open
+    torch.manual_seed(0)
+    sae = SparseCoder(16, SparseCoderConfig(num_latents=64, k=4), device="cpu")
+    norms = sae.W_dec.data.norm(dim=1)
+    assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5)
+    sae.save_to_disk(tmp_path / "layers.0")
+    with safe_open(str(tmp_path / "layers.0" / "sae.safetensors"), framework="pt") as f:
+        assert sorted(f.keys()) == ["W_dec", "b_dec", "encoder.bias", "encoder.weight"]
+    cfg = json.load(open(tmp_path / "layers.0" / "cfg.json"))
+    assert cfg["d_in"] == 16 and cfg["num_latents"] == 64 and cfg["transcode"] is False
+    back = SparseCoder.load_many(str(tmp_path), local=True)["layers.0"]
+    assert torch.equal(back.encoder.weight, sae.encoder.weight)
+    enc_only = SparseCoder.load_from_disk(tmp_path / "layers.0", decoder=False)
+    assert enc_only.W_dec is None
+
+
+def test_compute_on_cpu_fails_loudly():
+    sae = SparseCoder(16, SparseCoderConfig(num_latents=64, k=4), device="cpu")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        sae(torch.randn(4, 16))
