@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens per step of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None,
+                    help="time one kernel alone on random inputs of the given sizes instead of the step: "
+                         "encode | decode | bwd_acts | csr | rows | adam | normalize | all")
     return ap.parse_args()
 
 
@@ -330,9 +333,83 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def run_kernel(a):
+    """Times single entry points in isolation (CUDA events on the launching
+    stream, 2 warm-up + 5 timed launches) and prints one JSON line per kernel."""
+    from sparsify_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    N, D, M, k = a.tokens, a.d, a.latents, a.k
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(N, D, device=dev, generator=g).bfloat16()
+    W = (torch.randn(M, D, device=dev, generator=g) / D ** 0.5).bfloat16()
+    b = 0.1 * torch.randn(M, device=dev, generator=g)
+    peaks = measured_peaks()
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    which = a.kernel
+    results = []
+    vals, idx = ops.encode_topk_tc(x, W, b, k)
+    if which in ("encode", "all"):
+        ms = timed(lambda: ops.encode_topk_tc(x, W, b, k))
+        tf = 2.0 * N * D * M / (ms * 1e-3) / 1e12
+        results.append(dict(kernel="encode_topk", ms=ms, tflops=tf, frac=tf / peaks["tflops"]))
+    gout = torch.randn(N, D, device=dev, generator=g)
+    if which in ("decode", "all"):
+        ms = timed(lambda: ops.embedding_bag_fwd(idx, vals, W, None))
+        nbytes = N * k * D * 2 + N * k * 12 + N * D * 4
+        results.append(dict(kernel="embedding_bag_fwd", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+    if which in ("bwd_acts", "all"):
+        ms = timed(lambda: ops.embedding_bag_bwd_acts(idx, gout, W))
+        nbytes = N * k * D * 2 + N * D * 4 + N * k * 12
+        results.append(dict(kernel="embedding_bag_bwd_acts", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+    if which in ("csr", "rows", "all"):
+        ms = timed(lambda: ops.csr_build(idx, M))
+        results.append(dict(kernel="csr_build", ms=ms))
+        row_ptr, entries = ops.csr_build(idx, M)
+        out = {}
+        gacts = torch.randn(N, k, device=dev, generator=g)
+        def rows():
+            nonlocal out
+            out = ops.rows_accumulate(row_ptr, entries, k, M, D, vals, gout, coefB=gacts, vecB=x,
+                                      biasB=True, out=out)
+        ms = timed(rows)
+        nbytes = 2 * M * D * 4 + N * D * 4 + N * D * 2 + N * k * 12
+        results.append(dict(kernel="rows_accumulate", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+        del out
+    if which in ("adam", "normalize", "all"):
+        p = torch.randn(M, D, device=dev, generator=g)
+        gr, m, v = torch.randn_like(p), torch.zeros_like(p), torch.zeros_like(p)
+        sh = torch.empty(M, D, device=dev, dtype=torch.bfloat16)
+        kw = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, step=3)
+        ms = timed(lambda: ops.adam_rows_(p, gr, m, v, project=False, shadow=sh, **kw))
+        results.append(dict(kernel="adam_flat", ms=ms, gbs=M * D * 30 / ms / 1e6, frac=M * D * 30 / ms / 1e6 / peaks["hbm"]))
+        ms = timed(lambda: ops.adam_rows_(p, gr, m, v, project=True, shadow=sh, **kw))
+        results.append(dict(kernel="adam_rows_project", ms=ms, gbs=M * D * 34 / ms / 1e6, frac=M * D * 34 / ms / 1e6 / peaks["hbm"]))
+        ms = timed(lambda: ops.normalize_rows_(p, 1e-7, sh))
+        results.append(dict(kernel="normalize_rows", ms=ms, gbs=M * D * 10 / ms / 1e6, frac=M * D * 10 / ms / 1e6 / peaks["hbm"]))
+    for r in results:
+        r.update(N=N, D=D, M=M, k=k)
+        print(json.dumps(r), flush=True)
+
+
 if __name__ == "__main__":
     args = parse_args()
-    if args.impl == "reference":
+    if args.kernel:
+        run_kernel(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -82,7 +82,7 @@ int sc_groupmax_rows(const float* pre, int64_t N, int64_t M, int k,
 /* Fused tcgen05 path: bf16 x[N,D] and W[M,D], fp32 bias, fp32 TMEM
  * accumulation; bias + ReLU + running per-row top-k in the epilogue so the
  * N x M matrix never reaches HBM; then a merge picks the final k per row.
- * Requirements: D % 64 == 0, M % 8 == 0, k <= 128, M >= k.
+ * Requirements: D % 8 == 0 (16-byte rows), k <= 128, M >= k.
  * ws must hold sc_encode_topk_workspace_bytes(N, D, M, k) bytes, 256-aligned.
  * status_word (device int32, may be NULL) receives a non-zero code if a
  * bounded wait inside the kernel gave up.
@@ -146,6 +146,16 @@ int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv, void* ws,
  * if diff != NULL also writes diff = a - b. */
 int sc_sq_err(const float* a, const float* b, int64_t n, float* diff,
               float* sse, void* ws, size_t ws_bytes, void* stream);
+
+/* out[d] = sum_r w[r] * Y[r,d] (w == NULL: plain column sums), fp32 result,
+ * fixed summation order. Used for the b_dec gradient: column sums of the
+ * residual, and W_enc^T grad_b_enc, which equals the column sum of the
+ * encoder's input gradient (sparsify/fused_encoder.py:58-64 followed by the
+ * `x - b_dec` of sparsify/sparse_coder.py:191-192) without gathering it.
+ * ws: sc_loss_workspace_bytes(D) bytes. */
+int sc_weighted_colsum(const void* Y, int y_dtype, const float* w, int64_t R,
+                       int64_t D, float* out, void* ws, size_t ws_bytes,
+                       void* stream);
 
 /* ---- weight update ------------------------------------------------------
  * sparsify/sparse_coder.py:273-279: W[m,:] /= (||W[m,:]||_2 + eps), in place;

@@ -51,6 +51,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_loss_workspace_bytes": (c_size_t, [I64]),
     "sc_total_variance": (c_int, [P, I64, I64, P, P, c_size_t, P]),
     "sc_sq_err": (c_int, [P, P, I64, P, P, P, c_size_t, P]),
+    "sc_weighted_colsum": (c_int, [P, c_int, P, I64, I64, P, P, c_size_t, P]),
     "sc_normalize_rows": (c_int, [P, I64, I64, c_float, P, P]),
     "sc_adam_rows": (
         c_int,

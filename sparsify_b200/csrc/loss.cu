@@ -8,9 +8,10 @@ namespace {
 constexpr int kSlices = 64;       // row slices for the column sums
 constexpr int kRedBlocks = 1024;  // partial sums of the flat reductions
 
-// partial[s][d] = sum of y[n][d] over the rows n of slice s
+// partial[s][d] = sum of w[n] * y[n][d] over the rows n of slice s (w == NULL: 1)
+template <typename T>
 __global__ void __launch_bounds__(256)
-colsum_partial_kernel(const float* __restrict__ y, int64_t N, int64_t D,
+colsum_partial_kernel(const T* __restrict__ y, const float* __restrict__ w, int64_t N, int64_t D,
                       float* __restrict__ partial) {
   __shared__ float s_acc[8][33];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -20,7 +21,10 @@ colsum_partial_kernel(const float* __restrict__ y, int64_t N, int64_t D,
   const int64_t r1 = r0 + per < N ? r0 + per : N;
   float acc = 0.f;
   if (d < D)
-    for (int64_t r = r0 + warp; r < r1; r += 8) acc += __ldg(y + r * D + d);
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      const float wr = w != nullptr ? __ldg(w + r) : 1.f;
+      if (wr != 0.f) acc = fmaf(wr, sc::load1<T>(y + r * D + d), acc);
+    }
   s_acc[warp][lane] = acc;
   __syncthreads();
   if (warp == 0) {
@@ -31,13 +35,14 @@ colsum_partial_kernel(const float* __restrict__ y, int64_t N, int64_t D,
   }
 }
 
-__global__ void colmean_finish_kernel(const float* __restrict__ partial, int64_t N, int64_t D,
-                                      float* __restrict__ mean) {
+// out[d] = scale * sum_s partial[s][d]
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, float scale, int64_t D,
+                                     float* __restrict__ out) {
   int64_t d = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (d >= D) return;
   float t = 0.f;
   for (int s = 0; s < kSlices; ++s) t += partial[(int64_t)s * D + d];
-  mean[d] = t / (float)N;
+  out[d] = t * scale;
 }
 
 // block partials of sum((a[i] - b[i % D])^2) when BROADCAST, else sum((a[i]-b[i])^2)
@@ -90,10 +95,10 @@ extern "C" int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv
   float* mean = partial + (size_t)kSlices * D;
   float* red = mean + D;
   dim3 grid((unsigned)((D + 31) / 32), kSlices);
-  colsum_partial_kernel<<<grid, 256, 0, st>>>(y, N, D, partial);
+  colsum_partial_kernel<float><<<grid, 256, 0, st>>>(y, nullptr, N, D, partial);
   SC_CHECK_LAUNCH("colsum_partial");
-  colmean_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, N, D, mean);
-  SC_CHECK_LAUNCH("colmean_finish");
+  colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f / (float)N, D, mean);
+  SC_CHECK_LAUNCH("colsum_finish");
   const int blocks = flat_blocks(N * D);
   sqdiff_partial_kernel<true><<<blocks, 256, 0, st>>>(y, mean, N * D, D, nullptr, red);
   SC_CHECK_LAUNCH("sqdiff_partial");
@@ -116,5 +121,26 @@ extern "C" int sc_sq_err(const float* a, const float* b, int64_t n, float* diff,
   SC_CHECK_LAUNCH("sqdiff_partial");
   final_sum_kernel<<<1, 256, 0, st>>>(red, blocks, sse);
   SC_CHECK_LAUNCH("final_sum");
+  return SC_OK;
+}
+
+extern "C" int sc_weighted_colsum(const void* Y, int y_dtype, const float* w, int64_t R, int64_t D,
+                                  float* out, void* ws, size_t ws_bytes, void* stream) {
+  SC_REQUIRE(R > 0 && D > 0, "sc_weighted_colsum: bad shape");
+  SC_REQUIRE(Y && out && ws, "sc_weighted_colsum: null pointer");
+  SC_REQUIRE(sc::valid_dtype(y_dtype), "sc_weighted_colsum: bad dtype");
+  if (ws_bytes < sc_loss_workspace_bytes(D))
+    return sc::fail(SC_ERR_WORKSPACE, "sc_weighted_colsum: workspace %zu < %zu", ws_bytes,
+                    sc_loss_workspace_bytes(D));
+  cudaStream_t st = sc::as_stream(stream);
+  float* partial = static_cast<float*>(ws);
+  dim3 grid((unsigned)((D + 31) / 32), kSlices);
+  if (y_dtype == SC_F32)
+    colsum_partial_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(Y), w, R, D, partial);
+  else
+    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(Y), w, R, D, partial);
+  SC_CHECK_LAUNCH("colsum_partial");
+  colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f, D, out);
+  SC_CHECK_LAUNCH("colsum_finish");
   return SC_OK;
 }
