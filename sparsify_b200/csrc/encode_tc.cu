@@ -185,7 +185,10 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       int minpos = 0;
       // rows past N are padding: an infinite bound keeps them out of the lists
       const float tau = (grow < p.N) ? __ldcg(p.tau + grow) : INFINITY;
-      float thr_eff = fmaxf(thr, tau);
+      // Threshold the raw (pre-ReLU) value is compared with: max(thr, tau), or
+      // -inf while that is still negative (list not full and no bound known), so
+      // that every value, clamped to >= 0 on insertion, is taken.
+      float thr_cmp = fmaxf(thr, tau) < 0.f ? -INFINITY : fmaxf(thr, tau);
       __syncwarp();
 
       for (int t = t0; t < t1 && ok; ++t) {
@@ -209,15 +212,35 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
+          // Pass 1 (no cross-lane traffic, full ILP): add the bias and mark the
+          // columns that beat this row's threshold as it stood at chunk start.
+          float v[32];
+          const float4* sb4 = reinterpret_cast<const float4*>(sb + c * 32);
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 b4 = sb4[i4];
+            v[4 * i4 + 0] = __uint_as_float(r[4 * i4 + 0]) + b4.x;
+            v[4 * i4 + 1] = __uint_as_float(r[4 * i4 + 1]) + b4.y;
+            v[4 * i4 + 2] = __uint_as_float(r[4 * i4 + 2]) + b4.z;
+            v[4 * i4 + 3] = __uint_as_float(r[4 * i4 + 3]) + b4.w;
+          }
+          unsigned m = 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m |= (v[i] > thr_cmp ? 1u : 0u) << i;
+          const int valid = ncols - c * 32;  // columns of this chunk inside the matrix
+          if (valid < 32) m &= valid <= 0 ? 0u : ((1u << valid) - 1u);
+          const unsigned colmask = __reduce_or_sync(0xffffffffu, m);
+          if (colmask == 0) continue;
+          // Pass 2: the warp serves the marked (row, column) pairs one at a time.
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float v = fmaxf(__uint_as_float(r[i]) + sb[c * 32 + i], 0.f);
-            bool pr = (v > thr_eff) && (c * 32 + i < ncols);
+            if (((colmask >> i) & 1u) == 0) continue;  // warp-uniform
+            const bool pr = ((m >> i) & 1u) && (v[i] > thr_cmp);
             unsigned bal = __ballot_sync(0xffffffffu, pr);
             while (bal) {
               const int src = __ffs(bal) - 1;
               bal &= bal - 1;
-              const float bv = __shfl_sync(0xffffffffu, v, src);
+              const float bv = fmaxf(__shfl_sync(0xffffffffu, v[i], src), 0.f);
               const int bp = __shfl_sync(0xffffffffu, minpos, src);
               const int lrow = q * 32 + src;
               if (lane == 0) {
@@ -236,7 +259,8 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
               if (lane == src) {
                 thr = __int_as_float(mn);
                 minpos = mpos;
-                thr_eff = fmaxf(thr, tau);
+                const float te = fmaxf(thr, tau);
+                thr_cmp = te < 0.f ? -INFINITY : te;
               }
               __syncwarp();
             }

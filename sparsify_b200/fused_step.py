@@ -1,0 +1,101 @@
+"""The training hot path as one autograd function: encode -> top-k -> decode ->
+FVU, with a hand-scheduled backward.
+
+It computes what SparseCoder.forward composes from `fused_encoder`,
+`decoder_impl` and elementwise torch ops (sparsify/sparse_coder.py:205-271 with
+sparsify/fused_encoder.py:52-87 and sparsify/xformers.py:139-185 behind it), for
+the common case - no skip connection, no dead latents in this batch, no
+Multi-TopK, inputs that need no gradient - in fewer passes over memory:
+
+* `x - b_dec` and the bf16 cast are one kernel;
+* the residual e = y - out and its squared sum are one kernel; the gradient of
+  the output is s*e with s = -2*dFVU/tv, and s is folded into the [N,k]
+  coefficients instead of being applied to an [N,D] tensor;
+* the CSR of the selected latents is built once and one pass produces the
+  gradients of W_dec, W_enc and b_enc;
+* the encoder's input gradient is never gathered: its column sum, which is all
+  that b_dec needs, equals W_enc^T grad_b_enc.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import ops
+
+
+class FusedSaeStep(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, y: Tensor | None, W_enc: Tensor, b_enc: Tensor, W_dec: Tensor,
+                b_dec: Tensor, sae):
+        cfg = sae.cfg
+        lowp = sae._lowp()
+        comp = torch.bfloat16 if lowp else torch.float32
+        M, D = W_enc.shape
+        k = cfg.k
+        x = x.detach()
+        xe = ops.prep_input(x, None if cfg.transcode else b_dec.detach(), comp)
+        w_enc_src = sae.shadow("encoder.weight") if lowp else W_enc.detach()
+        if cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
+            acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), k)
+        else:
+            pre = ops.preacts_dense(xe, w_enc_src, b_enc.detach())
+            acts, idx = (ops.topk_rows if cfg.activation == "topk" else ops.groupmax_rows)(pre, k)
+            del pre
+        gather_lp = sae.precision == "bf16" and W_dec.dtype == torch.float32
+        w_dec_src = sae.shadow("W_dec") if gather_lp else W_dec.detach()
+        out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())
+        target = (x if y is None else y.detach()).to(torch.float32)
+        tv = ops.total_variance(target)
+        sse, e = ops.sq_err(target, out, want_diff=True)
+        fvu = sse / tv
+
+        ctx.save_for_backward(xe, idx, acts, e, tv)
+        ctx.w_enc_src, ctx.w_dec_src = w_enc_src, w_dec_src
+        ctx.shape = (M, D, k)
+        ctx.transcode = cfg.transcode
+        ctx.set_materialize_grads(False)
+        ctx.mark_non_differentiable(idx)
+        return out, acts, idx, fvu
+
+    @staticmethod
+    def backward(ctx, g_out, g_acts, g_idx, g_fvu):
+        xe, idx, acts, e, tv = ctx.saved_tensors
+        M, D, k = ctx.shape
+        dev = e.device
+        # d fvu / d out = -2 e / tv
+        s = (-2.0 * g_fvu / tv).to(torch.float32) if g_fvu is not None else torch.zeros((), device=dev)
+        if g_out is not None:
+            gout = torch.addcmul(g_out.to(torch.float32), e, s)  # general case: materialise
+            scale = torch.ones((), device=dev)
+        else:
+            gout, scale = e, s
+
+        gacts = ops.embedding_bag_bwd_acts(idx, gout, ctx.w_dec_src) * scale
+        if g_acts is not None:
+            gacts = gacts + g_acts
+        row_ptr, entries = ops.csr_build(idx, M)
+        res = ops.rows_accumulate(row_ptr, entries, k, M, D, acts * scale, gout,
+                                  coefB=gacts, vecB=xe, biasB=True)
+        g_W_dec, g_W_enc, g_b_enc = res["gradA"], res["gradB"], res["gbiasB"]
+        g_b_dec = ops.weighted_colsum(gout) * scale
+        if not ctx.transcode:
+            # minus the column sum of the encoder's input gradient
+            g_b_dec = g_b_dec - ops.weighted_colsum(ctx.w_enc_src, g_b_enc)
+        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None
+
+
+def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
+    """The fused function covers the common training case; everything else runs
+    the composed path in SparseCoder.forward."""
+    return (
+        x.is_cuda
+        and sae.W_dec is not None
+        and sae.W_skip is None
+        and not sae.cfg.multi_topk
+        and num_dead == 0
+        and not x.requires_grad
+        and x.shape[-1] % 4 == 0
+        and sae.dtype == torch.float32
+    )

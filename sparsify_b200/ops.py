@@ -246,6 +246,20 @@ def sq_err(a: Tensor, b: Tensor, want_diff: bool = False) -> tuple[Tensor, Tenso
     return sse, diff
 
 
+def weighted_colsum(Y: Tensor, w: Tensor | None = None) -> Tensor:
+    """sum_r w[r] * Y[r, :] (w=None: column sums) as an fp32 [D] tensor."""
+    _check_cuda(Y, w)
+    Y = Y.detach().contiguous()
+    R, D = Y.shape
+    out = torch.empty(D, dtype=torch.float32, device=Y.device)
+    ws = _ws(_lib.lib().sc_loss_workspace_bytes(D), Y.device)
+    w32 = _f32(w)
+    with torch.cuda.device(Y.device):
+        call("sc_weighted_colsum", ptr(Y), dtype_code(Y), ptr(w32), R, D, ptr(out), ptr(ws),
+             ws.numel(), _stream(Y))
+    return out
+
+
 def normalize_rows_(W: Tensor, eps: float, shadow: Tensor | None = None) -> None:
     """In place W[m] /= ||W[m]|| + eps; optionally refreshes a bf16 shadow."""
     _check_cuda(W, shadow)

@@ -31,6 +31,7 @@ from torch import Tensor, nn
 from . import ops
 from .config import SparseCoderConfig
 from .fused_encoder import EncoderOutput, fused_encoder
+from .fused_step import FusedSaeStep, fused_supported
 from .utils import decoder_impl
 
 
@@ -76,6 +77,7 @@ class SparseCoder(nn.Module):
         self.d_in = d_in
         self.num_latents = cfg.num_latents or d_in * cfg.expansion_factor
         self.precision = "bf16"
+        self.fused = True  # use the single-function training path when it applies
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 
         self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
@@ -222,6 +224,11 @@ class SparseCoder(nn.Module):
         self, x: Tensor, y: Tensor | None = None, *, dead_mask: Tensor | None = None
     ) -> ForwardOutput:
         num_dead = int(dead_mask.sum()) if dead_mask is not None else 0
+        if self.fused and fused_supported(self, x, num_dead):
+            sae_out, top_acts, top_indices, fvu = FusedSaeStep.apply(
+                x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self)
+            zero = fvu.new_tensor(0.0)
+            return ForwardOutput(sae_out, top_acts, top_indices, fvu, zero, zero)
         need_dense = self.cfg.multi_topk or num_dead > 0
         top_acts, top_indices, pre_acts = self.encode(x, need_pre_acts=need_dense)
 
