@@ -17,6 +17,8 @@
 // insertions after the first wave of units.
 #include "tc.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 using namespace sc::tc;
@@ -37,7 +39,7 @@ struct Plan {
   int stages;     // smem ring depth
   int units;      // n_rb * n_strips
   size_t smem;    // dynamic shared memory bytes
-  size_t off_lists_val, off_lists_idx, off_bias, off_bars;
+  size_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
 
 // Status codes written to the device status word by a wait that gave up.
@@ -51,7 +53,8 @@ struct Params {
   int32_t* status;
   int64_t N, D, M;
   int k, n_rb, n_ct, n_strips, stages, units;
-  uint32_t off_lists_val, off_lists_idx, off_bias, off_bars;
+  int debug;  // diagnostics: bit 0 = epilogue only drains (no bias / top-k work)
+  uint32_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
 
 __device__ __forceinline__ void decode_unit(const Params& p, int u, int& rb, int& strip, int& t0, int& t1) {
@@ -62,6 +65,72 @@ __device__ __forceinline__ void decode_unit(const Params& p, int u, int& rb, int
   rb = g * kRowGroup + rem % rg;
   t0 = (int)(((int64_t)strip * p.n_ct) / p.n_strips);
   t1 = (int)(((int64_t)(strip + 1) * p.n_ct) / p.n_strips);
+}
+
+// Per-row running top-k list, owned by one thread (the row's TMEM lane) and
+// kept in shared memory column-wise - entry j of row r at l_val[j * 128 + r] -
+// so that the 32 rows of a warp touch 32 different banks. Entries are grouped
+// by eight with each group's minimum cached (g_val / g_pos), so replacing the
+// row minimum rescans one group and the group minima instead of all k
+// entries. While the list still has free slots, values are appended without
+// any scan. Lanes of a warp with a candidate in the same column run this
+// together (plain SIMT divergence, no cross-lane traffic). Out of line: it is
+// called from 32 unrolled sites.
+struct RowState {
+  float thr;      // smallest value in the row's list (-1 while it has free slots)
+  float thr_cmp;  // what a raw pre-activation must exceed to enter the list
+  int minpos;     // position of the smallest value
+  int cnt;        // filled entries (== k once the list is full)
+};
+
+constexpr int kGroup = 8;
+
+__device__ __forceinline__ void group_min(const float* lv, int k, int g, float& best, int& pos) {
+  best = INFINITY;
+  pos = g * kGroup;
+  const int hi = min(k, (g + 1) * kGroup);
+  for (int j = g * kGroup; j < hi; ++j) {
+    const float x = lv[j * BM];
+    if (x < best) { best = x; pos = j; }
+  }
+}
+
+__device__ __forceinline__ void global_min(const float* gv, const uint16_t* gp, int groups, RowState& st) {
+  float best = gv[0];
+  int pos = gp[0];
+  for (int g = 1; g < groups; ++g) {
+    const float x = gv[g * BM];
+    if (x < best) { best = x; pos = gp[g * BM]; }
+  }
+  st.thr = best;
+  st.minpos = pos;
+}
+
+__device__ __noinline__ RowState list_insert(float* lv, uint16_t* li, float* gv, uint16_t* gp, int k, float v,
+                                             uint16_t rel_col, float tau, RowState st) {
+  const int groups = (k + kGroup - 1) / kGroup;
+  if (st.cnt < k) {  // append
+    lv[st.cnt * BM] = fmaxf(v, 0.f);
+    li[st.cnt * BM] = rel_col;
+    if (++st.cnt < k) return st;
+    for (int g = 0; g < groups; ++g) {  // list just became full: build the group minima
+      float best; int pos;
+      group_min(lv, k, g, best, pos);
+      gv[g * BM] = best;
+      gp[g * BM] = (uint16_t)pos;
+    }
+  } else {  // replace the minimum
+    lv[st.minpos * BM] = fmaxf(v, 0.f);
+    li[st.minpos * BM] = rel_col;
+    const int g = st.minpos / kGroup;
+    float best; int pos;
+    group_min(lv, k, g, best, pos);
+    gv[g * BM] = best;
+    gp[g * BM] = (uint16_t)pos;
+  }
+  global_min(gv, gp, groups, st);
+  st.thr_cmp = fmaxf(st.thr, tau);
+  return st;
 }
 
 __global__ void init_tau_kernel(float* tau, int64_t n, int32_t* status) {
@@ -171,6 +240,11 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;          // row inside the tile
     const int k = p.k;
+    float* lv = l_val + row;                // this row's list: lv[j * BM], li[j * BM]
+    uint16_t* li = l_idx + row;
+    float* gv = reinterpret_cast<float*>(smem + p.off_gmin) + row;            // group minima
+    uint16_t* gp = reinterpret_cast<uint16_t*>(smem + p.off_gpos) + row;
+    float* sb = s_bias + (warp - 2) * BN;   // this warp's copy of the tile's bias
     int buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -179,21 +253,18 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       decode_unit(p, u, rb, strip, t0, t1);
       const int64_t grow = (int64_t)rb * BM + row;
       const int64_t strip_col0 = (int64_t)t0 * BN;
-      // reset this row's list
-      for (int j = 0; j < k; ++j) l_val[row * k + j] = -1.f;
-      float thr = -1.f;    // smallest value in the list (-1 while it has free slots)
-      int minpos = 0;
+      RowState st;
+      st.thr = -1.f; st.minpos = 0; st.cnt = 0;
+      float published = -1.f;  // last bound this thread pushed to p.tau
+      unsigned n_ins = 0, n_cols = 0;  // diagnostics (debug bit 1)
       // rows past N are padding: an infinite bound keeps them out of the lists
-      const float tau = (grow < p.N) ? __ldcg(p.tau + grow) : INFINITY;
+      float tau = (grow < p.N) ? __ldcg(p.tau + grow) : INFINITY;
       // Threshold the raw (pre-ReLU) value is compared with: max(thr, tau), or
       // -inf while that is still negative (list not full and no bound known), so
       // that every value, clamped to >= 0 on insertion, is taken.
-      float thr_cmp = fmaxf(thr, tau) < 0.f ? -INFINITY : fmaxf(thr, tau);
-      __syncwarp();
+      st.thr_cmp = tau < 0.f ? -INFINITY : tau;
 
       for (int t = t0; t < t1 && ok; ++t) {
-        // stage the bias of this tile (one private copy per warp: no cross-warp barrier)
-        float* sb = s_bias + (warp - 2) * BN;
         __syncwarp();
         for (int c = lane; c < BN; c += 32) {
           const int64_t col = (int64_t)t * BN + c;
@@ -208,12 +279,12 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         const int ncols = (int)min((int64_t)BN, p.M - tile_col0);
         const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < ((p.debug & 1) ? 0 : BN / 32); ++c) {
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
-          // Pass 1 (no cross-lane traffic, full ILP): add the bias and mark the
-          // columns that beat this row's threshold as it stood at chunk start.
+          // Pass 1 (full ILP): add the bias and mark the columns that beat this
+          // row's threshold as it stood at chunk start.
           float v[32];
           const float4* sb4 = reinterpret_cast<const float4*>(sb + c * 32);
 #pragma unroll
@@ -226,45 +297,33 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           }
           unsigned m = 0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m |= (v[i] > thr_cmp ? 1u : 0u) << i;
+          for (int i = 0; i < 32; ++i) m |= (v[i] > st.thr_cmp ? 1u : 0u) << i;
           const int valid = ncols - c * 32;  // columns of this chunk inside the matrix
           if (valid < 32) m &= valid <= 0 ? 0u : ((1u << valid) - 1u);
           const unsigned colmask = __reduce_or_sync(0xffffffffu, m);
           if (colmask == 0) continue;
-          // Pass 2: the warp serves the marked (row, column) pairs one at a time.
+          // Pass 2: rows with a marked column insert it into their own list.
+          const uint16_t rel0 = (uint16_t)(tile_col0 - strip_col0 + c * 32);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (((colmask >> i) & 1u) == 0) continue;  // warp-uniform
-            const bool pr = ((m >> i) & 1u) && (v[i] > thr_cmp);
-            unsigned bal = __ballot_sync(0xffffffffu, pr);
-            while (bal) {
-              const int src = __ffs(bal) - 1;
-              bal &= bal - 1;
-              const float bv = fmaxf(__shfl_sync(0xffffffffu, v[i], src), 0.f);
-              const int bp = __shfl_sync(0xffffffffu, minpos, src);
-              const int lrow = q * 32 + src;
-              if (lane == 0) {
-                l_val[lrow * k + bp] = bv;
-                l_idx[lrow * k + bp] = (uint16_t)(tile_col0 - strip_col0 + c * 32 + i);
-              }
-              __syncwarp();
-              int key = 0x7fffffff, pos = 0;
-              for (int j = lane; j < k; j += 32) {
-                const int kk = __float_as_int(l_val[lrow * k + j]);
-                if (kk < key) { key = kk; pos = j; }
-              }
-              const int mn = __reduce_min_sync(0xffffffffu, key);
-              const unsigned who = __ballot_sync(0xffffffffu, key == mn);
-              const int mpos = __shfl_sync(0xffffffffu, pos, __ffs(who) - 1);
-              if (lane == src) {
-                thr = __int_as_float(mn);
-                minpos = mpos;
-                const float te = fmaxf(thr, tau);
-                thr_cmp = te < 0.f ? -INFINITY : te;
-              }
-              __syncwarp();
+            if (((colmask >> i) & 1u) == 0) continue;  // warp-uniform skip
+            ++n_cols;
+            if (((m >> i) & 1u) && v[i] > st.thr_cmp) {
+              st = list_insert(lv, li, gv, gp, k, v[i], (uint16_t)(rel0 + i), tau, st);
+              ++n_ins;
             }
           }
+        }
+        // Exchange the row's lower bound with the CTAs working on other strips of
+        // the same rows: push ours when it grew, pull theirs for the next tile.
+        if (grow < p.N) {
+          if (st.cnt == k && st.thr > published) {
+            atomicMax(reinterpret_cast<int*>(p.tau + grow), __float_as_int(st.thr));
+            published = st.thr;
+          }
+          tau = fmaxf(tau, __ldcg(p.tau + grow));
+          if (st.cnt == k) st.thr_cmp = fmaxf(st.thr, tau);
+          else st.thr_cmp = tau < 0.f ? -INFINITY : tau;
         }
         // accumulator drained
         fence_before_sync();
@@ -274,24 +333,25 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         if (buf == 0) acc_phase ^= 1;
       }
       if (!ok) break;
-      // write this strip's candidates and publish the row's lower bound
-      __syncwarp();
-      for (int rr = 0; rr < 32; ++rr) {
-        const int lrow = q * 32 + rr;
-        const int64_t gr = (int64_t)rb * BM + lrow;
-        if (gr >= p.N) break;
-        float* cv = p.cand_vals + (gr * p.n_strips + strip) * k;
-        int32_t* ci = p.cand_idx + (gr * p.n_strips + strip) * k;
-        for (int j = lane; j < k; j += 32) {
-          const float v = l_val[lrow * k + j];
-          cv[j] = v;
-          ci[j] = v >= 0.f ? (int32_t)(strip_col0 + l_idx[lrow * k + j]) : -1;
-        }
+      if ((p.debug & 2) && p.status != nullptr) {  // status[1] = insertions, status[2] = visited columns
+        atomicAdd(p.status + 1, (int)n_ins);
+        if (lane == 0) atomicAdd(p.status + 2, (int)n_cols);
       }
-      if (grow < p.N && thr >= 0.f) atomicMax(reinterpret_cast<int*>(p.tau + grow), __float_as_int(thr));
-      __syncwarp();
+      // write this strip's candidates and publish the row's lower bound
+      if (grow < p.N) {
+        float* cv = p.cand_vals + (grow * p.n_strips + strip) * k;
+        int32_t* ci = p.cand_idx + (grow * p.n_strips + strip) * k;
+        for (int j = 0; j < k; ++j) {
+          const bool used = j < st.cnt;
+          cv[j] = used ? lv[j * BM] : -1.f;
+          ci[j] = used ? (int32_t)(strip_col0 + li[j * BM]) : -1;
+        }
+        if (st.cnt == k && st.thr > published)
+          atomicMax(reinterpret_cast<int*>(p.tau + grow), __float_as_int(st.thr));
+      }
     }
   }
+
 
   // teardown
   fence_before_sync();
@@ -365,7 +425,9 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
   pl->units = pl->n_rb * pl->n_strips;
   const size_t lists_val = (size_t)BM * k * sizeof(float);
   const size_t lists_idx = (size_t)BM * k * sizeof(uint16_t);
-  const size_t fixed = lists_val + lists_idx + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
+  const size_t groups = (size_t)(k + 7) / 8;
+  const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
+  const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
   const size_t budget = 227 * 1024;
   if (fixed + 2 * kStageBytes > budget) return SC_ERR_UNSUPPORTED;
   int stages = (int)((budget - fixed) / kStageBytes);
@@ -373,7 +435,9 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
   pl->stages = stages;
   pl->off_lists_val = (size_t)stages * kStageBytes;
   pl->off_lists_idx = pl->off_lists_val + lists_val;
-  pl->off_bias = pl->off_lists_idx + lists_idx;
+  pl->off_gmin = pl->off_lists_idx + lists_idx;
+  pl->off_gpos = pl->off_gmin + gmin;
+  pl->off_bias = pl->off_gpos + gpos;
   pl->off_bars = pl->off_bias + 4 * BN * sizeof(float);
   pl->smem = pl->off_bars + 256 + 1024;
   return SC_OK;
@@ -425,8 +489,11 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   Params p;
   p.bias = bias; p.cand_vals = cand_vals; p.cand_idx = cand_idx; p.tau = tau; p.status = status_word;
   p.N = N; p.D = D; p.M = M; p.k = k;
+  const char* dbg = getenv("SC_ENCODE_DEBUG");
+  p.debug = dbg ? atoi(dbg) : 0;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
   p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
+  p.off_gmin = (uint32_t)pl.off_gmin; p.off_gpos = (uint32_t)pl.off_gpos;
   p.off_bias = (uint32_t)pl.off_bias; p.off_bars = (uint32_t)pl.off_bars;
 
   cudaStream_t st = sc::as_stream(stream);
