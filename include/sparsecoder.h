@@ -118,6 +118,23 @@ int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M,
                  int32_t* row_ptr, int32_t* entries, void* ws, size_t ws_bytes,
                  void* stream);
 
+/* sc_csr_build for callers that cannot hand over scratch memory. It has no
+ * counterpart in the reference. Some hosts of this library may not allocate on
+ * the device at the point where they need the CSR: code running inside another
+ * framework's memory plan or a fixed arena, or inside a region where
+ * cudaMalloc and cudaFree are off limits because they synchronise the device.
+ * This variant takes inputs and outputs only; its two counter arrays live in
+ * a static device array inside the library (2 MiB, held by every GPU that
+ * loads the library until the process exits), which caps it at
+ * M <= 262144 latents: a larger M returns SC_ERR_TOO_LARGE. It calls no
+ * cudaMalloc, cudaFree or allocating routine. The first call on each device
+ * resolves the array's device address (cudaGetSymbolAddress) and should
+ * therefore come before any stream capture on that device. All calls share the
+ * one array: calls that may overlap on the GPU (different streams, or the same
+ * device from several threads) race and must be serialised by the caller. */
+int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_t M,
+                         int32_t* row_ptr, int32_t* entries, void* stream);
+
 /* Per-latent row accumulate over latents [lat_begin, lat_end):
  *   gradA[m,:] = sum_e coefA[e] * vecA[e / k, :]   gbiasA[m] = sum_e coefA[e]
  *   gradB[m,:] = sum_e coefB[e] * vecB[e / k, :]   gbiasB[m] = sum_e coefB[e]

@@ -4,6 +4,8 @@
 // per-latent sort of the claimed slots, so that the entries of each latent
 // come out in ascending flat position n*k+j whatever order the atomics ran in.
 // Latents with more than kSortMax entries keep the arrival order.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -154,6 +156,76 @@ extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int
     SC_CHECK_LAUNCH("csr_fill");
     csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(
         row_ptr, M, entries);
+    SC_CHECK_LAUNCH("csr_sort");
+  } else {
+    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
+    SC_CHECK_LAUNCH("csr_scan");
+  }
+  return SC_OK;
+}
+
+// ---------------------------------------------------------------------------
+// sc_csr_build_noalloc: the same CSR build for callers that cannot obtain
+// device memory for the scratch (see include/sparsecoder.h). The scratch lives
+// in a fixed array that is part of the library image on every GPU.
+namespace {
+
+constexpr int64_t kNoAllocMaxLatents = 262144;  // 2 x 1 MiB of counters
+static __device__ __align__(256) unsigned char g_csr_scratch[2 * kNoAllocMaxLatents * sizeof(int32_t)];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};  // device address of g_csr_scratch, per device
+
+// Resolves the device address of the static scratch for the current device.
+// In host code the symbol name is only a handle: the address a kernel may use
+// has to come from cudaGetSymbolAddress, once per device, with that device
+// current.
+int scratch_for_current_device(void** out) {
+  int dev = -1;
+  SC_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return sc::fail(SC_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    SC_CUDA(cudaGetSymbolAddress(&p, g_csr_scratch));
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return SC_OK;
+}
+
+}  // namespace
+
+extern "C" int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_t M, int32_t* row_ptr,
+                                    int32_t* entries, void* stream) {
+  SC_REQUIRE(N >= 0 && k > 0 && M > 0, "sc_csr_build_noalloc: bad shape N=%lld k=%d M=%lld",
+             (long long)N, k, (long long)M);
+  if (M > kNoAllocMaxLatents)
+    return sc::fail(SC_ERR_TOO_LARGE, "sc_csr_build_noalloc: M=%lld exceeds the built-in scratch (max %lld latents)",
+                    (long long)M, (long long)kNoAllocMaxLatents);
+  SC_REQUIRE(row_ptr != nullptr, "sc_csr_build_noalloc: null pointer");
+  SC_REQUIRE(N * (int64_t)k < (int64_t(1) << 31), "sc_csr_build_noalloc: N*k must be below 2^31");
+  void* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);
+  if (rc != SC_OK) return rc;
+  cudaStream_t st = sc::as_stream(stream);
+  int32_t* counts = static_cast<int32_t*>(scratch);
+  int32_t* cursor = counts + kNoAllocMaxLatents;
+  const int64_t total = N * k;
+  // the array keeps whatever the previous call left: the histogram must start at zero
+  SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
+  if (total > 0) {
+    SC_REQUIRE(idx && entries, "sc_csr_build_noalloc: null pointer");
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
+    SC_CHECK_LAUNCH("csr_count");
+    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
+    SC_CHECK_LAUNCH("csr_scan");
+    csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
+    SC_CHECK_LAUNCH("csr_fill");
+    csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(row_ptr, M, entries);
     SC_CHECK_LAUNCH("csr_sort");
   } else {
     csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
