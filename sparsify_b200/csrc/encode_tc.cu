@@ -206,15 +206,21 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       int buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      long long wait_tmem = 0, wait_full = 0;  // diagnostics (debug bit 2)
+      const long long t_begin = clock64();
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
         int rb, strip, t0, t1;
         decode_unit(p, u, rb, strip, t0, t1);
         for (int t = t0; t < t1 && ok; ++t) {
+          const long long w0 = clock64();
           if (!mbar_wait(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+          wait_tmem += clock64() - w0;
           fence_after_sync();
           const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
           for (int kc = 0; kc < kc_count; ++kc) {
+            const long long w1 = clock64();
             if (!mbar_wait(&full[stage], phase, p.status, kWaitFull)) { ok = false; break; }
+            wait_full += clock64() - w1;
             fence_after_sync();
             const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
             const uint64_t adesc = make_smem_desc_sw128(sa);
@@ -233,6 +239,12 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           buf ^= 1;
           if (buf == 0) acc_phase ^= 1;
         }
+      }
+      if ((p.debug & 4) && p.status != nullptr && blockIdx.x == 0) {
+        // kilo-cycles of SM 0's MMA thread: total, waiting for a free accumulator, waiting for operands
+        p.status[3] = (int)((clock64() - t_begin) >> 10);
+        p.status[4] = (int)(wait_tmem >> 10);
+        p.status[5] = (int)(wait_full >> 10);
       }
     }
   } else {

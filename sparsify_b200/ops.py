@@ -117,7 +117,7 @@ def encode_topk_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tupl
     idx = torch.empty(N, k, dtype=torch.int64, device=dev)
     nbytes = _lib.lib().sc_encode_topk_workspace_bytes(N, D, M, int(k))
     ws = _ws(nbytes, dev)
-    status = torch.zeros(4, dtype=torch.int32, device=dev)  # [0] wait-timeout code, [1:] diagnostics
+    status = torch.zeros(8, dtype=torch.int32, device=dev)  # [0] wait-timeout code, [1:] diagnostics
     bias32 = _f32(bias)
     with torch.cuda.device(dev):
         end = _timed("encode_topk", dev)
