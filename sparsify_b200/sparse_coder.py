@@ -63,6 +63,9 @@ class ForwardOutput(NamedTuple):
 
 
 class SparseCoder(nn.Module):
+    default_precision = "bf16"
+    """Precision new instances start with ("bf16", "mixed" or "fp32")."""
+
     def __init__(
         self,
         d_in: int,
@@ -76,7 +79,7 @@ class SparseCoder(nn.Module):
         self.cfg = cfg
         self.d_in = d_in
         self.num_latents = cfg.num_latents or d_in * cfg.expansion_factor
-        self.precision = "bf16"
+        self.precision = type(self).default_precision
         self.fused = True  # use the single-function training path when it applies
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 

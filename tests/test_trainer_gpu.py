@@ -1,0 +1,75 @@
+"""The Trainer on the GPU against the reference Trainer's frozen trajectory
+(tests/golden/trainer_adam.safetensors) and its checkpoint tree."""
+
+import json
+import os
+
+import pytest
+import torch
+
+from tests.conftest import load_golden, rel_l2
+from tests.fake_model import FakeModel, dataset
+
+pytestmark = pytest.mark.gpu
+
+
+def make_trainer(tmp_path, meta, acts, precision, **over):
+    from sparsify_b200 import SparseCoder, SparseCoderConfig, TrainConfig, Trainer
+    SparseCoder.default_precision = precision
+    try:
+        cfg = TrainConfig(
+            SparseCoderConfig(num_latents=meta["M"], k=meta["k"]), batch_size=meta["B"], optimizer="adam",
+            lr=meta["lr"], lr_warmup_steps=meta["warmup"], auxk_alpha=meta["auxk_alpha"],
+            dead_feature_threshold=meta["dead_feature_threshold"], hookpoints=["layers.0"],
+            log_to_wandb=False, save_dir=str(tmp_path), run_name="run", save_every=10 ** 9, **over)
+        model = FakeModel(acts, device="cuda")
+        return Trainer(cfg, dataset(meta["steps"], meta["B"], meta["T"]), model)
+    finally:
+        SparseCoder.default_precision = "bf16"
+
+
+def test_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
+    t, meta = load_golden("trainer_adam")
+    trainer = make_trainer(tmp_path, meta, t["acts"], "fp32")
+    sae = trainer.saes["layers.0"]
+    # same initial weights as the reference run (its init is seeded identically, but pin it)
+    with torch.no_grad():
+        sae.encoder.weight.copy_(t["init.W_enc"]); sae.encoder.bias.copy_(t["init.b_enc"])
+        sae.W_dec.copy_(t["init.W_dec"]); sae.b_dec.copy_(t["init.b_dec"])
+    trainer.fit()
+    fvus = [row["fvu/layers.0"] for row in trainer.metrics]
+    assert len(fvus) == meta["steps"]
+    for got, want in zip(fvus, t["fvu"].tolist()):
+        assert abs(got - want) < 1e-3 * max(1.0, abs(want)), (fvus, t["fvu"].tolist())
+    for name, p in (("W_enc", sae.encoder.weight), ("b_enc", sae.encoder.bias),
+                    ("W_dec", sae.W_dec), ("b_dec", sae.b_dec)):
+        assert rel_l2(p.detach(), t[f"final.{name}"]) < 5e-3, name
+    assert torch.equal(trainer.num_tokens_since_fired["layers.0"].cpu(), t["num_tokens_since_fired"])
+
+    # checkpoint tree of the reference (trainer.py:648-699)
+    root = tmp_path / "run"
+    for f in ("state.pt", "config.json", "optimizer_0.pt", "lr_scheduler_0.pt", "rank_0_state.pt",
+              "layers.0/sae.safetensors", "layers.0/cfg.json"):
+        assert (root / f).exists(), f
+    assert torch.load(root / "state.pt")["global_step"] == meta["steps"]
+    assert json.load(open(root / "layers.0" / "cfg.json"))["d_in"] == meta["D"]
+
+    # resume: a new trainer picks up step count, optimiser state and weights
+    again = make_trainer(tmp_path, meta, t["acts"], "fp32")
+    again.load_state(str(root))
+    assert again.global_step == meta["steps"]
+    assert torch.equal(again.saes["layers.0"].W_dec, sae.W_dec)
+    st = again.optimizers[0].state_dict()["state"]
+    assert int(st[0]["step"]) == meta["steps"]
+
+
+def test_bf16_trajectory_close_to_fp32(cuda_lib, tmp_path):
+    """FVU over the run in the bf16 configuration stays within 2 % of the fp32 one."""
+    t, meta = load_golden("trainer_adam")
+    runs = {}
+    for prec in ("fp32", "bf16"):
+        tr = make_trainer(tmp_path / prec, meta, t["acts"], prec)
+        tr.fit()
+        runs[prec] = [row["fvu/layers.0"] for row in tr.metrics]
+    for a, b in zip(runs["bf16"], runs["fp32"]):
+        assert abs(a - b) < 0.02 * b, runs
