@@ -7,12 +7,15 @@ __version__ = "0.1.0"
 from .config import SaeConfig, SparseCoderConfig, TrainConfig, TranscoderConfig
 from .fused_encoder import EncoderOutput, FusedEncoder, fused_encoder
 from .sparse_coder import ForwardOutput, Sae, SparseCoder
+from .trainer import SaeTrainer, Trainer
 
 __all__ = [
     "EncoderOutput",
     "ForwardOutput",
     "FusedEncoder",
     "Sae",
+    "SaeTrainer",
+    "Trainer",
     "SaeConfig",
     "SparseCoder",
     "SparseCoderConfig",
