@@ -30,7 +30,7 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kStageBytes = (BM + BN) * BK * 2;  // 48 KiB
 constexpr int kMaxK = 128;
-constexpr int kRowGroup = 32;  // row blocks whose units run together (L2 footprint of x)
+constexpr int kRowGroupDefault = 32;  // row blocks whose units run together (L2 footprint of x)
 
 struct Plan {
   int n_rb;       // row blocks
@@ -53,16 +53,17 @@ struct Params {
   int32_t* status;
   int64_t N, D, M;
   int k, n_rb, n_ct, n_strips, stages, units;
+  int row_group;  // row blocks per scheduling group
   int debug;  // diagnostics: bit 0 = epilogue only drains (no bias / top-k work)
   uint32_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
 
 __device__ __forceinline__ void decode_unit(const Params& p, int u, int& rb, int& strip, int& t0, int& t1) {
-  const int per_group = kRowGroup * p.n_strips;
+  const int per_group = p.row_group * p.n_strips;
   const int g = u / per_group, rem = u % per_group;
-  const int rg = min(kRowGroup, p.n_rb - g * kRowGroup);
+  const int rg = min(p.row_group, p.n_rb - g * p.row_group);
   strip = rem / rg;
-  rb = g * kRowGroup + rem % rg;
+  rb = g * p.row_group + rem % rg;
   t0 = (int)(((int64_t)strip * p.n_ct) / p.n_strips);
   t1 = (int)(((int64_t)(strip + 1) * p.n_ct) / p.n_strips);
 }
@@ -85,52 +86,74 @@ struct RowState {
 
 constexpr int kGroup = 8;
 
+// Minimum of group g (entries g*8 .. g*8+7, those below k) with its position.
+// All eight loads are issued before the first comparison.
 __device__ __forceinline__ void group_min(const float* lv, int k, int g, float& best, int& pos) {
-  best = INFINITY;
-  pos = g * kGroup;
-  const int hi = min(k, (g + 1) * kGroup);
-  for (int j = g * kGroup; j < hi; ++j) {
-    const float x = lv[j * BM];
-    if (x < best) { best = x; pos = j; }
+  float x[kGroup];
+#pragma unroll
+  for (int j = 0; j < kGroup; ++j) {
+    const int e = g * kGroup + j;
+    x[j] = e < k ? lv[e * BM] : INFINITY;
   }
+  best = x[0];
+  pos = g * kGroup;
+#pragma unroll
+  for (int j = 1; j < kGroup; ++j)
+    if (x[j] < best) { best = x[j]; pos = g * kGroup + j; }
 }
 
-__device__ __forceinline__ void global_min(const float* gv, const uint16_t* gp, int groups, RowState& st) {
-  float best = gv[0];
-  int pos = gp[0];
-  for (int g = 1; g < groups; ++g) {
-    const float x = gv[g * BM];
-    if (x < best) { best = x; pos = gp[g * BM]; }
+// The list is full: overwrite its minimum with (v, rel_col), refresh the cached
+// minimum of the touched group and find the new row minimum among the G groups.
+template <int G>
+__device__ __forceinline__ RowState replace_min(float* lv, uint16_t* li, float* gv, uint16_t* gp, int k,
+                                                int groups, float v, uint16_t rel_col, float tau, RowState st) {
+  const int g = st.minpos / kGroup;
+  float gm[G];
+#pragma unroll
+  for (int i = 0; i < G; ++i) gm[i] = i < groups ? gv[i * BM] : INFINITY;  // independent of the rescan
+  lv[st.minpos * BM] = fmaxf(v, 0.f);
+  li[st.minpos * BM] = rel_col;
+  float best; int pos;
+  group_min(lv, k, g, best, pos);
+  gv[g * BM] = best;
+  gp[g * BM] = (uint16_t)pos;
+  float rbest = INFINITY;
+  int rg = 0;
+#pragma unroll
+  for (int i = 0; i < G; ++i) {
+    const float x = (i == g) ? best : gm[i];
+    if (x < rbest) { rbest = x; rg = i; }
   }
-  st.thr = best;
-  st.minpos = pos;
+  st.thr = rbest;
+  st.minpos = (rg == g) ? pos : (int)gp[rg * BM];
+  st.thr_cmp = fmaxf(rbest, tau);
+  return st;
 }
 
 __device__ __noinline__ RowState list_insert(float* lv, uint16_t* li, float* gv, uint16_t* gp, int k, float v,
                                              uint16_t rel_col, float tau, RowState st) {
   const int groups = (k + kGroup - 1) / kGroup;
-  if (st.cnt < k) {  // append
+  if (st.cnt < k) {  // append; on the k-th entry build the group minima
     lv[st.cnt * BM] = fmaxf(v, 0.f);
     li[st.cnt * BM] = rel_col;
     if (++st.cnt < k) return st;
-    for (int g = 0; g < groups; ++g) {  // list just became full: build the group minima
+    float rbest = INFINITY;
+    int rpos = 0;
+    for (int g = 0; g < groups; ++g) {
       float best; int pos;
       group_min(lv, k, g, best, pos);
       gv[g * BM] = best;
       gp[g * BM] = (uint16_t)pos;
+      if (best < rbest) { rbest = best; rpos = pos; }
     }
-  } else {  // replace the minimum
-    lv[st.minpos * BM] = fmaxf(v, 0.f);
-    li[st.minpos * BM] = rel_col;
-    const int g = st.minpos / kGroup;
-    float best; int pos;
-    group_min(lv, k, g, best, pos);
-    gv[g * BM] = best;
-    gp[g * BM] = (uint16_t)pos;
+    st.thr = rbest;
+    st.minpos = rpos;
+    st.thr_cmp = fmaxf(rbest, tau);
+    return st;
   }
-  global_min(gv, gp, groups, st);
-  st.thr_cmp = fmaxf(st.thr, tau);
-  return st;
+  if (groups <= 4) return replace_min<4>(lv, li, gv, gp, k, groups, v, rel_col, tau, st);
+  if (groups <= 8) return replace_min<8>(lv, li, gv, gp, k, groups, v, rel_col, tau, st);
+  return replace_min<16>(lv, li, gv, gp, k, groups, v, rel_col, tau, st);
 }
 
 __global__ void init_tau_kernel(float* tau, int64_t n, int32_t* status) {
@@ -321,7 +344,13 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             if (((colmask >> i) & 1u) == 0) continue;  // warp-uniform skip
             ++n_cols;
             if (((m >> i) & 1u) && v[i] > st.thr_cmp) {
-              st = list_insert(lv, li, gv, gp, k, v[i], (uint16_t)(rel0 + i), tau, st);
+              if (st.cnt + 1 < k) {  // free slots left: append in line
+                lv[st.cnt * BM] = fmaxf(v[i], 0.f);
+                li[st.cnt * BM] = (uint16_t)(rel0 + i);
+                ++st.cnt;
+              } else {
+                st = list_insert(lv, li, gv, gp, k, v[i], (uint16_t)(rel0 + i), tau, st);
+              }
               ++n_ins;
             }
           }
@@ -503,6 +532,8 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   p.N = N; p.D = D; p.M = M; p.k = k;
   const char* dbg = getenv("SC_ENCODE_DEBUG");
   p.debug = dbg ? atoi(dbg) : 0;
+  const char* rg_env = getenv("SC_ENCODE_ROWGROUP");
+  p.row_group = rg_env && atoi(rg_env) > 0 ? atoi(rg_env) : kRowGroupDefault;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
   p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
   p.off_gmin = (uint32_t)pl.off_gmin; p.off_gpos = (uint32_t)pl.off_gpos;
