@@ -172,7 +172,7 @@ def run_reference(a):
 
 # --------------------------------------------------------------------------- GPU arm
 LAUNCHES_PER_CALL = {  # kernels each C-ABI entry point enqueues
-    "sc_encode_topk": 3, "sc_csr_build": 4, "sc_total_variance": 4, "sc_sq_err": 2,
+    "sc_encode_topk": 3, "sc_csr_build": 4, "sc_total_variance": 4, "sc_sq_err": 2, "sc_weighted_colsum": 2,
 }
 
 
@@ -214,6 +214,8 @@ def run_ours(a):
     lr = 2e-4 / (M / 2 ** 14) ** 0.5
     opt = FusedAdam(sae.parameters(), lr=lr)
     sae.attach_optimizer(opt)
+    if world == 1:
+        opt.enable_sparse_update(sae)  # single process: gradients go to the optimiser in sparse form
     alpha = 1 / 32
     since_fired = torch.zeros(M, dtype=torch.long, device=dev)
     dead_threshold = 10_000_000

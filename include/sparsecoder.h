@@ -151,6 +151,11 @@ int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries, int k,
                        float* gbiasB, int64_t M, int64_t D, int64_t lat_begin,
                        int64_t lat_end, void* stream);
 
+/* out[m] = sum of coef[e] over the CSR entries of latent m (the bias gradient
+ * of sparsify/fused_encoder.py:79-84 on its own). */
+int sc_csr_segment_sum(const int32_t* row_ptr, const int32_t* entries,
+                       const float* coef, int64_t M, float* out, void* stream);
+
 /* ---- losses -------------------------------------------------------------
  * sparsify/sparse_coder.py:225-228,253-254:
  *   total_variance = sum((y - mean_0(y))^2);  e = y - out;  l2 = sum(e^2).
@@ -189,6 +194,32 @@ int sc_normalize_rows(float* W, int64_t M, int64_t D, float eps,
 int sc_adam_rows(float* p, float* g, float* m, float* v, int64_t M, int64_t D,
                  float lr, float beta1, float beta2, float eps, int64_t step,
                  int project, void* shadow_bf16, void* stream);
+
+/* Host-side Adam hyper-parameters of one parameter (torch.optim.Adam names);
+ * step is the 1-based step count. */
+typedef struct sc_adam_hparams {
+  float lr, beta1, beta2, eps;
+  int64_t step;
+} sc_adam_hparams;
+
+/* Sparse weight gradients and the optimiser step in one pass over the latents:
+ * per latent m the CSR segment is walked as in sc_rows_accumulate
+ * (A = decoder: coefA * vecA rows, B = encoder: coefB * vecB rows) and the two
+ * gradient rows, held in registers, go straight into
+ *   B: Adam on pB[m,:] (sparsify/trainer.py:517-519), bf16 shadow refresh;
+ *   A: optional projection (sparsify/sparse_coder.py:281-295), Adam, optional
+ *      row normalisation W /= ||W|| + norm_eps (sparse_coder.py:273-279, which
+ *      the reference applies before the next forward), bf16 shadow refresh.
+ * The dense [M,D] gradients are never materialised. D % 4 == 0, D <= 4096.
+ * hpA / hpB are host pointers. shadow pointers may be NULL. */
+int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
+                 const float* coefA, const void* vecA, int vecA_dtype,
+                 const float* coefB, const void* vecB, int vecB_dtype,
+                 int64_t M, int64_t D, float* pA, float* mA, float* vA,
+                 void* shadowA_bf16, int projectA, int normalizeA,
+                 float norm_eps, const sc_adam_hparams* hpA, float* pB,
+                 float* mB, float* vB, void* shadowB_bf16,
+                 const sc_adam_hparams* hpB, void* stream);
 
 /* fp32 -> bf16 copy (shadow refresh). */
 int sc_cast_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);

@@ -59,7 +59,19 @@ SIGNATURES: dict[str, tuple] = {
         [P, P, P, P, I64, I64, c_float, c_float, c_float, c_float, I64, c_int, P, P],
     ),
     "sc_cast_bf16": (c_int, [P, P, I64, P]),
+    "sc_csr_segment_sum": (c_int, [P, P, P, I64, P, P]),
+    "sc_rows_adam": (
+        c_int,
+        [P, P, c_int, P, P, c_int, P, P, c_int, I64, I64, P, P, P, P, c_int, c_int, c_float, P,
+         P, P, P, P, P, P],
+    ),
 }
+
+class AdamHparams(ctypes.Structure):
+    """Mirror of sc_adam_hparams."""
+    _fields_ = [("lr", c_float), ("beta1", c_float), ("beta2", c_float), ("eps", c_float),
+                ("step", c_int64)]
+
 
 _lib = None
 

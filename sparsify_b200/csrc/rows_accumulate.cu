@@ -82,6 +82,17 @@ rows_accumulate_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __res
   }
 }
 
+// out[m] = sum of coef[e] over the CSR entries e of latent m
+__global__ void __launch_bounds__(256)
+segment_sum_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ entries,
+                   const float* __restrict__ coef, int64_t M, float* __restrict__ out) {
+  const int64_t m = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float s = 0.f;
+  for (int32_t p = row_ptr[m]; p < row_ptr[m + 1]; ++p) s += coef[entries[p]];
+  out[m] = s;
+}
+
 template <typename TA, typename TB>
 int launch(const int32_t* row_ptr, const int32_t* entries, int k, const float* coefA,
            const void* vecA, float* gradA, float* gbiasA, const float* coefB, const void* vecB,
@@ -135,4 +146,13 @@ extern "C" int sc_rows_accumulate(const int32_t* row_ptr, const int32_t* entries
   if (vecA_dtype == SC_BF16 && vecB_dtype == SC_F32)
     return launch<bf16, float>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
   return launch<bf16, bf16>(row_ptr, entries, k, coefA, vecA, gradA, gbiasA, coefB, vecB, gradB, gbiasB, D, lat_begin, nlat, st);
+}
+
+extern "C" int sc_csr_segment_sum(const int32_t* row_ptr, const int32_t* entries, const float* coef,
+                                  int64_t M, float* out, void* stream) {
+  SC_REQUIRE(M > 0, "sc_csr_segment_sum: bad shape");
+  SC_REQUIRE(row_ptr && entries && coef && out, "sc_csr_segment_sum: null pointer");
+  segment_sum_kernel<<<(unsigned)((M + 255) / 256), 256, 0, sc::as_stream(stream)>>>(row_ptr, entries, coef, M, out);
+  SC_CHECK_LAUNCH("sc_csr_segment_sum");
+  return SC_OK;
 }

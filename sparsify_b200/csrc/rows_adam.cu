@@ -1,0 +1,198 @@
+// Sparse weight gradients and the optimiser step in one pass.
+//
+// One CTA per latent m. It walks the latent's CSR segment like
+// rows_accumulate, but keeps both gradient rows (decoder: sum acts * grad_out,
+// encoder: sum grad_acts * x') in registers and applies them at once:
+//   encoder row: Adam, bf16 shadow refresh;
+//   decoder row: removal of the gradient component parallel to the row, Adam,
+//                row normalisation for the next forward, bf16 shadow refresh.
+// The two [M,D] gradients are therefore never written to or read from HBM, and
+// the separate projection and normalisation passes disappear. Valid when no
+// other consumer needs the dense gradients (single process, no accumulation).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kNV = 4;  // float4 groups per thread: rows of up to 4096 floats
+
+struct Hp {
+  float lr, beta1, beta2, eps, bc1, bc2_sqrt;
+};
+
+__device__ __forceinline__ float adam1(float p, float g, float& m, float& v, const Hp& a) {
+  m = m + (g - m) * (1.f - a.beta1);
+  v = v * a.beta2 + (1.f - a.beta2) * g * g;
+  const float denom = sqrtf(v) / a.bc2_sqrt + a.eps;
+  return p - (a.lr / a.bc1) * (m / denom);
+}
+
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, float4 v) {
+  uint2 packed;
+  packed.x = sc::pack_bf16x2(v.x, v.y);
+  packed.y = sc::pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+struct Args {
+  const int32_t* row_ptr;
+  const int32_t* entries;
+  const float* coefA;
+  const float* coefB;
+  float *pA, *mA, *vA, *pB, *mB, *vB;
+  __nv_bfloat16 *shadowA, *shadowB;
+  int64_t D;
+  int k;
+  int projectA, normalizeA;
+  float norm_eps;
+  Hp hpA, hpB;
+};
+
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(kThreads)
+rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const Args a) {
+  __shared__ float scratch[33];
+  const int64_t m = blockIdx.x;
+  const int64_t D = a.D;
+  const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
+  const int64_t off = m * D;
+
+  float4 gA[kNV], gB[kNV];
+  int64_t col[kNV];
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) {
+    gA[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    gB[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    col[c] = ((int64_t)c * kThreads + threadIdx.x) * 4;
+  }
+#pragma unroll 2
+  for (int32_t p = lo; p < hi; ++p) {
+    const int32_t e = a.entries[p];
+    const int64_t n = e / a.k;
+    const float ca = a.coefA[e], cb = a.coefB[e];
+    const TA* ra = vecA + n * D;
+    const TB* rb = vecB + n * D;
+#pragma unroll
+    for (int c = 0; c < kNV; ++c) {
+      if (col[c] < D) {
+        const float4 x = sc::load4<TA>(ra + col[c]);
+        const float4 y = sc::load4<TB>(rb + col[c]);
+        gA[c].x = fmaf(ca, x.x, gA[c].x); gA[c].y = fmaf(ca, x.y, gA[c].y);
+        gA[c].z = fmaf(ca, x.z, gA[c].z); gA[c].w = fmaf(ca, x.w, gA[c].w);
+        gB[c].x = fmaf(cb, y.x, gB[c].x); gB[c].y = fmaf(cb, y.y, gB[c].y);
+        gB[c].z = fmaf(cb, y.z, gB[c].z); gB[c].w = fmaf(cb, y.w, gB[c].w);
+      }
+    }
+  }
+
+  // ---- encoder row: Adam ----
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) {
+    if (col[c] < D) {
+      float4 pw = *reinterpret_cast<const float4*>(a.pB + off + col[c]);
+      float4 mw = *reinterpret_cast<const float4*>(a.mB + off + col[c]);
+      float4 vw = *reinterpret_cast<const float4*>(a.vB + off + col[c]);
+      pw.x = adam1(pw.x, gB[c].x, mw.x, vw.x, a.hpB);
+      pw.y = adam1(pw.y, gB[c].y, mw.y, vw.y, a.hpB);
+      pw.z = adam1(pw.z, gB[c].z, mw.z, vw.z, a.hpB);
+      pw.w = adam1(pw.w, gB[c].w, mw.w, vw.w, a.hpB);
+      *reinterpret_cast<float4*>(a.pB + off + col[c]) = pw;
+      *reinterpret_cast<float4*>(a.mB + off + col[c]) = mw;
+      *reinterpret_cast<float4*>(a.vB + off + col[c]) = vw;
+      if (a.shadowB != nullptr) store_bf16x4(a.shadowB + off + col[c], pw);
+    }
+  }
+
+  // ---- decoder row: project, Adam, normalise ----
+  float4 pw[kNV];
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) {
+    if (col[c] < D) {
+      pw[c] = *reinterpret_cast<const float4*>(a.pA + off + col[c]);
+      dot += gA[c].x * pw[c].x + gA[c].y * pw[c].y + gA[c].z * pw[c].z + gA[c].w * pw[c].w;
+    }
+  }
+  if (a.projectA) dot = sc::block_sum(dot, scratch);
+  else dot = 0.f;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) {
+    if (col[c] < D) {
+      float4 mw = *reinterpret_cast<const float4*>(a.mA + off + col[c]);
+      float4 vw = *reinterpret_cast<const float4*>(a.vA + off + col[c]);
+      const float4 g = make_float4(gA[c].x - dot * pw[c].x, gA[c].y - dot * pw[c].y,
+                                   gA[c].z - dot * pw[c].z, gA[c].w - dot * pw[c].w);
+      pw[c].x = adam1(pw[c].x, g.x, mw.x, vw.x, a.hpA);
+      pw[c].y = adam1(pw[c].y, g.y, mw.y, vw.y, a.hpA);
+      pw[c].z = adam1(pw[c].z, g.z, mw.z, vw.z, a.hpA);
+      pw[c].w = adam1(pw[c].w, g.w, mw.w, vw.w, a.hpA);
+      *reinterpret_cast<float4*>(a.mA + off + col[c]) = mw;
+      *reinterpret_cast<float4*>(a.vA + off + col[c]) = vw;
+      ss += pw[c].x * pw[c].x + pw[c].y * pw[c].y + pw[c].z * pw[c].z + pw[c].w * pw[c].w;
+    }
+  }
+  if (a.normalizeA) ss = sc::block_sum(ss, scratch);
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) {
+    if (col[c] < D) {
+      float4 o = pw[c];
+      if (a.normalizeA) {
+        const float denom = sqrtf(ss) + a.norm_eps;  // same division as sc_normalize_rows
+        o = make_float4(o.x / denom, o.y / denom, o.z / denom, o.w / denom);
+      }
+      *reinterpret_cast<float4*>(a.pA + off + col[c]) = o;
+      if (a.shadowA != nullptr) store_bf16x4(a.shadowA + off + col[c], o);
+    }
+  }
+}
+
+Hp make_hp(const sc_adam_hparams* h) {
+  Hp o;
+  o.lr = h->lr; o.beta1 = h->beta1; o.beta2 = h->beta2; o.eps = h->eps;
+  o.bc1 = (float)(1.0 - pow((double)h->beta1, (double)h->step));
+  o.bc2_sqrt = (float)sqrt(1.0 - pow((double)h->beta2, (double)h->step));
+  return o;
+}
+
+}  // namespace
+
+extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k, const float* coefA,
+                            const void* vecA, int vecA_dtype, const float* coefB, const void* vecB,
+                            int vecB_dtype, int64_t M, int64_t D, float* pA, float* mA, float* vA,
+                            void* shadowA_bf16, int projectA, int normalizeA, float norm_eps,
+                            const sc_adam_hparams* hpA, float* pB, float* mB, float* vB,
+                            void* shadowB_bf16, const sc_adam_hparams* hpB, void* stream) {
+  SC_REQUIRE(M > 0 && D > 0 && k > 0 && M <= 0x7fffffffLL, "sc_rows_adam: bad shape");
+  SC_REQUIRE(row_ptr && entries && coefA && vecA && coefB && vecB && pA && mA && vA && pB && mB && vB && hpA && hpB,
+             "sc_rows_adam: null pointer");
+  SC_REQUIRE(sc::valid_dtype(vecA_dtype) && sc::valid_dtype(vecB_dtype), "sc_rows_adam: bad dtype");
+  SC_REQUIRE(hpA->step >= 1 && hpB->step >= 1, "sc_rows_adam: step counts from 1");
+  if (D % 4 != 0 || D > (int64_t)kThreads * 4 * kNV)
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_rows_adam: D=%lld must be a multiple of 4 and at most %d",
+                    (long long)D, kThreads * 4 * kNV);
+  const void* ptrs[] = {vecA, vecB, pA, mA, vA, pB, mB, vB};
+  for (const void* q : ptrs) SC_REQUIRE(sc::aligned(q, 16), "sc_rows_adam: pointers must be 16-byte aligned");
+  Args a;
+  a.row_ptr = row_ptr; a.entries = entries; a.coefA = coefA; a.coefB = coefB;
+  a.pA = pA; a.mA = mA; a.vA = vA; a.pB = pB; a.mB = mB; a.vB = vB;
+  a.shadowA = static_cast<__nv_bfloat16*>(shadowA_bf16);
+  a.shadowB = static_cast<__nv_bfloat16*>(shadowB_bf16);
+  a.D = D; a.k = k; a.projectA = projectA; a.normalizeA = normalizeA; a.norm_eps = norm_eps;
+  a.hpA = make_hp(hpA); a.hpB = make_hp(hpB);
+  cudaStream_t st = sc::as_stream(stream);
+  dim3 grid((unsigned)M), block(kThreads);
+  using bf16 = __nv_bfloat16;
+  if (vecA_dtype == SC_F32 && vecB_dtype == SC_F32)
+    rows_adam_kernel<float, float><<<grid, block, 0, st>>>((const float*)vecA, (const float*)vecB, a);
+  else if (vecA_dtype == SC_F32)
+    rows_adam_kernel<float, bf16><<<grid, block, 0, st>>>((const float*)vecA, (const bf16*)vecB, a);
+  else if (vecB_dtype == SC_F32)
+    rows_adam_kernel<bf16, float><<<grid, block, 0, st>>>((const bf16*)vecA, (const float*)vecB, a);
+  else
+    rows_adam_kernel<bf16, bf16><<<grid, block, 0, st>>>((const bf16*)vecA, (const bf16*)vecB, a);
+  SC_CHECK_LAUNCH("sc_rows_adam");
+  return SC_OK;
+}

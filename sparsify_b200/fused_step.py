@@ -13,6 +13,10 @@ Multi-TopK, inputs that need no gradient - in fewer passes over memory:
   coefficients instead of being applied to an [N,D] tensor;
 * the CSR of the selected latents is built once and one pass produces the
   gradients of W_dec, W_enc and b_enc;
+* when the optimiser is a FusedAdam that registered this coder
+  (`defer_weight_update`), the weight gradients are handed over in sparse form
+  and applied by one kernel that also projects, normalises and refreshes the
+  bf16 copies, so the dense [M, D] gradients never exist;
 * the encoder's input gradient is never gathered: its column sum, which is all
   that b_dec needs, equals W_enc^T grad_b_enc.
 """
@@ -55,6 +59,7 @@ class FusedSaeStep(torch.autograd.Function):
         ctx.w_enc_src, ctx.w_dec_src = w_enc_src, w_dec_src
         ctx.shape = (M, D, k)
         ctx.transcode = cfg.transcode
+        ctx.sae = sae
         ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(idx)
         return out, acts, idx, fvu
@@ -76,9 +81,20 @@ class FusedSaeStep(torch.autograd.Function):
         if g_acts is not None:
             gacts = gacts + g_acts
         row_ptr, entries = ops.csr_build(idx, M)
-        res = ops.rows_accumulate(row_ptr, entries, k, M, D, acts * scale, gout,
-                                  coefB=gacts, vecB=xe, biasB=True)
-        g_W_dec, g_W_enc, g_b_enc = res["gradA"], res["gradB"], res["gbiasB"]
+        sae = ctx.sae
+        if sae._pending is not None:
+            sae.materialize_pending()  # a second backward before the optimiser step: go dense
+        if sae.defer_weight_update and ctx.needs_input_grad[2] and ctx.needs_input_grad[4]:
+            # The optimiser consumes the sparse form directly (sc_rows_adam): keep the
+            # CSR and the coefficient / row tensors instead of two dense [M, D] gradients.
+            sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, coefA=acts * scale, vecA=gout,
+                                coefB=gacts, vecB=xe)
+            g_W_dec = g_W_enc = None
+            g_b_enc = ops.csr_segment_sum(row_ptr, entries, gacts, M)
+        else:
+            res = ops.rows_accumulate(row_ptr, entries, k, M, D, acts * scale, gout,
+                                      coefB=gacts, vecB=xe, biasB=True)
+            g_W_dec, g_W_enc, g_b_enc = res["gradA"], res["gradB"], res["gbiasB"]
         g_b_dec = ops.weighted_colsum(gout) * scale
         if not ctx.transcode:
             # minus the column sum of the encoder's input gradient

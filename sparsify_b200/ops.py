@@ -220,6 +220,39 @@ def rows_accumulate(
     return out
 
 
+def csr_segment_sum(row_ptr: Tensor, entries: Tensor, coef: Tensor, M: int) -> Tensor:
+    """out[m] = sum of coef over the CSR entries of latent m."""
+    _check_cuda(row_ptr, entries, coef)
+    coef = _f32(coef).reshape(-1)
+    out = torch.empty(M, dtype=torch.float32, device=coef.device)
+    with torch.cuda.device(coef.device):
+        call("sc_csr_segment_sum", ptr(row_ptr), ptr(entries), ptr(coef), int(M), ptr(out), _stream(coef))
+    return out
+
+
+def rows_adam_(row_ptr: Tensor, entries: Tensor, k: int, coefA: Tensor, vecA: Tensor, coefB: Tensor,
+               vecB: Tensor, *, pA: Tensor, mA: Tensor, vA: Tensor, shadowA: Tensor | None, projectA: bool,
+               normalizeA: bool, norm_eps: float, hpA: dict, pB: Tensor, mB: Tensor, vB: Tensor,
+               shadowB: Tensor | None, hpB: dict) -> None:
+    """Sparse gradients of the decoder (A) and encoder (B) applied straight to the
+    parameters: projection, Adam, decoder normalisation and bf16 shadows in one pass.
+    hpA / hpB: dict(lr, beta1, beta2, eps, step)."""
+    import ctypes
+    _check_cuda(row_ptr, entries, coefA, vecA, coefB, vecB, pA, mA, vA, pB, mB, vB, shadowA, shadowB)
+    M, D = pA.shape
+    coefA, coefB = _f32(coefA).reshape(-1), _f32(coefB).reshape(-1)
+    vecA, vecB = vecA.detach().contiguous(), vecB.detach().contiguous()
+    for t in (pA, mA, vA, pB, mB, vB):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    ha = _lib.AdamHparams(hpA["lr"], hpA["beta1"], hpA["beta2"], hpA["eps"], hpA["step"])
+    hb = _lib.AdamHparams(hpB["lr"], hpB["beta1"], hpB["beta2"], hpB["eps"], hpB["step"])
+    with torch.cuda.device(pA.device):
+        call("sc_rows_adam", ptr(row_ptr), ptr(entries), int(k), ptr(coefA), ptr(vecA), dtype_code(vecA),
+             ptr(coefB), ptr(vecB), dtype_code(vecB), int(M), int(D), ptr(pA), ptr(mA), ptr(vA), ptr(shadowA),
+             int(bool(projectA)), int(bool(normalizeA)), float(norm_eps), ctypes.byref(ha), ptr(pB), ptr(mB),
+             ptr(vB), ptr(shadowB), ctypes.byref(hb), _stream(pA))
+
+
 def total_variance(y: Tensor) -> Tensor:
     """sum((y - y.mean(0))**2) as a 0-d fp32 device tensor."""
     _check_cuda(y)

@@ -81,6 +81,9 @@ class SparseCoder(nn.Module):
         self.num_latents = cfg.num_latents or d_in * cfg.expansion_factor
         self.precision = type(self).default_precision
         self.fused = True  # use the single-function training path when it applies
+        self.defer_weight_update = False  # set by FusedAdam.enable_sparse_update
+        self._pending: dict | None = None  # weight gradients in sparse form, awaiting the optimiser
+        self._dec_unit_norm: tuple | None = None  # (data_ptr, version) at which W_dec rows had unit norm
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 
         self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
@@ -282,6 +285,8 @@ class SparseCoder(nn.Module):
         assert self.W_dec is not None, "Decoder weight was not initialized."
         eps = torch.finfo(self.W_dec.dtype).eps
         W = self.W_dec.data
+        if self._dec_unit_norm == (W.data_ptr(), self.W_dec._version):
+            return  # the last fused update already left the rows at unit norm
         if W.is_cuda and W.dtype == torch.float32 and W.is_contiguous():
             # the kernel writes through raw pointers (no version bump): refresh the
             # cached bf16 copy in the same pass, or drop it
@@ -294,6 +299,18 @@ class SparseCoder(nn.Module):
             # construction / checkpoint handling on the host before .to("cuda")
             norm = torch.norm(W, dim=1, keepdim=True)
             self.W_dec.data /= norm + eps
+
+    def materialize_pending(self) -> None:
+        """Turns a deferred sparse weight gradient into dense .grad tensors
+        (accumulating), for consumers that need them."""
+        pend, self._pending = self._pending, None
+        if pend is None:
+            return
+        M, D = self.encoder.weight.shape
+        res = ops.rows_accumulate(pend["row_ptr"], pend["entries"], pend["k"], M, D, pend["coefA"],
+                                  pend["vecA"], coefB=pend["coefB"], vecB=pend["vecB"])
+        for p, g in ((self.W_dec, res["gradA"]), (self.encoder.weight, res["gradB"])):
+            p.grad = g if p.grad is None else p.grad + g
 
     def attach_optimizer(self, opt) -> None:
         """Lets a FusedAdam keep the bf16 copies current inside its update kernel

@@ -102,8 +102,12 @@ class Trainer:
                        for sae in self.saes.values()]
                 lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
                 adam = FusedAdam(pgs)
+                single = not dist.is_initialized() and cfg.grad_acc_steps * cfg.micro_acc_steps == 1
                 for sae in self.saes.values():
                     sae.attach_optimizer(adam)
+                    if single:
+                        # nothing but the optimiser needs the dense weight gradients
+                        adam.enable_sparse_update(sae)
                 self.optimizers = [adam]
                 self.lr_schedulers = [linear_schedule_with_warmup(adam, cfg.lr_warmup_steps, num_batches)]
             case "muon":

@@ -136,3 +136,41 @@ def test_cpu_tensors_are_rejected():
     from sparsify_b200 import ops
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.embedding_bag_fwd(torch.zeros(2, 2, dtype=torch.long), torch.zeros(2, 2), torch.zeros(4, 4))
+
+
+def test_sparse_fused_update_matches_dense_path(cuda_lib):
+    """sc_rows_adam (gradients applied in sparse form: projection, Adam, decoder
+    normalisation, bf16 copies in one kernel) against the separate kernels."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    from sparsify_b200.optim import FusedAdam
+    N, D, M, k = 1024, 256, 4096, 32
+    g = torch.Generator().manual_seed(21)
+    xs = [torch.randn(N, D, generator=g).cuda() for _ in range(3)]
+    models = []
+    for sparse in (False, True):
+        torch.manual_seed(0)
+        sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+        opt = FusedAdam(sae.parameters(), lr=1e-3)
+        sae.attach_optimizer(opt)
+        if sparse:
+            assert opt.enable_sparse_update(sae)
+        for x in xs:
+            sae.set_decoder_norm_to_unit_norm()
+            out = sae(x)
+            out.fvu.backward()
+            if sparse:
+                assert sae.W_dec.grad is None and sae._pending is not None
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        sae.set_decoder_norm_to_unit_norm()
+        models.append((sae, opt))
+    (a, oa), (b, ob) = models
+    for (n1, p1), (_, p2) in zip(a.named_parameters(), b.named_parameters()):
+        assert rel_l2(p2.detach(), p1.detach()) < 1e-5, n1
+    for name in ("encoder.weight", "W_dec"):
+        assert torch.equal(b.shadow(name), dict(b.named_parameters())[name].detach().bfloat16()), name
+    sa, sb = oa.state[a.W_dec], ob.state[b.W_dec]
+    assert int(sa["step"]) == int(sb["step"]) == 3
+    assert rel_l2(sb["exp_avg"], sa["exp_avg"]) < 1e-5 and rel_l2(sb["exp_avg_sq"], sa["exp_avg_sq"]) < 1e-4
+    norms = b.W_dec.detach().norm(dim=1)
+    assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5)
