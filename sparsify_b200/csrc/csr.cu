@@ -21,45 +21,106 @@ __global__ void csr_count_kernel(const int64_t* __restrict__ idx, int64_t total,
   }
 }
 
-// Exclusive scan of counts[0..M) into row_ptr[0..M]; also seeds cursor = row_ptr.
-// One CTA; each thread owns a contiguous slice.
+// Exclusive scan of counts[0..M) into row_ptr[0..M] (also seeds cursor = row_ptr)
+// in three small launches: per-tile sums, a scan of the tile sums by one CTA,
+// and the per-tile scans with their offsets.
+constexpr int kScanTile = 1024;  // elements per CTA (256 threads x 4)
+
+__global__ void __launch_bounds__(256)
+scan_tile_sums_kernel(const int32_t* __restrict__ counts, int64_t M, int32_t* __restrict__ tile_sums) {
+  __shared__ int32_t s_warp[8];
+  const int64_t base = (int64_t)blockIdx.x * kScanTile + threadIdx.x * 4;
+  int32_t v = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v += base + i < M ? counts[base + i] : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t t = 0;
+    for (int w = 0; w < 8; ++w) t += s_warp[w];
+    tile_sums[blockIdx.x] = t;
+  }
+}
+
+// In-place exclusive scan of tile_sums[0..n) by one CTA; writes the total to *total.
 __global__ void __launch_bounds__(1024)
-csr_scan_kernel(const int32_t* __restrict__ counts, int64_t M, int32_t* __restrict__ row_ptr,
-                int32_t* __restrict__ cursor) {
+scan_tile_offsets_kernel(int32_t* __restrict__ tile_sums, int n, int32_t* __restrict__ total) {
   __shared__ int32_t s_warp[32];
-  const int t = threadIdx.x;
-  const int64_t per = (M + blockDim.x - 1) / blockDim.x;
-  const int64_t lo = (int64_t)t * per;
-  const int64_t hi = lo + per < M ? lo + per : M;
-  int32_t local = 0;
-  for (int64_t i = lo; i < hi; ++i) local += counts[i];
-  // inclusive scan of `local` over the block
-  int32_t incl = local;
-  const int lane = t & 31, warp = t >> 5;
+  __shared__ int32_t s_carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int32_t v = i < n ? tile_sums[i] : 0;
+    int32_t incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int32_t w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int32_t carry = s_carry;
+    const int32_t excl = carry + incl - v + (warp > 0 ? s_warp[warp - 1] : 0);
+    if (i < n) tile_sums[i] = excl;
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = carry + s_warp[31];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *total = s_carry;
+}
+
+__global__ void __launch_bounds__(256)
+scan_tiles_kernel(const int32_t* __restrict__ counts, int64_t M, const int32_t* __restrict__ tile_offsets,
+                  int32_t* __restrict__ row_ptr, int32_t* __restrict__ cursor) {
+  __shared__ int32_t s_warp[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t base = (int64_t)blockIdx.x * kScanTile + threadIdx.x * 4;
+  int32_t c[4];
+  int32_t v = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { c[i] = base + i < M ? counts[base + i] : 0; v += c[i]; }
+  int32_t incl = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    int32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+    const int32_t y = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += y;
   }
   if (lane == 31) s_warp[warp] = incl;
   __syncthreads();
-  if (warp == 0) {
-    int32_t w = s_warp[lane];
+  int32_t before = tile_offsets[blockIdx.x] + incl - v;
+  for (int w = 0; w < warp; ++w) before += s_warp[w];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int32_t y = __shfl_up_sync(0xffffffffu, w, o);
-      if (lane >= o) w += y;
-    }
-    s_warp[lane] = w;
+  for (int i = 0; i < 4; ++i) {
+    if (base + i < M) { row_ptr[base + i] = before; cursor[base + i] = before; }
+    before += c[i];
   }
-  __syncthreads();
-  int32_t run = incl - local + (warp > 0 ? s_warp[warp - 1] : 0);
-  for (int64_t i = lo; i < hi; ++i) {
-    row_ptr[i] = run;
-    cursor[i] = run;
-    run += counts[i];
-  }
-  if (t == blockDim.x - 1) row_ptr[M] = s_warp[31];
+}
+
+// counts -> row_ptr[0..M], cursor[0..M); tile_sums holds ceil(M / kScanTile) ints.
+int launch_scan(const int32_t* counts, int64_t M, int32_t* row_ptr, int32_t* cursor, int32_t* tile_sums,
+                cudaStream_t st) {
+  const int tiles = (int)((M + kScanTile - 1) / kScanTile);
+  scan_tile_sums_kernel<<<tiles, 256, 0, st>>>(counts, M, tile_sums);
+  SC_CHECK_LAUNCH("scan_tile_sums");
+  scan_tile_offsets_kernel<<<1, 1024, 0, st>>>(tile_sums, tiles, row_ptr + M);
+  SC_CHECK_LAUNCH("scan_tile_offsets");
+  scan_tiles_kernel<<<tiles, 256, 0, st>>>(counts, M, tile_sums, row_ptr, cursor);
+  SC_CHECK_LAUNCH("scan_tiles");
+  return SC_OK;
 }
 
 __global__ void csr_fill_kernel(const int64_t* __restrict__ idx, int64_t total, int64_t M,
@@ -123,9 +184,10 @@ csr_sort_kernel(const int32_t* __restrict__ row_ptr, int64_t M, int32_t* __restr
 
 extern "C" size_t sc_csr_workspace_bytes(int64_t M) {
   if (M < 0) return 0;
-  // counts[M] + cursor[M], each padded to 256 bytes
+  // counts[M] + cursor[M] + tile sums of the scan, each padded to 256 bytes
   size_t one = (((size_t)M * sizeof(int32_t)) + 255) & ~size_t(255);
-  return 2 * one;
+  size_t tiles = ((((size_t)M + kScanTile - 1) / kScanTile) * sizeof(int32_t) + 255) & ~size_t(255);
+  return 2 * one + tiles;
 }
 
 extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int32_t* row_ptr,
@@ -142,6 +204,7 @@ extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int
   const size_t one = (((size_t)M * sizeof(int32_t)) + 255) & ~size_t(255);
   int32_t* counts = static_cast<int32_t*>(ws);
   int32_t* cursor = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + one);
+  int32_t* tile_sums = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + 2 * one);
   const int64_t total = N * k;
   SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
   if (total > 0) {
@@ -150,16 +213,16 @@ extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int
     if (blocks > 148 * 16) blocks = 148 * 16;
     csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
     SC_CHECK_LAUNCH("csr_count");
-    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
-    SC_CHECK_LAUNCH("csr_scan");
+    int rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+    if (rc != SC_OK) return rc;
     csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
     SC_CHECK_LAUNCH("csr_fill");
     csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(
         row_ptr, M, entries);
     SC_CHECK_LAUNCH("csr_sort");
   } else {
-    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
-    SC_CHECK_LAUNCH("csr_scan");
+    int rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+    if (rc != SC_OK) return rc;
   }
   return SC_OK;
 }
@@ -171,7 +234,7 @@ extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int
 namespace {
 
 constexpr int64_t kNoAllocMaxLatents = 262144;  // 2 x 1 MiB of counters
-static __device__ __align__(256) unsigned char g_csr_scratch[2 * kNoAllocMaxLatents * sizeof(int32_t)];
+static __device__ __align__(256) unsigned char g_csr_scratch[(2 * kNoAllocMaxLatents + kNoAllocMaxLatents / kScanTile) * sizeof(int32_t)];
 
 constexpr int kMaxDevices = 64;
 std::mutex g_scratch_mutex;
@@ -212,6 +275,7 @@ extern "C" int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_
   cudaStream_t st = sc::as_stream(stream);
   int32_t* counts = static_cast<int32_t*>(scratch);
   int32_t* cursor = counts + kNoAllocMaxLatents;
+  int32_t* tile_sums = cursor + kNoAllocMaxLatents;
   const int64_t total = N * k;
   // the array keeps whatever the previous call left: the histogram must start at zero
   SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
@@ -221,15 +285,15 @@ extern "C" int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_
     if (blocks > 148 * 16) blocks = 148 * 16;
     csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
     SC_CHECK_LAUNCH("csr_count");
-    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
-    SC_CHECK_LAUNCH("csr_scan");
+    rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+    if (rc != SC_OK) return rc;
     csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
     SC_CHECK_LAUNCH("csr_fill");
     csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(row_ptr, M, entries);
     SC_CHECK_LAUNCH("csr_sort");
   } else {
-    csr_scan_kernel<<<1, 1024, 0, st>>>(counts, M, row_ptr, cursor);
-    SC_CHECK_LAUNCH("csr_scan");
+    rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+    if (rc != SC_OK) return rc;
   }
   return SC_OK;
 }

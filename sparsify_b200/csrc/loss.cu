@@ -8,30 +8,56 @@ namespace {
 constexpr int kSlices = 64;       // row slices for the column sums
 constexpr int kRedBlocks = 1024;  // partial sums of the flat reductions
 
-// partial[s][d] = sum of w[n] * y[n][d] over the rows n of slice s (w == NULL: 1)
-template <typename T>
+// partial[s][d] = sum of w[n] * y[n][d] over the rows n of slice s (w == NULL: 1).
+// VEC = 4: each lane owns four consecutive columns (8/16-byte loads); VEC = 1
+// serves widths that are not a multiple of four.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const T* __restrict__ y, const float* __restrict__ w, int64_t N, int64_t D,
                       float* __restrict__ partial) {
-  __shared__ float s_acc[8][33];
+  __shared__ float s_acc[8][32 * VEC + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t d = (int64_t)blockIdx.x * 32 + lane;
+  const int64_t d = ((int64_t)blockIdx.x * 32 + lane) * VEC;
   const int64_t per = (N + kSlices - 1) / kSlices;
   const int64_t r0 = (int64_t)blockIdx.y * per;
   const int64_t r1 = r0 + per < N ? r0 + per : N;
-  float acc = 0.f;
-  if (d < D)
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  if (d < D) {
+#pragma unroll 4
     for (int64_t r = r0 + warp; r < r1; r += 8) {
       const float wr = w != nullptr ? __ldg(w + r) : 1.f;
-      if (wr != 0.f) acc = fmaf(wr, sc::load1<T>(y + r * D + d), acc);
+      if (wr == 0.f) continue;
+      if constexpr (VEC == 4) {
+        const float4 x = sc::load4<T>(y + r * D + d);
+        acc[0] = fmaf(wr, x.x, acc[0]); acc[1] = fmaf(wr, x.y, acc[1]);
+        acc[2] = fmaf(wr, x.z, acc[2]); acc[3] = fmaf(wr, x.w, acc[3]);
+      } else {
+        acc[0] = fmaf(wr, sc::load1<T>(y + r * D + d), acc[0]);
+      }
     }
-  s_acc[warp][lane] = acc;
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) s_acc[warp][lane * VEC + v] = acc[v];
   __syncthreads();
-  if (warp == 0) {
+  for (int c = threadIdx.x; c < 32 * VEC; c += blockDim.x) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += s_acc[w][lane];
-    if (d < D) partial[(int64_t)blockIdx.y * D + d] = t;
+    for (int ww = 0; ww < 8; ++ww) t += s_acc[ww][c];
+    const int64_t dd = (int64_t)blockIdx.x * 32 * VEC + c;
+    if (dd < D) partial[(int64_t)blockIdx.y * D + dd] = t;
+  }
+}
+
+template <typename T>
+void launch_colsum(const T* y, const float* w, int64_t N, int64_t D, float* partial, cudaStream_t st) {
+  if (D % 4 == 0 && sc::aligned(y, 16)) {
+    dim3 grid((unsigned)((D + 127) / 128), kSlices);
+    colsum_partial_kernel<T, 4><<<grid, 256, 0, st>>>(y, w, N, D, partial);
+  } else {
+    dim3 grid((unsigned)((D + 31) / 32), kSlices);
+    colsum_partial_kernel<T, 1><<<grid, 256, 0, st>>>(y, w, N, D, partial);
   }
 }
 
@@ -94,8 +120,7 @@ extern "C" int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv
   float* partial = static_cast<float*>(ws);
   float* mean = partial + (size_t)kSlices * D;
   float* red = mean + D;
-  dim3 grid((unsigned)((D + 31) / 32), kSlices);
-  colsum_partial_kernel<float><<<grid, 256, 0, st>>>(y, nullptr, N, D, partial);
+  launch_colsum<float>(y, nullptr, N, D, partial, st);
   SC_CHECK_LAUNCH("colsum_partial");
   colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f / (float)N, D, mean);
   SC_CHECK_LAUNCH("colsum_finish");
@@ -134,11 +159,8 @@ extern "C" int sc_weighted_colsum(const void* Y, int y_dtype, const float* w, in
                     sc_loss_workspace_bytes(D));
   cudaStream_t st = sc::as_stream(stream);
   float* partial = static_cast<float*>(ws);
-  dim3 grid((unsigned)((D + 31) / 32), kSlices);
-  if (y_dtype == SC_F32)
-    colsum_partial_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(Y), w, R, D, partial);
-  else
-    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(Y), w, R, D, partial);
+  if (y_dtype == SC_F32) launch_colsum<float>(static_cast<const float*>(Y), w, R, D, partial, st);
+  else launch_colsum<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(Y), w, R, D, partial, st);
   SC_CHECK_LAUNCH("colsum_partial");
   colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f, D, out);
   SC_CHECK_LAUNCH("colsum_finish");

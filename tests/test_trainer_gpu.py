@@ -41,9 +41,12 @@ def test_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
     assert len(fvus) == meta["steps"]
     for got, want in zip(fvus, t["fvu"].tolist()):
         assert abs(got - want) < 1e-3 * max(1.0, abs(want)), (fvus, t["fvu"].tolist())
-    for name, p in (("W_enc", sae.encoder.weight), ("b_enc", sae.encoder.bias),
-                    ("W_dec", sae.W_dec), ("b_dec", sae.b_dec)):
+    for name, p in (("W_enc", sae.encoder.weight), ("b_enc", sae.encoder.bias), ("b_dec", sae.b_dec)):
         assert rel_l2(p.detach(), t[f"final.{name}"]) < 5e-3, name
+    # The fused update leaves the decoder rows at unit norm (the reference renormalises them
+    # at the start of its next step): compare directions.
+    unit = lambda w: w / w.norm(dim=1, keepdim=True)
+    assert rel_l2(unit(sae.W_dec.detach().cpu()), unit(t["final.W_dec"])) < 5e-3
     assert torch.equal(trainer.num_tokens_since_fired["layers.0"].cpu(), t["num_tokens_since_fired"])
 
     # checkpoint tree of the reference (trainer.py:648-699)
