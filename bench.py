@@ -214,8 +214,9 @@ def run_ours(a):
     lr = 2e-4 / (M / 2 ** 14) ** 0.5
     opt = FusedAdam(sae.parameters(), lr=lr)
     sae.attach_optimizer(opt)
-    if world == 1:
-        opt.enable_sparse_update(sae)  # single process: gradients go to the optimiser in sparse form
+    # gradients go to the optimiser in sparse form; with several ranks the factors are
+    # exchanged and each rank updates its slice of the latents
+    opt.enable_sparse_update(sae)
     alpha = 1 / 32
     since_fired = torch.zeros(M, dtype=torch.long, device=dev)
     dead_threshold = 10_000_000
@@ -240,8 +241,9 @@ def run_ours(a):
         loss.backward()
         if world > 1:
             for p in grads:
-                dist.all_reduce(p.grad)
-                p.grad /= world
+                if p.grad is not None:  # biases; the matrices travel as sparse factors
+                    dist.all_reduce(p.grad)
+                    p.grad /= world
         opt.step()
         opt.zero_grad(set_to_none=True)
         with torch.no_grad():

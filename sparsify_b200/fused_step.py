@@ -87,8 +87,11 @@ class FusedSaeStep(torch.autograd.Function):
         if sae.defer_weight_update and ctx.needs_input_grad[2] and ctx.needs_input_grad[4]:
             # The optimiser consumes the sparse form directly (sc_rows_adam): keep the
             # CSR and the coefficient / row tensors instead of two dense [M, D] gradients.
-            sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, coefA=acts * scale, vecA=gout,
-                                coefB=gacts, vecB=xe)
+            # in the bf16 configuration the residual rows are gathered (and, across ranks,
+            # exchanged) as bf16 like every other gathered operand
+            vecA = ops.prep_input(gout, None, torch.bfloat16) if sae.precision == "bf16" else gout
+            sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, idx=idx, coefA=acts * scale,
+                                vecA=vecA, coefB=gacts, vecB=xe)
             g_W_dec = g_W_enc = None
             g_b_enc = ops.csr_segment_sum(row_ptr, entries, gacts, M)
         else:

@@ -13,6 +13,7 @@ the Adam update, and the refresh of a bf16 shadow copy when one is registered.
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 from torch import Tensor
 
 from . import ops
@@ -37,19 +38,46 @@ class FusedAdam(torch.optim.Optimizer):
         `p` inside the update kernel; `on_refresh()` is called afterwards."""
         self._shadow[id(p)] = (shadow, on_refresh)
 
-    def enable_sparse_update(self, sae) -> bool:
+    def enable_sparse_update(self, sae, data_parallel: bool = True) -> bool:
         """Lets `sae` hand its W_enc / W_dec gradients over in sparse form (CSR +
         coefficients) so that one kernel applies them: projection, Adam, decoder
         normalisation and bf16 copies, with no dense gradient in between. Only
         for a single process without gradient accumulation: nothing else may
-        need `.grad` of the two matrices. Returns whether it was enabled."""
+        need `.grad` of the two matrices. With torch.distributed initialised and
+        `data_parallel` (replicas on every rank) the update is sharded over ranks;
+        pass data_parallel=False for a coder that lives on one rank only.
+        Returns whether it was enabled."""
         W = sae.encoder.weight
         ok = (sae.W_dec is not None and W.is_cuda and W.dtype == torch.float32 and W.shape[1] % 4 == 0
               and W.shape[1] <= 4096 and sae.W_skip is None)
+        if ok and data_parallel and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            # Data parallel: ranks exchange the sparse factors (indices, coefficients,
+            # residual and input rows) instead of dense gradients and each rank updates
+            # only its slice of the latents, then the bf16 copies are all-gathered.
+            ok = W.shape[0] % dist.get_world_size() == 0 and sae.precision == "bf16"
+            if ok:
+                sae._shard = (dist.get_rank(), dist.get_world_size())
         if ok:
             sae.defer_weight_update = True
             self._sparse.append(sae)
         return ok
+
+    def sync_masters(self, sae=None) -> None:
+        """In sharded data-parallel mode a rank keeps the fp32 values and Adam
+        moments of its own latent slice current; this all-gathers them so that
+        every rank holds the full tensors again (before a checkpoint or a dense
+        update)."""
+        for s_ in ([sae] if sae is not None else self._sparse):
+            if getattr(s_, "_shard", None) is None or not getattr(s_, "_masters_stale", False):
+                continue
+            rank, world = s_._shard
+            for p in (s_.W_dec, s_.encoder.weight):
+                rows = p.shape[0] // world
+                state = self._state_for(p)
+                for t in (p.data, state["exp_avg"], state["exp_avg_sq"]):
+                    mine = t[rank * rows:(rank + 1) * rows].clone()
+                    dist.all_gather_into_tensor(t.view(-1), mine.view(-1))
+            s_._masters_stale = False
 
     def _group_of(self, p):
         for group in self.param_groups:
@@ -70,8 +98,12 @@ class FusedAdam(torch.optim.Optimizer):
         W_enc, W_dec = sae.encoder.weight, sae.W_dec
         if W_enc.grad is not None or W_dec.grad is not None:
             sae.materialize_pending()  # dense gradients exist as well: fold and go dense
+            self.sync_masters(sae)
             return
         sae._pending = None
+        shard = getattr(sae, "_shard", None)
+        if shard is not None:
+            pend = self._exchange_factors(sae, pend, shard)
         hps, states = [], []
         for p in (W_dec, W_enc):
             group, state = self._group_of(p), self._state_for(p)
@@ -83,17 +115,67 @@ class FusedAdam(torch.optim.Optimizer):
         shadow_dec = self._shadow.get(id(W_dec), (None, None))
         shadow_enc = self._shadow.get(id(W_enc), (None, None))
         normalize = sae.cfg.normalize_decoder and not sae.cfg.transcode
+        rows = slice(None)
+        if shard is not None:
+            per = W_dec.shape[0] // shard[1]
+            rows = slice(shard[0] * per, (shard[0] + 1) * per)
+        sl = lambda t: None if t is None else t[rows]
         ops.rows_adam_(
             pend["row_ptr"], pend["entries"], pend["k"], pend["coefA"], pend["vecA"], pend["coefB"],
-            pend["vecB"], pA=W_dec.data, mA=states[0]["exp_avg"], vA=states[0]["exp_avg_sq"],
-            shadowA=shadow_dec[0], projectA=id(W_dec) in self._project, normalizeA=normalize,
-            norm_eps=torch.finfo(torch.float32).eps, hpA=hps[0], pB=W_enc.data, mB=states[1]["exp_avg"],
-            vB=states[1]["exp_avg_sq"], shadowB=shadow_enc[0], hpB=hps[1])
+            pend["vecB"], pA=W_dec.data[rows], mA=states[0]["exp_avg"][rows], vA=states[0]["exp_avg_sq"][rows],
+            shadowA=sl(shadow_dec[0]), projectA=id(W_dec) in self._project, normalizeA=normalize,
+            norm_eps=torch.finfo(torch.float32).eps, hpA=hps[0], pB=W_enc.data[rows],
+            mB=states[1]["exp_avg"][rows], vB=states[1]["exp_avg_sq"][rows], shadowB=sl(shadow_enc[0]),
+            hpB=hps[1])
+        if shard is not None:
+            for buf in (shadow_enc[0], shadow_dec[0]):  # everyone needs every row for the next forward
+                mine = buf[rows].clone()
+                dist.all_gather_into_tensor(buf.view(-1), mine.view(-1))
+            sae._masters_stale = True
         for _, cb in (shadow_dec, shadow_enc):
             if cb is not None:
                 cb()
         if normalize:
             sae._dec_unit_norm = (W_dec.data_ptr(), W_dec._version)
+
+    def _exchange_factors(self, sae, pend: dict, shard) -> dict:
+        """All-gathers the sparse gradient factors of every rank and builds the CSR
+        of this rank's latent slice over the concatenated tokens. Coefficients are
+        divided by the world size: the result is the mean of the per-rank
+        gradients, as DistributedDataParallel averages them."""
+        rank, world = shard
+        idx = pend["idx"].to(torch.int32)
+        N, k = idx.shape
+        coefA = (pend["coefA"].to(torch.float32) / world).reshape(N, k)
+        coefB = (pend["coefB"].to(torch.float32) / world).reshape(N, k)
+        vecA, vecB = pend["vecA"].contiguous(), pend["vecB"].contiguous()
+        if getattr(sae, "ragged_tokens", False):
+            # ranks may hold different token counts: pad to the maximum with inert rows
+            n_max = torch.tensor([N], device=idx.device)
+            dist.all_reduce(n_max, op=dist.ReduceOp.MAX)
+            n_max = int(n_max)
+            if n_max > N:
+                pad = n_max - N
+                idx = torch.cat([idx, idx.new_full((pad, k), -1)])
+                coefA = torch.cat([coefA, coefA.new_zeros(pad, k)])
+                coefB = torch.cat([coefB, coefB.new_zeros(pad, k)])
+                vecA = torch.cat([vecA, vecA.new_zeros(pad, vecA.shape[1])])
+                vecB = torch.cat([vecB, vecB.new_zeros(pad, vecB.shape[1])])
+                N = n_max
+
+        def gather(t):
+            out = t.new_empty((world * t.shape[0],) + tuple(t.shape[1:]))
+            dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1))
+            return out
+
+        idx_all, coefA_all, coefB_all = gather(idx), gather(coefA), gather(coefB)
+        vecA_all, vecB_all = gather(vecA), gather(vecB)
+        per = sae.encoder.weight.shape[0] // world
+        # indices relative to this rank's slice; the CSR build skips the ones outside [0, per)
+        local = idx_all.to(torch.int64) - rank * per
+        row_ptr, entries = ops.csr_build(local, per)
+        return dict(row_ptr=row_ptr, entries=entries, k=k, coefA=coefA_all, vecA=vecA_all, coefB=coefB_all,
+                    vecB=vecB_all)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -101,6 +183,9 @@ class FusedAdam(torch.optim.Optimizer):
         for sae in self._sparse:
             if sae._pending is not None:
                 self._sparse_step(sae)
+            elif getattr(sae, "_masters_stale", False) and (
+                    sae.W_dec.grad is not None or sae.encoder.weight.grad is not None):
+                self.sync_masters(sae)  # a dense update of a sharded matrix needs full replicas
         for group in self.param_groups:
             lr = group["lr"]
             lr = float(lr) if not isinstance(lr, Tensor) else float(lr.item())

@@ -102,12 +102,14 @@ class Trainer:
                        for sae in self.saes.values()]
                 lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
                 adam = FusedAdam(pgs)
-                single = not dist.is_initialized() and cfg.grad_acc_steps * cfg.micro_acc_steps == 1
+                no_acc = cfg.grad_acc_steps * cfg.micro_acc_steps == 1
                 for sae in self.saes.values():
                     sae.attach_optimizer(adam)
-                    if single:
-                        # nothing but the optimiser needs the dense weight gradients
-                        adam.enable_sparse_update(sae)
+                    sae.ragged_tokens = bool(cfg.exclude_tokens)
+                    if no_acc:
+                        # Nothing but the optimiser needs the dense weight gradients: hand them
+                        # over in sparse form (sharded over ranks when data parallel).
+                        adam.enable_sparse_update(sae, data_parallel=not cfg.distribute_modules)
                 self.optimizers = [adam]
                 self.lr_schedulers = [linear_schedule_with_warmup(adam, cfg.lr_warmup_steps, num_batches)]
             case "muon":
@@ -417,6 +419,9 @@ class Trainer:
         """Save the SAEs and training state to disk."""
         path = f'{self.cfg.save_dir}/{self.cfg.run_name or "unnamed"}'
         rank_zero = not dist.is_initialized() or dist.get_rank() == 0
+        for opt in self.optimizers:
+            if isinstance(opt, FusedAdam):
+                opt.sync_masters()  # sharded updates: make every replica whole before writing
         if rank_zero or self.cfg.distribute_modules:
             self._checkpoint(self.saes, path, rank_zero)
         if dist.is_initialized():
