@@ -221,6 +221,24 @@ int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
                  float* mB, float* vB, void* shadowB_bf16,
                  const sc_adam_hparams* hpB, void* stream);
 
+/* ---- dense bf16 GEMM on tcgen05 ---------------------------------------------
+ * out[m,n] = act(alpha * sum_k A[m,k] B[n,k] + beta * Cin[m,n] + bias[n]),
+ * A [M,K] and B [N,K] row-major bf16, fp32 accumulation in tensor memory, out
+ * (and the optional Cin) fp32 or bf16 [M,N], bias fp32 [N] or NULL, relu 0/1.
+ * K % 8 == 0. Replaces the library matmuls of the path:
+ * sparsify/muon.py:32-36 (A = X X^T, B = bA + cAA, X = aX + BX),
+ * sparsify/sparse_coder.py:221-222 (skip connection) and
+ * sparsify/fused_encoder.py:29 when the dense pre-activations are wanted.
+ * status_word as in sc_encode_topk (may be NULL). */
+int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M, int64_t N,
+                    int64_t K, float alpha, float beta, const void* Cin,
+                    int cin_dtype, const float* bias, int relu, void* out,
+                    int out_dtype, int32_t* status_word, void* stream);
+
+/* out[c,r] = in[r,c] for a bf16 matrix (puts the right operand of X = aX + BX
+ * into K-major form, sparsify/muon.py:36). */
+int sc_transpose_bf16(const void* in, int64_t R, int64_t C, void* out, void* stream);
+
 /* fp32 -> bf16 copy (shadow refresh). */
 int sc_cast_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
 

@@ -24,6 +24,8 @@ def quintic_newtonschulz(G: Tensor, steps: int) -> Tensor:
     starting from G / (||G||_F + 1e-7), in bf16 (sparsify/muon.py:11-40)."""
     assert G.ndim >= 2
     a, b, c = NS_COEFFS
+    if G.is_cuda and G.ndim == 2 and G.shape[0] % 8 == 0 and G.shape[1] % 8 == 0:
+        return _newtonschulz_tc(G, steps)
     X = G.bfloat16()
     transposed = G.size(-2) > G.size(-1)
     if transposed:
@@ -35,6 +37,28 @@ def quintic_newtonschulz(G: Tensor, steps: int) -> Tensor:
         X = torch.addmm(X, B, X, beta=a) if X.ndim == 2 else a * X + B @ X
     if transposed:
         X = X.mT
+    return X
+
+
+def _newtonschulz_tc(G: Tensor, steps: int) -> Tensor:
+    """The same iteration with every product on the tcgen05 GEMM kernel. All
+    three products are written as P Q^T with both operands K-major:
+    A = X X^T, B = bA + c A A^T (A is symmetric), X = aX + B (X^T)^T, the last
+    one after an explicit transpose of X."""
+    from . import ops
+    a, b, c = NS_COEFFS
+    X = G.bfloat16()
+    transposed = G.size(-2) > G.size(-1)
+    if transposed:
+        X = ops.transpose_bf16(X)
+    X = (X / (X.norm() + 1e-7)).contiguous()
+    for _ in range(steps):
+        A = ops.gemm_nt(X, X)
+        B = ops.gemm_nt(A, A, alpha=c, beta=b, Cin=A)
+        XT = ops.transpose_bf16(X)
+        X = ops.gemm_nt(B, XT, alpha=1.0, beta=a, Cin=X)
+    if transposed:
+        X = ops.transpose_bf16(X)
     return X
 
 

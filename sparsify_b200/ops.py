@@ -327,3 +327,39 @@ def cast_bf16(src: Tensor, dst: Tensor | None = None) -> Tensor:
     with torch.cuda.device(src.device):
         call("sc_cast_bf16", ptr(src), ptr(dst), src.numel(), _stream(src))
     return dst
+
+
+def gemm_nt(A: Tensor, B: Tensor, *, alpha: float = 1.0, beta: float = 0.0, Cin: Tensor | None = None,
+            bias: Tensor | None = None, relu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
+            out: Tensor | None = None) -> Tensor:
+    """act(alpha * A @ B.T + beta * Cin + bias) on the tensor cores; A [M,K], B [N,K] bf16."""
+    _check_cuda(A, B, Cin, bias, out)
+    assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.shape[1] == B.shape[1]
+    A, B = A.contiguous(), B.contiguous()
+    M, K = A.shape
+    N = B.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=A.device)
+    assert out.shape == (M, N) and out.is_contiguous()
+    if Cin is not None:
+        Cin = Cin.contiguous()
+        assert Cin.shape == (M, N)
+    bias32 = _f32(bias)
+    status = torch.zeros(8, dtype=torch.int32, device=A.device)
+    with torch.cuda.device(A.device):
+        call("sc_gemm_bf16_nt", ptr(A), ptr(B), M, N, K, float(alpha), float(beta), ptr(Cin),
+             dtype_code(Cin) if Cin is not None else 0, ptr(bias32), int(bool(relu)), ptr(out),
+             dtype_code(out), ptr(status), _stream(A))
+    gemm_nt.last_status = status
+    return out
+
+
+def transpose_bf16(x: Tensor) -> Tensor:
+    _check_cuda(x)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2
+    x = x.contiguous()
+    R, C = x.shape
+    out = torch.empty(C, R, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        call("sc_transpose_bf16", ptr(x), R, C, ptr(out), _stream(x))
+    return out

@@ -30,6 +30,7 @@ from torch import Tensor, nn
 
 from . import ops
 from .config import SparseCoderConfig
+from .dense import linear_nt
 from .fused_encoder import EncoderOutput, fused_encoder
 from .fused_step import FusedSaeStep, fused_supported
 from .utils import decoder_impl
@@ -245,7 +246,11 @@ class SparseCoder(nn.Module):
 
         sae_out = self.decode(top_acts, top_indices)
         if self.W_skip is not None:
-            sae_out += x.to(self.dtype) @ self.W_skip.mT
+            D = self.d_in
+            if self._lowp() and x.is_cuda and D % 8 == 0:
+                sae_out = sae_out + linear_nt(x, self.W_skip)  # tensor-core GEMM, bf16 operands
+            else:
+                sae_out += x.to(self.dtype) @ self.W_skip.mT
 
         e = y - sae_out
 

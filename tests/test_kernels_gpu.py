@@ -227,3 +227,40 @@ def test_normalize_and_adam(cuda_lib):
             ops.adam_rows_(pg, gg, mg, vg, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=step,
                            project=project)
         assert rel_l2(pg, p) < 1e-6 and rel_l2(mg, m) < 1e-5 and rel_l2(vg, v) < 5e-5
+
+
+# ----------------------------------------------------------------------------- dense GEMM / Muon
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 264), (1024, 4096, 1024), (4096, 1000, 72)])
+def test_gemm_tc(cuda_lib, M, N, K):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    A = bf16_round(torch.randn(M, K, generator=g))
+    B = bf16_round(torch.randn(N, K, generator=g))
+    C = bf16_round(torch.randn(M, N, generator=g))
+    bias = torch.randn(N, generator=g)
+    ref = 0.5 * (A.double() @ B.double().T) - 1.5 * C.double() + bias.double()
+    out = ops.gemm_nt(A.cuda().bfloat16(), B.cuda().bfloat16(), alpha=0.5, beta=-1.5, Cin=C.cuda().bfloat16(),
+                      bias=bias.cuda(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert int(ops.gemm_nt.last_status[0]) == 0
+    assert rel_l2(out, ref) < 1e-5
+    out_bf = ops.gemm_nt(A.cuda().bfloat16(), B.cuda().bfloat16(), relu=True)
+    assert rel_l2(out_bf.float(), (A.double() @ B.double().T).clamp_min(0)) < 4e-3  # bf16 output rounding
+    t = ops.transpose_bf16(A.cuda().bfloat16())
+    assert torch.equal(t.cpu(), A.bfloat16().T.contiguous())
+
+
+def test_newtonschulz_tc_vs_oracle(cuda_lib):
+    from sparsify_b200.muon import quintic_newtonschulz
+    for name in ("wide", "tall"):
+        t, _ = load_golden(f"newtonschulz_{name}")
+        X = quintic_newtonschulz(t["G"].cuda(), 5).float().cpu()
+        assert X.shape == t["G"].shape
+        assert rel_l2(X, t["X"]) < 2e-2  # bf16 products in a different summation order
+    g = torch.Generator().manual_seed(9)
+    G = torch.randn(256, 1024, generator=g)
+    X = quintic_newtonschulz(G.cuda(), 5).float().cpu()
+    ref = O.quintic_newtonschulz(G, 5).float()
+    assert rel_l2(X, ref) < 3e-2
+    s = torch.linalg.svdvals(X)
+    assert float(s.max()) < 1.6 and float(s.min()) > 0.3  # singular values pushed towards 1

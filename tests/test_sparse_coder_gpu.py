@@ -174,3 +174,16 @@ def test_sparse_fused_update_matches_dense_path(cuda_lib):
     assert rel_l2(sb["exp_avg"], sa["exp_avg"]) < 1e-5 and rel_l2(sb["exp_avg_sq"], sa["exp_avg_sq"]) < 1e-4
     norms = b.W_dec.detach().norm(dim=1)
     assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5)
+
+
+def test_transcoder_skip_bf16_vs_oracle(cuda_lib):
+    """Transcoder with a dense skip connection in the bf16 configuration: the skip
+    product and its gradients run on the tcgen05 GEMM."""
+    t, meta = load_golden("forward_transcoder_skip")
+    sae = build_sae(t, meta["cfg"], "bf16")
+    out = sae(t["x"].cuda(), t["y"].cuda())
+    out.fvu.backward()
+    assert abs(float(out.fvu) - float(t["fvu"])) < 2e-2 * float(t["fvu"])
+    assert rel_l2(out.sae_out.detach(), t["sae_out"]) < 2e-2
+    assert rel_l2(sae.W_skip.grad, t["grad.W_skip"]) < 3e-2
+    assert rel_l2(sae.W_dec.grad, t["grad.W_dec"]) < 3e-2
