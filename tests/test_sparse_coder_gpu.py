@@ -138,7 +138,8 @@ def test_cpu_tensors_are_rejected():
         ops.embedding_bag_fwd(torch.zeros(2, 2, dtype=torch.long), torch.zeros(2, 2), torch.zeros(4, 4))
 
 
-def test_sparse_fused_update_matches_dense_path(cuda_lib):
+@pytest.mark.parametrize("precision,tol", [("mixed", 1e-5), ("bf16", 2e-3)])
+def test_sparse_fused_update_matches_dense_path(cuda_lib, precision, tol):
     """sc_rows_adam (gradients applied in sparse form: projection, Adam, decoder
     normalisation, bf16 copies in one kernel) against the separate kernels."""
     from sparsify_b200 import SparseCoder, SparseCoderConfig
@@ -150,6 +151,7 @@ def test_sparse_fused_update_matches_dense_path(cuda_lib):
     for sparse in (False, True):
         torch.manual_seed(0)
         sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+        sae.precision = precision
         opt = FusedAdam(sae.parameters(), lr=1e-3)
         sae.attach_optimizer(opt)
         if sparse:
@@ -166,12 +168,14 @@ def test_sparse_fused_update_matches_dense_path(cuda_lib):
         models.append((sae, opt))
     (a, oa), (b, ob) = models
     for (n1, p1), (_, p2) in zip(a.named_parameters(), b.named_parameters()):
-        assert rel_l2(p2.detach(), p1.detach()) < 1e-5, n1
-    for name in ("encoder.weight", "W_dec"):
+        # "mixed": both paths use fp32 residual rows (same arithmetic, tight bound);
+        # "bf16": the sparse path gathers the residual rows as bf16, the dense one as fp32
+        assert rel_l2(p2.detach(), p1.detach()) < tol, n1
+    for name in ("encoder.weight",) + (("W_dec",) if precision == "bf16" else ()):
         assert torch.equal(b.shadow(name), dict(b.named_parameters())[name].detach().bfloat16()), name
     sa, sb = oa.state[a.W_dec], ob.state[b.W_dec]
     assert int(sa["step"]) == int(sb["step"]) == 3
-    assert rel_l2(sb["exp_avg"], sa["exp_avg"]) < 1e-5 and rel_l2(sb["exp_avg_sq"], sa["exp_avg_sq"]) < 1e-4
+    assert rel_l2(sb["exp_avg"], sa["exp_avg"]) < 10 * tol and rel_l2(sb["exp_avg_sq"], sa["exp_avg_sq"]) < 100 * tol
     norms = b.W_dec.detach().norm(dim=1)
     assert torch.allclose(norms, torch.ones_like(norms), atol=1e-5)
 
