@@ -46,6 +46,7 @@ struct Args {
   int64_t D;
   int k;
   int projectA, normalizeA;
+  int parts;  // bit 0: decoder (A), bit 1: encoder (B)
   float norm_eps;
   Hp hpA, hpB;
 };
@@ -59,6 +60,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
   const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
   const int64_t off = m * D;
 
+  const bool doA = (a.parts & 1) != 0, doB = (a.parts & 2) != 0;
   float4 gA[kNV], gB[kNV];
   int64_t col[kNV];
 #pragma unroll
@@ -71,18 +73,28 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
   for (int32_t p = lo; p < hi; ++p) {
     const int32_t e = a.entries[p];
     const int64_t n = e / a.k;
-    const float ca = a.coefA[e], cb = a.coefB[e];
-    const TA* ra = vecA + n * D;
-    const TB* rb = vecB + n * D;
+    if (doA) {
+      const float ca = a.coefA[e];
+      const TA* ra = vecA + n * D;
 #pragma unroll
-    for (int c = 0; c < kNV; ++c) {
-      if (col[c] < D) {
-        const float4 x = sc::load4<TA>(ra + col[c]);
-        const float4 y = sc::load4<TB>(rb + col[c]);
-        gA[c].x = fmaf(ca, x.x, gA[c].x); gA[c].y = fmaf(ca, x.y, gA[c].y);
-        gA[c].z = fmaf(ca, x.z, gA[c].z); gA[c].w = fmaf(ca, x.w, gA[c].w);
-        gB[c].x = fmaf(cb, y.x, gB[c].x); gB[c].y = fmaf(cb, y.y, gB[c].y);
-        gB[c].z = fmaf(cb, y.z, gB[c].z); gB[c].w = fmaf(cb, y.w, gB[c].w);
+      for (int c = 0; c < kNV; ++c) {
+        if (col[c] < D) {
+          const float4 x = sc::load4<TA>(ra + col[c]);
+          gA[c].x = fmaf(ca, x.x, gA[c].x); gA[c].y = fmaf(ca, x.y, gA[c].y);
+          gA[c].z = fmaf(ca, x.z, gA[c].z); gA[c].w = fmaf(ca, x.w, gA[c].w);
+        }
+      }
+    }
+    if (doB) {
+      const float cb = a.coefB[e];
+      const TB* rb = vecB + n * D;
+#pragma unroll
+      for (int c = 0; c < kNV; ++c) {
+        if (col[c] < D) {
+          const float4 y = sc::load4<TB>(rb + col[c]);
+          gB[c].x = fmaf(cb, y.x, gB[c].x); gB[c].y = fmaf(cb, y.y, gB[c].y);
+          gB[c].z = fmaf(cb, y.z, gB[c].z); gB[c].w = fmaf(cb, y.w, gB[c].w);
+        }
       }
     }
   }
@@ -90,7 +102,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
   // ---- encoder row: Adam ----
 #pragma unroll
   for (int c = 0; c < kNV; ++c) {
-    if (col[c] < D) {
+    if (doB && col[c] < D) {
       float4 pw = *reinterpret_cast<const float4*>(a.pB + off + col[c]);
       float4 mw = *reinterpret_cast<const float4*>(a.mB + off + col[c]);
       float4 vw = *reinterpret_cast<const float4*>(a.vB + off + col[c]);
@@ -105,6 +117,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
     }
   }
 
+  if (!doA) return;
   // ---- decoder row: project, Adam, normalise ----
   float4 pw[kNV];
   float dot = 0.f;
@@ -164,8 +177,9 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
                             int vecB_dtype, int64_t M, int64_t D, float* pA, float* mA, float* vA,
                             void* shadowA_bf16, int projectA, int normalizeA, float norm_eps,
                             const sc_adam_hparams* hpA, float* pB, float* mB, float* vB,
-                            void* shadowB_bf16, const sc_adam_hparams* hpB, void* stream) {
+                            void* shadowB_bf16, const sc_adam_hparams* hpB, int parts, void* stream) {
   SC_REQUIRE(M > 0 && D > 0 && k > 0 && M <= 0x7fffffffLL, "sc_rows_adam: bad shape");
+  SC_REQUIRE(parts >= 1 && parts <= 3, "sc_rows_adam: parts must be 1 (decoder), 2 (encoder) or 3 (both)");
   SC_REQUIRE(row_ptr && entries && coefA && vecA && coefB && vecB && pA && mA && vA && pB && mB && vB && hpA && hpB,
              "sc_rows_adam: null pointer");
   SC_REQUIRE(sc::valid_dtype(vecA_dtype) && sc::valid_dtype(vecB_dtype), "sc_rows_adam: bad dtype");
@@ -180,6 +194,7 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
   a.pA = pA; a.mA = mA; a.vA = vA; a.pB = pB; a.mB = mB; a.vB = vB;
   a.shadowA = static_cast<__nv_bfloat16*>(shadowA_bf16);
   a.shadowB = static_cast<__nv_bfloat16*>(shadowB_bf16);
+  a.parts = parts;
   a.D = D; a.k = k; a.projectA = projectA; a.normalizeA = normalizeA; a.norm_eps = norm_eps;
   a.hpA = make_hp(hpA); a.hpB = make_hp(hpB);
   cudaStream_t st = sc::as_stream(stream);

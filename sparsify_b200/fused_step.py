@@ -47,6 +47,7 @@ class FusedSaeStep(torch.autograd.Function):
             pre = ops.preacts_dense(xe, w_enc_src, b_enc.detach())
             acts, idx = (ops.topk_rows if cfg.activation == "topk" else ops.groupmax_rows)(pre, k)
             del pre
+        sae.wait_decoder()  # a decoder update may still be running under the encoder above
         gather_lp = sae.precision == "bf16" and W_dec.dtype == torch.float32
         w_dec_src = sae.shadow("W_dec") if gather_lp else W_dec.detach()
         out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())

@@ -38,7 +38,7 @@ class FusedAdam(torch.optim.Optimizer):
         `p` inside the update kernel; `on_refresh()` is called afterwards."""
         self._shadow[id(p)] = (shadow, on_refresh)
 
-    def enable_sparse_update(self, sae, data_parallel: bool = True) -> bool:
+    def enable_sparse_update(self, sae, data_parallel: bool = True, overlap_decoder: bool = False) -> bool:
         """Lets `sae` hand its W_enc / W_dec gradients over in sparse form (CSR +
         coefficients) so that one kernel applies them: projection, Adam, decoder
         normalisation and bf16 copies, with no dense gradient in between. Only
@@ -46,6 +46,10 @@ class FusedAdam(torch.optim.Optimizer):
         need `.grad` of the two matrices. With torch.distributed initialised and
         `data_parallel` (replicas on every rank) the update is sharded over ranks;
         pass data_parallel=False for a coder that lives on one rank only.
+        overlap_decoder=True runs the decoder half of the update on a second
+        stream, so that it overlaps the next forward's encoder GEMM (which does
+        not read W_dec); readers of W_dec inside this package wait for it, code
+        that reads `sae.W_dec` directly must call `sae.wait_decoder()` first.
         Returns whether it was enabled."""
         W = sae.encoder.weight
         ok = (sae.W_dec is not None and W.is_cuda and W.dtype == torch.float32 and W.shape[1] % 4 == 0
@@ -59,6 +63,7 @@ class FusedAdam(torch.optim.Optimizer):
                 sae._shard = (dist.get_rank(), dist.get_world_size())
         if ok:
             sae.defer_weight_update = True
+            sae._overlap_decoder = bool(overlap_decoder) and getattr(sae, "_shard", None) is None
             self._sparse.append(sae)
         return ok
 
@@ -120,13 +125,33 @@ class FusedAdam(torch.optim.Optimizer):
             per = W_dec.shape[0] // shard[1]
             rows = slice(shard[0] * per, (shard[0] + 1) * per)
         sl = lambda t: None if t is None else t[rows]
-        ops.rows_adam_(
-            pend["row_ptr"], pend["entries"], pend["k"], pend["coefA"], pend["vecA"], pend["coefB"],
-            pend["vecB"], pA=W_dec.data[rows], mA=states[0]["exp_avg"][rows], vA=states[0]["exp_avg_sq"][rows],
-            shadowA=sl(shadow_dec[0]), projectA=id(W_dec) in self._project, normalizeA=normalize,
-            norm_eps=torch.finfo(torch.float32).eps, hpA=hps[0], pB=W_enc.data[rows],
-            mB=states[1]["exp_avg"][rows], vB=states[1]["exp_avg_sq"][rows], shadowB=sl(shadow_enc[0]),
-            hpB=hps[1])
+        kw = dict(pA=W_dec.data[rows], mA=states[0]["exp_avg"][rows], vA=states[0]["exp_avg_sq"][rows],
+                  shadowA=sl(shadow_dec[0]), projectA=id(W_dec) in self._project, normalizeA=normalize,
+                  norm_eps=torch.finfo(torch.float32).eps, hpA=hps[0], pB=W_enc.data[rows],
+                  mB=states[1]["exp_avg"][rows], vB=states[1]["exp_avg_sq"][rows], shadowB=sl(shadow_enc[0]),
+                  hpB=hps[1])
+        args = (pend["row_ptr"], pend["entries"], pend["k"], pend["coefA"], pend["vecA"], pend["coefB"],
+                pend["vecB"])
+        if getattr(sae, "_overlap_decoder", False):
+            # Encoder half now; decoder half on a side stream, where it can run under the
+            # next forward's encoder GEMM. Consumers of W_dec wait on the recorded event.
+            sae.wait_decoder()
+            main = torch.cuda.current_stream(W_dec.device)
+            ops.rows_adam_(*args, parts=2, **kw)
+            if getattr(sae, "_side_stream", None) is None:
+                sae._side_stream = torch.cuda.Stream(device=W_dec.device)
+            side = sae._side_stream
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ops.rows_adam_(*args, parts=1, **kw)
+                event = torch.cuda.Event()
+                event.record(side)
+            for t in args:
+                if isinstance(t, Tensor):
+                    t.record_stream(side)  # allocated on the main stream, still in use on the side stream
+            sae._dec_event = event
+        else:
+            ops.rows_adam_(*args, **kw)
         if shard is not None:
             for buf in (shadow_enc[0], shadow_dec[0]):  # everyone needs every row for the next forward
                 mine = buf[rows].clone()
@@ -181,9 +206,12 @@ class FusedAdam(torch.optim.Optimizer):
     def step(self, closure=None):
         assert closure is None, "Closure is not supported."
         for sae in self._sparse:
-            if sae._pending is not None:
+            had_pending = sae._pending is not None
+            if had_pending:
                 self._sparse_step(sae)
-            elif getattr(sae, "_masters_stale", False) and (
+            if sae.W_dec.grad is not None:
+                sae.wait_decoder()  # a dense update of W_dec must not race the side stream
+            if not had_pending and getattr(sae, "_masters_stale", False) and (
                     sae.W_dec.grad is not None or sae.encoder.weight.grad is not None):
                 self.sync_masters(sae)  # a dense update of a sharded matrix needs full replicas
         for group in self.param_groups:

@@ -85,6 +85,7 @@ class SparseCoder(nn.Module):
         self.defer_weight_update = False  # set by FusedAdam.enable_sparse_update
         self._pending: dict | None = None  # weight gradients in sparse form, awaiting the optimiser
         self._dec_unit_norm: tuple | None = None  # (data_ptr, version) at which W_dec rows had unit norm
+        self._dec_event = None  # completion of a decoder update running on a side stream
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 
         self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
@@ -165,6 +166,7 @@ class SparseCoder(nn.Module):
         return sae
 
     def save_to_disk(self, path: Path | str):
+        self.wait_decoder()
         path = Path(path)
         path.mkdir(parents=True, exist_ok=True)
         save_model(self, str(path / "sae.safetensors"))
@@ -223,6 +225,7 @@ class SparseCoder(nn.Module):
 
     def decode(self, top_acts: Tensor, top_indices: Tensor) -> Tensor:
         assert self.W_dec is not None, "Decoder weight was not initialized."
+        self.wait_decoder()
         w_lp = self.shadow("W_dec") if (self.precision == "bf16" and self.dtype == torch.float32) else None
         y = decoder_impl(top_indices, top_acts.to(self.dtype), self.W_dec.mT, w_lp)
         return y + self.b_dec
@@ -292,6 +295,7 @@ class SparseCoder(nn.Module):
         W = self.W_dec.data
         if self._dec_unit_norm == (W.data_ptr(), self.W_dec._version):
             return  # the last fused update already left the rows at unit norm
+        self.wait_decoder()
         if W.is_cuda and W.dtype == torch.float32 and W.is_contiguous():
             # the kernel writes through raw pointers (no version bump): refresh the
             # cached bf16 copy in the same pass, or drop it
@@ -304,6 +308,14 @@ class SparseCoder(nn.Module):
             # construction / checkpoint handling on the host before .to("cuda")
             norm = torch.norm(W, dim=1, keepdim=True)
             self.W_dec.data /= norm + eps
+
+    def wait_decoder(self) -> None:
+        """Makes the current stream wait for a decoder update that FusedAdam
+        placed on its side stream (`overlap_decoder`). Call before reading
+        `W_dec` (or its bf16 copy) outside this package's own methods."""
+        event, self._dec_event = self._dec_event, None
+        if event is not None:
+            torch.cuda.current_stream(self.device).wait_event(event)
 
     def materialize_pending(self) -> None:
         """Turns a deferred sparse weight gradient into dense .grad tensors
