@@ -216,7 +216,7 @@ def run_ours(a):
     sae.attach_optimizer(opt)
     # gradients go to the optimiser in sparse form; with several ranks the factors are
     # exchanged and each rank updates its slice of the latents
-    opt.enable_sparse_update(sae, overlap_decoder=True)
+    opt.enable_sparse_update(sae)
     alpha = 1 / 32
     since_fired = torch.zeros(M, dtype=torch.long, device=dev)
     dead_threshold = 10_000_000

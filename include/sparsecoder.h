@@ -214,7 +214,10 @@ typedef struct sc_adam_hparams {
  * hpA / hpB are host pointers. shadow pointers may be NULL. parts selects the
  * matrices a launch updates: 1 = decoder (A) only, 2 = encoder (B) only, 3 =
  * both (the decoder half can then run on a second stream under the next
- * forward's encoder GEMM, which does not read W_dec). */
+ * forward's encoder GEMM, which does not read W_dec). max_ctas > 0 caps the
+ * grid (persistent CTAs striding over the latents) so that such a background
+ * launch leaves room on every SM for the kernel it overlaps; 0 = one CTA per
+ * latent. */
 int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
                  const float* coefA, const void* vecA, int vecA_dtype,
                  const float* coefB, const void* vecB, int vecB_dtype,
@@ -222,7 +225,8 @@ int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
                  void* shadowA_bf16, int projectA, int normalizeA,
                  float norm_eps, const sc_adam_hparams* hpA, float* pB,
                  float* mB, float* vB, void* shadowB_bf16,
-                 const sc_adam_hparams* hpB, int parts, void* stream);
+                 const sc_adam_hparams* hpB, int parts, int max_ctas,
+                 void* stream);
 
 /* ---- dense bf16 GEMM on tcgen05 ---------------------------------------------
  * out[m,n] = act(alpha * sum_k A[m,k] B[n,k] + beta * Cin[m,n] + bias[n]),

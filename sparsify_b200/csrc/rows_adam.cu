@@ -43,7 +43,7 @@ struct Args {
   const float* coefB;
   float *pA, *mA, *vA, *pB, *mB, *vB;
   __nv_bfloat16 *shadowA, *shadowB;
-  int64_t D;
+  int64_t D, M;
   int k;
   int projectA, normalizeA;
   int parts;  // bit 0: decoder (A), bit 1: encoder (B)
@@ -55,8 +55,9 @@ template <typename TA, typename TB>
 __global__ void __launch_bounds__(kThreads)
 rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const Args a) {
   __shared__ float scratch[33];
-  const int64_t m = blockIdx.x;
   const int64_t D = a.D;
+  // one CTA per latent, or (grid smaller than M) a persistent CTA striding over the latents
+  for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
   const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
   const int64_t off = m * D;
 
@@ -117,7 +118,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
     }
   }
 
-  if (!doA) return;
+  if (!doA) continue;
   // ---- decoder row: project, Adam, normalise ----
   float4 pw[kNV];
   float dot = 0.f;
@@ -160,6 +161,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
       if (a.shadowA != nullptr) store_bf16x4(a.shadowA + off + col[c], o);
     }
   }
+  }  // latent loop
 }
 
 Hp make_hp(const sc_adam_hparams* h) {
@@ -177,7 +179,8 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
                             int vecB_dtype, int64_t M, int64_t D, float* pA, float* mA, float* vA,
                             void* shadowA_bf16, int projectA, int normalizeA, float norm_eps,
                             const sc_adam_hparams* hpA, float* pB, float* mB, float* vB,
-                            void* shadowB_bf16, const sc_adam_hparams* hpB, int parts, void* stream) {
+                            void* shadowB_bf16, const sc_adam_hparams* hpB, int parts, int max_ctas,
+                            void* stream) {
   SC_REQUIRE(M > 0 && D > 0 && k > 0 && M <= 0x7fffffffLL, "sc_rows_adam: bad shape");
   SC_REQUIRE(parts >= 1 && parts <= 3, "sc_rows_adam: parts must be 1 (decoder), 2 (encoder) or 3 (both)");
   SC_REQUIRE(row_ptr && entries && coefA && vecA && coefB && vecB && pA && mA && vA && pB && mB && vB && hpA && hpB,
@@ -195,10 +198,11 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
   a.shadowA = static_cast<__nv_bfloat16*>(shadowA_bf16);
   a.shadowB = static_cast<__nv_bfloat16*>(shadowB_bf16);
   a.parts = parts;
+  a.M = M;
   a.D = D; a.k = k; a.projectA = projectA; a.normalizeA = normalizeA; a.norm_eps = norm_eps;
   a.hpA = make_hp(hpA); a.hpB = make_hp(hpB);
   cudaStream_t st = sc::as_stream(stream);
-  dim3 grid((unsigned)M), block(kThreads);
+  dim3 grid((unsigned)(max_ctas > 0 && max_ctas < M ? max_ctas : M)), block(kThreads);
   using bf16 = __nv_bfloat16;
   if (vecA_dtype == SC_F32 && vecB_dtype == SC_F32)
     rows_adam_kernel<float, float><<<grid, block, 0, st>>>((const float*)vecA, (const float*)vecB, a);

@@ -12,6 +12,8 @@ the Adam update, and the refresh of a bf16 shadow copy when one is registered.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import Tensor
@@ -47,9 +49,11 @@ class FusedAdam(torch.optim.Optimizer):
         `data_parallel` (replicas on every rank) the update is sharded over ranks;
         pass data_parallel=False for a coder that lives on one rank only.
         overlap_decoder=True runs the decoder half of the update on a second
-        stream, so that it overlaps the next forward's encoder GEMM (which does
+        stream, so that it may overlap the next forward's encoder GEMM (which does
         not read W_dec); readers of W_dec inside this package wait for it, code
         that reads `sae.W_dec` directly must call `sae.wait_decoder()` first.
+        (Measured on B200 at d=4096, 131072 latents: 0.5 ms of 28 with the full
+        grid, a loss with a small persistent grid; off by default.)
         Returns whether it was enabled."""
         W = sae.encoder.weight
         ok = (sae.W_dec is not None and W.is_cuda and W.dtype == torch.float32 and W.shape[1] % 4 == 0
@@ -64,6 +68,7 @@ class FusedAdam(torch.optim.Optimizer):
         if ok:
             sae.defer_weight_update = True
             sae._overlap_decoder = bool(overlap_decoder) and getattr(sae, "_shard", None) is None
+            sae._overlap_ctas_per_sm = int(os.environ.get("SC_OVERLAP_CTAS_PER_SM", "0"))
             self._sparse.append(sae)
         return ok
 
@@ -143,7 +148,10 @@ class FusedAdam(torch.optim.Optimizer):
             side = sae._side_stream
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                ops.rows_adam_(*args, parts=1, **kw)
+                # optionally a small persistent grid (SC_OVERLAP_CTAS_PER_SM > 0), which leaves
+                # room on every SM for the encoder kernel launched after it
+                sms = torch.cuda.get_device_properties(W_dec.device).multi_processor_count
+                ops.rows_adam_(*args, parts=1, max_ctas=sms * sae._overlap_ctas_per_sm, **kw)
                 event = torch.cuda.Event()
                 event.record(side)
             for t in args:

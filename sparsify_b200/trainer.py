@@ -109,7 +109,7 @@ class Trainer:
                     if no_acc:
                         # Nothing but the optimiser needs the dense weight gradients: hand them
                         # over in sparse form (sharded over ranks when data parallel).
-                        adam.enable_sparse_update(sae, data_parallel=not cfg.distribute_modules, overlap_decoder=True)
+                        adam.enable_sparse_update(sae, data_parallel=not cfg.distribute_modules)
                 self.optimizers = [adam]
                 self.lr_schedulers = [linear_schedule_with_warmup(adam, cfg.lr_warmup_steps, num_batches)]
             case "muon":

@@ -138,7 +138,7 @@ def test_cpu_tensors_are_rejected():
         ops.embedding_bag_fwd(torch.zeros(2, 2, dtype=torch.long), torch.zeros(2, 2), torch.zeros(4, 4))
 
 
-@pytest.mark.parametrize("precision,tol", [("mixed", 1e-5), ("bf16", 2e-3)])
+@pytest.mark.parametrize("precision,tol", [("mixed", 1e-5), ("bf16", 5e-3)])
 def test_sparse_fused_update_matches_dense_path(cuda_lib, precision, tol):
     """sc_rows_adam (gradients applied in sparse form: projection, Adam, decoder
     normalisation, bf16 copies in one kernel) against the separate kernels."""
