@@ -234,9 +234,15 @@ def run_ours(a):
         sae.b_dec.copy_(mean)
     grads = [p for p in sae.parameters()]
 
+    tokens_seen = 0
+
     def step(x):
+        nonlocal tokens_seen
         sae.set_decoder_norm_to_unit_norm()
-        out = sae(x, dead_mask=since_fired > dead_threshold)
+        # as the Trainer does: the dead mask is only built once a counter can have passed the threshold
+        dead = since_fired > dead_threshold if tokens_seen > dead_threshold else None
+        tokens_seen += N
+        out = sae(x, dead_mask=dead)
         loss = out.fvu + alpha * out.auxk_loss
         loss.backward()
         if world > 1:

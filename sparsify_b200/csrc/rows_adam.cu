@@ -51,117 +51,111 @@ struct Args {
   Hp hpA, hpB;
 };
 
+// sum over the CSR segment [lo, hi) of coef[e] * vec[e / k, cols of this thread]
+template <typename T>
+__device__ __forceinline__ void gather_rows(const int32_t* __restrict__ entries, int32_t lo, int32_t hi, int k,
+                                            const float* __restrict__ coef, const T* __restrict__ vec, int64_t D,
+                                            float4 (&g)[kNV]) {
+#pragma unroll
+  for (int c = 0; c < kNV; ++c) g[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int32_t p = lo; p < hi; ++p) {
+    const int32_t e = entries[p];
+    const float cf = coef[e];
+    const T* r = vec + (int64_t)(e / k) * D;
+#pragma unroll
+    for (int c = 0; c < kNV; ++c) {
+      const int col = (c * kThreads + threadIdx.x) * 4;
+      if (col < D) {
+        const float4 x = sc::load4<T>(r + col);
+        g[c].x = fmaf(cf, x.x, g[c].x); g[c].y = fmaf(cf, x.y, g[c].y);
+        g[c].z = fmaf(cf, x.z, g[c].z); g[c].w = fmaf(cf, x.w, g[c].w);
+      }
+    }
+  }
+}
+
+// The two matrices are handled one after the other (encoder, then decoder) so that
+// only one gradient row is live at a time: 64 registers, four CTAs per SM.
 template <typename TA, typename TB>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const Args a) {
   __shared__ float scratch[33];
   const int64_t D = a.D;
+  const bool doA = (a.parts & 1) != 0, doB = (a.parts & 2) != 0;
   // one CTA per latent, or (grid smaller than M) a persistent CTA striding over the latents
   for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
-  const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
-  const int64_t off = m * D;
+    const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
+    const int64_t off = m * D;
+    float4 g[kNV];
 
-  const bool doA = (a.parts & 1) != 0, doB = (a.parts & 2) != 0;
-  float4 gA[kNV], gB[kNV];
-  int64_t col[kNV];
-#pragma unroll
-  for (int c = 0; c < kNV; ++c) {
-    gA[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    gB[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    col[c] = ((int64_t)c * kThreads + threadIdx.x) * 4;
-  }
-#pragma unroll 2
-  for (int32_t p = lo; p < hi; ++p) {
-    const int32_t e = a.entries[p];
-    const int64_t n = e / a.k;
-    if (doA) {
-      const float ca = a.coefA[e];
-      const TA* ra = vecA + n * D;
+    if (doB) {  // ---- encoder row: Adam ----
+      gather_rows<TB>(a.entries, lo, hi, a.k, a.coefB, vecB, D, g);
 #pragma unroll
       for (int c = 0; c < kNV; ++c) {
-        if (col[c] < D) {
-          const float4 x = sc::load4<TA>(ra + col[c]);
-          gA[c].x = fmaf(ca, x.x, gA[c].x); gA[c].y = fmaf(ca, x.y, gA[c].y);
-          gA[c].z = fmaf(ca, x.z, gA[c].z); gA[c].w = fmaf(ca, x.w, gA[c].w);
+        const int col = (c * kThreads + threadIdx.x) * 4;
+        if (col < D) {
+          float4 pw = *reinterpret_cast<const float4*>(a.pB + off + col);
+          float4 mw = *reinterpret_cast<const float4*>(a.mB + off + col);
+          float4 vw = *reinterpret_cast<const float4*>(a.vB + off + col);
+          pw.x = adam1(pw.x, g[c].x, mw.x, vw.x, a.hpB);
+          pw.y = adam1(pw.y, g[c].y, mw.y, vw.y, a.hpB);
+          pw.z = adam1(pw.z, g[c].z, mw.z, vw.z, a.hpB);
+          pw.w = adam1(pw.w, g[c].w, mw.w, vw.w, a.hpB);
+          *reinterpret_cast<float4*>(a.pB + off + col) = pw;
+          *reinterpret_cast<float4*>(a.mB + off + col) = mw;
+          *reinterpret_cast<float4*>(a.vB + off + col) = vw;
+          if (a.shadowB != nullptr) store_bf16x4(a.shadowB + off + col, pw);
         }
       }
     }
-    if (doB) {
-      const float cb = a.coefB[e];
-      const TB* rb = vecB + n * D;
+    if (!doA) continue;
+
+    // ---- decoder row: project, Adam, normalise ----
+    gather_rows<TA>(a.entries, lo, hi, a.k, a.coefA, vecA, D, g);
+    float4 pw[kNV];
+    float dot = 0.f;
 #pragma unroll
-      for (int c = 0; c < kNV; ++c) {
-        if (col[c] < D) {
-          const float4 y = sc::load4<TB>(rb + col[c]);
-          gB[c].x = fmaf(cb, y.x, gB[c].x); gB[c].y = fmaf(cb, y.y, gB[c].y);
-          gB[c].z = fmaf(cb, y.z, gB[c].z); gB[c].w = fmaf(cb, y.w, gB[c].w);
-        }
+    for (int c = 0; c < kNV; ++c) {
+      const int col = (c * kThreads + threadIdx.x) * 4;
+      if (col < D) {
+        pw[c] = *reinterpret_cast<const float4*>(a.pA + off + col);
+        dot += g[c].x * pw[c].x + g[c].y * pw[c].y + g[c].z * pw[c].z + g[c].w * pw[c].w;
+      }
+    }
+    if (a.projectA) dot = sc::block_sum(dot, scratch);
+    else dot = 0.f;
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < kNV; ++c) {
+      const int col = (c * kThreads + threadIdx.x) * 4;
+      if (col < D) {
+        float4 mw = *reinterpret_cast<const float4*>(a.mA + off + col);
+        float4 vw = *reinterpret_cast<const float4*>(a.vA + off + col);
+        const float4 gp = make_float4(g[c].x - dot * pw[c].x, g[c].y - dot * pw[c].y,
+                                      g[c].z - dot * pw[c].z, g[c].w - dot * pw[c].w);
+        pw[c].x = adam1(pw[c].x, gp.x, mw.x, vw.x, a.hpA);
+        pw[c].y = adam1(pw[c].y, gp.y, mw.y, vw.y, a.hpA);
+        pw[c].z = adam1(pw[c].z, gp.z, mw.z, vw.z, a.hpA);
+        pw[c].w = adam1(pw[c].w, gp.w, mw.w, vw.w, a.hpA);
+        *reinterpret_cast<float4*>(a.mA + off + col) = mw;
+        *reinterpret_cast<float4*>(a.vA + off + col) = vw;
+        ss += pw[c].x * pw[c].x + pw[c].y * pw[c].y + pw[c].z * pw[c].z + pw[c].w * pw[c].w;
+      }
+    }
+    if (a.normalizeA) ss = sc::block_sum(ss, scratch);
+    const float denom = sqrtf(ss) + a.norm_eps;  // same division as sc_normalize_rows
+#pragma unroll
+    for (int c = 0; c < kNV; ++c) {
+      const int col = (c * kThreads + threadIdx.x) * 4;
+      if (col < D) {
+        float4 o = pw[c];
+        if (a.normalizeA) o = make_float4(o.x / denom, o.y / denom, o.z / denom, o.w / denom);
+        *reinterpret_cast<float4*>(a.pA + off + col) = o;
+        if (a.shadowA != nullptr) store_bf16x4(a.shadowA + off + col, o);
       }
     }
   }
-
-  // ---- encoder row: Adam ----
-#pragma unroll
-  for (int c = 0; c < kNV; ++c) {
-    if (doB && col[c] < D) {
-      float4 pw = *reinterpret_cast<const float4*>(a.pB + off + col[c]);
-      float4 mw = *reinterpret_cast<const float4*>(a.mB + off + col[c]);
-      float4 vw = *reinterpret_cast<const float4*>(a.vB + off + col[c]);
-      pw.x = adam1(pw.x, gB[c].x, mw.x, vw.x, a.hpB);
-      pw.y = adam1(pw.y, gB[c].y, mw.y, vw.y, a.hpB);
-      pw.z = adam1(pw.z, gB[c].z, mw.z, vw.z, a.hpB);
-      pw.w = adam1(pw.w, gB[c].w, mw.w, vw.w, a.hpB);
-      *reinterpret_cast<float4*>(a.pB + off + col[c]) = pw;
-      *reinterpret_cast<float4*>(a.mB + off + col[c]) = mw;
-      *reinterpret_cast<float4*>(a.vB + off + col[c]) = vw;
-      if (a.shadowB != nullptr) store_bf16x4(a.shadowB + off + col[c], pw);
-    }
-  }
-
-  if (!doA) continue;
-  // ---- decoder row: project, Adam, normalise ----
-  float4 pw[kNV];
-  float dot = 0.f;
-#pragma unroll
-  for (int c = 0; c < kNV; ++c) {
-    if (col[c] < D) {
-      pw[c] = *reinterpret_cast<const float4*>(a.pA + off + col[c]);
-      dot += gA[c].x * pw[c].x + gA[c].y * pw[c].y + gA[c].z * pw[c].z + gA[c].w * pw[c].w;
-    }
-  }
-  if (a.projectA) dot = sc::block_sum(dot, scratch);
-  else dot = 0.f;
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < kNV; ++c) {
-    if (col[c] < D) {
-      float4 mw = *reinterpret_cast<const float4*>(a.mA + off + col[c]);
-      float4 vw = *reinterpret_cast<const float4*>(a.vA + off + col[c]);
-      const float4 g = make_float4(gA[c].x - dot * pw[c].x, gA[c].y - dot * pw[c].y,
-                                   gA[c].z - dot * pw[c].z, gA[c].w - dot * pw[c].w);
-      pw[c].x = adam1(pw[c].x, g.x, mw.x, vw.x, a.hpA);
-      pw[c].y = adam1(pw[c].y, g.y, mw.y, vw.y, a.hpA);
-      pw[c].z = adam1(pw[c].z, g.z, mw.z, vw.z, a.hpA);
-      pw[c].w = adam1(pw[c].w, g.w, mw.w, vw.w, a.hpA);
-      *reinterpret_cast<float4*>(a.mA + off + col[c]) = mw;
-      *reinterpret_cast<float4*>(a.vA + off + col[c]) = vw;
-      ss += pw[c].x * pw[c].x + pw[c].y * pw[c].y + pw[c].z * pw[c].z + pw[c].w * pw[c].w;
-    }
-  }
-  if (a.normalizeA) ss = sc::block_sum(ss, scratch);
-#pragma unroll
-  for (int c = 0; c < kNV; ++c) {
-    if (col[c] < D) {
-      float4 o = pw[c];
-      if (a.normalizeA) {
-        const float denom = sqrtf(ss) + a.norm_eps;  // same division as sc_normalize_rows
-        o = make_float4(o.x / denom, o.y / denom, o.z / denom, o.w / denom);
-      }
-      *reinterpret_cast<float4*>(a.pA + off + col[c]) = o;
-      if (a.shadowA != nullptr) store_bf16x4(a.shadowA + off + col[c], o);
-    }
-  }
-  }  // latent loop
 }
 
 Hp make_hp(const sc_adam_hparams* h) {

@@ -147,6 +147,7 @@ class Trainer:
         self.final_k = self.cfg.sae.k
         self.best_loss = {name: float("inf") for name in self.local_hookpoints()}
         self.metrics: list[dict] = []
+        self._tokens_seen = 0  # upper bound of every num_tokens_since_fired counter
 
     # ------------------------------------------------------------------ state
     def load_state(self, path: str):
@@ -160,6 +161,7 @@ class Trainer:
             for k in self.local_hookpoints():
                 if k in rank_state["num_tokens_since_fired"]:
                     self.num_tokens_since_fired[k] = rank_state["num_tokens_since_fired"][k]
+                    self._tokens_seen = max(self._tokens_seen, int(self.num_tokens_since_fired[k].max()))
                 if not isinstance(rank_state["best_loss"], dict):
                     self.best_loss = rank_state["best_loss"]
                 elif k in rank_state["best_loss"]:
@@ -261,11 +263,15 @@ class Trainer:
                 if raw.cfg.normalize_decoder and not self.cfg.sae.transcode:
                     raw.set_decoder_norm_to_unit_norm()
 
+                # No counter can exceed the number of tokens this rank has trained on, so
+                # until that passes the threshold the mask is known to be empty and is not
+                # built (the forward would otherwise read its sum back to the host).
+                may_be_dead = self.cfg.auxk_alpha > 0 and self._tokens_seen > self.cfg.dead_feature_threshold
                 out = raw(
                     x=inputs,
                     y=outputs,
                     dead_mask=(self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold
-                               if self.cfg.auxk_alpha > 0 else None),
+                               if may_be_dead else None),
                 )
                 did_fire[name][out.latent_indices.flatten()] = True
                 self.maybe_all_reduce(did_fire[name], "max")
@@ -329,6 +335,7 @@ class Trainer:
                 for sae in self.saes.values():
                     sae.cfg.k = k
 
+                self._tokens_seen += num_tokens_in_step
                 with torch.no_grad():
                     for name, counts in self.num_tokens_since_fired.items():
                         counts += num_tokens_in_step
