@@ -76,7 +76,11 @@ class FusedEncoder(torch.autograd.Function):
                 wb = weight_bf16 if weight_bf16 is not None else (
                     weight.detach().contiguous() if weight.dtype == torch.bfloat16
                     else ops.cast_bf16(weight.detach().contiguous()))
-                preacts = ops.preacts_dense(xb, wb, bias)
+                if D % 8 == 0:
+                    # tensor-core GEMM with bias + ReLU in the epilogue, fp32 result
+                    preacts = ops.gemm_nt(xb, wb, bias=bias, relu=True, out_dtype=torch.float32)
+                else:
+                    preacts = ops.preacts_dense(xb, wb, bias)
                 x_saved = xb
             else:
                 preacts = ops.preacts_dense(x_c.float(), weight.detach().float(), bias)

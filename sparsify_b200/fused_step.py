@@ -44,7 +44,10 @@ class FusedSaeStep(torch.autograd.Function):
         if cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
             acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), k)
         else:
-            pre = ops.preacts_dense(xe, w_enc_src, b_enc.detach())
+            if lowp and D % 8 == 0:
+                pre = ops.gemm_nt(xe, w_enc_src, bias=b_enc.detach(), relu=True, out_dtype=torch.float32)
+            else:
+                pre = ops.preacts_dense(xe, w_enc_src, b_enc.detach())
             acts, idx = (ops.topk_rows if cfg.activation == "topk" else ops.groupmax_rows)(pre, k)
             del pre
         sae.wait_decoder()  # a decoder update may still be running under the encoder above
