@@ -293,13 +293,34 @@ def run_ours(a):
     launches = counter.n
 
     # ---- end to end: pinned host input -> device, step, loss back to host ----
-    xbuf = torch.empty_like(pool[0])
+    # Every step's input crosses PCIe inside the timed region. The copy of step t+1 is
+    # issued on a copy stream while step t computes (two device buffers), as an input
+    # pipeline would do; the loss of every step is read back to the host.
+    bufs = [torch.empty_like(pool[0]) for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    main = torch.cuda.current_stream(dev)
+
+    def fetch(t):
+        b = t % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[b])  # the step that last read this buffer is done
+            bufs[b].copy_(host_pool[t % len(host_pool)], non_blocking=True)
+            ready[b].record(copy_stream)
+
     sync()
+    for b in range(2):
+        consumed[b].record(main)
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
+    fetch(0)
     for t in range(a.steps):
-        xbuf.copy_(host_pool[t % len(host_pool)], non_blocking=True)
-        fvu = step(xbuf)
+        if t + 1 < a.steps:
+            fetch(t + 1)
+        main.wait_event(ready[t % 2])
+        fvu = step(bufs[t % 2])
+        consumed[t % 2].record(main)
         float(fvu.cpu())
     f1.record()
     sync()
