@@ -161,9 +161,14 @@ class FusedAdam(torch.optim.Optimizer):
         else:
             ops.rows_adam_(*args, **kw)
         if shard is not None:
-            for buf in (shadow_enc[0], shadow_dec[0]):  # everyone needs every row for the next forward
-                mine = buf[rows].clone()
-                dist.all_gather_into_tensor(buf.view(-1), mine.view(-1))
+            # everyone needs every row for the next forward: the encoder copy right away, the
+            # decoder copy only at decode time, so its all-gather runs under the encoder GEMM
+            mine = shadow_enc[0][rows].clone()
+            dist.all_gather_into_tensor(shadow_enc[0].view(-1), mine.view(-1))
+            mine_dec = shadow_dec[0][rows].clone()
+            sae.wait_decoder()
+            sae._dec_work = dist.all_gather_into_tensor(shadow_dec[0].view(-1), mine_dec.view(-1), async_op=True)
+            sae._dec_work_src = mine_dec  # keep the send buffer alive until the wait
             sae._masters_stale = True
         for _, cb in (shadow_dec, shadow_enc):
             if cb is not None:

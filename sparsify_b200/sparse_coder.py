@@ -86,6 +86,7 @@ class SparseCoder(nn.Module):
         self._pending: dict | None = None  # weight gradients in sparse form, awaiting the optimiser
         self._dec_unit_norm: tuple | None = None  # (data_ptr, version) at which W_dec rows had unit norm
         self._dec_event = None  # completion of a decoder update running on a side stream
+        self._dec_work = None  # asynchronous all-gather of the decoder's bf16 copy
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 
         self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
@@ -310,12 +311,16 @@ class SparseCoder(nn.Module):
             self.W_dec.data /= norm + eps
 
     def wait_decoder(self) -> None:
-        """Makes the current stream wait for a decoder update that FusedAdam
-        placed on its side stream (`overlap_decoder`). Call before reading
-        `W_dec` (or its bf16 copy) outside this package's own methods."""
+        """Makes the current stream wait for decoder work that FusedAdam left in
+        flight (an update on its side stream with `overlap_decoder`, the
+        all-gather of the bf16 copy in sharded mode). Call before reading `W_dec`
+        or its bf16 copy outside this package's own methods."""
         event, self._dec_event = self._dec_event, None
         if event is not None:
             torch.cuda.current_stream(self.device).wait_event(event)
+        work, self._dec_work = self._dec_work, None
+        if work is not None:
+            work.wait()  # asynchronous all-gather of the decoder's bf16 copy (sharded update)
 
     def materialize_pending(self) -> None:
         """Turns a deferred sparse weight gradient into dense .grad tensors
