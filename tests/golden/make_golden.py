@@ -254,6 +254,44 @@ def gen_trainer(sparsify):
                                      auxk_alpha=1 / 32, dead_feature_threshold=100))
 
 
+def gen_trainer_muon(sparsify):
+    """The reference Trainer with optimizer="muon" (Newton-Schulz in bf16 on the
+    two matrices, Adam on the biases) for a few steps on stored activations."""
+    from sparsify import SparseCoderConfig, TrainConfig, Trainer
+    steps, B, T, D, M, k = 4, 4, 16, 32, 256, 4
+    g = torch.Generator().manual_seed(6)
+    atoms = torch.nn.functional.normalize(torch.randn(512, D, generator=g), dim=1)
+    ids = torch.randint(0, 512, (steps, B, T, 6), generator=g)
+    coef = -torch.log1p(-torch.rand(steps, B, T, 6, generator=g))
+    acts = (atoms[ids] * coef.unsqueeze(-1)).sum(-2) + 0.05 * torch.randn(steps, B, T, D, generator=g)
+    model = FakeModel(acts)
+    dataset = [{"input_ids": torch.zeros(T, dtype=torch.long)} for _ in range(steps * B)]
+    fvus = []
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="muon", lr=2e-3,
+                          lr_warmup_steps=2, hookpoints=["layers.0"], log_to_wandb=False, save_dir=tmp,
+                          run_name="golden", save_every=10**9)
+        trainer = Trainer(cfg, dataset, model)
+        sae = trainer.saes["layers.0"]
+        init = dict(W_enc=sae.encoder.weight.detach().clone(), b_enc=sae.encoder.bias.detach().clone(),
+                    W_dec=sae.W_dec.detach().clone(), b_dec=sae.b_dec.detach().clone())
+        orig_forward = sae.forward
+
+        def recording_forward(*a, **kw):
+            out = orig_forward(*a, **kw)
+            fvus.append(out.fvu.detach().clone())
+            return out
+
+        sae.forward = recording_forward
+        trainer.fit()
+        t = dict(acts=acts, fvu=torch.stack(fvus))
+        for k_, v in init.items():
+            t[f"init.{k_}"] = v
+        for k_, v in dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec).items():
+            t[f"final.{k_}"] = v
+        save("trainer_muon", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=2e-3, warmup=2))
+
+
 def gen_muon(sparsify):
     from sparsify.muon import quintic_newtonschulz
     g = torch.Generator().manual_seed(3)
@@ -270,4 +308,5 @@ if __name__ == "__main__":
     gen_decoder(ref)
     gen_forward(ref)
     gen_trainer(ref)
+    gen_trainer_muon(ref)
     gen_muon(ref)

@@ -76,3 +76,31 @@ def test_bf16_trajectory_close_to_fp32(cuda_lib, tmp_path):
         runs[prec] = [row["fvu/layers.0"] for row in tr.metrics]
     for a, b in zip(runs["bf16"], runs["fp32"]):
         assert abs(a - b) < 0.02 * b, runs
+
+
+def test_muon_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
+    """optimizer="muon": Newton-Schulz on the tensor-core GEMM for the matrices,
+    fused Adam for the biases, against the reference Trainer's frozen run."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig, TrainConfig, Trainer
+    t, meta = load_golden("trainer_muon")
+    SparseCoder.default_precision = "fp32"
+    try:
+        cfg = TrainConfig(SparseCoderConfig(num_latents=meta["M"], k=meta["k"]), batch_size=meta["B"],
+                          optimizer="muon", lr=meta["lr"], lr_warmup_steps=meta["warmup"],
+                          hookpoints=["layers.0"], log_to_wandb=False, save_dir=str(tmp_path), run_name="run",
+                          save_every=10 ** 9)
+        trainer = Trainer(cfg, dataset(meta["steps"], meta["B"], meta["T"]), FakeModel(t["acts"], device="cuda"))
+    finally:
+        SparseCoder.default_precision = "bf16"
+    sae = trainer.saes["layers.0"]
+    with torch.no_grad():
+        sae.encoder.weight.copy_(t["init.W_enc"]); sae.encoder.bias.copy_(t["init.b_enc"])
+        sae.W_dec.copy_(t["init.W_dec"]); sae.b_dec.copy_(t["init.b_dec"])
+    trainer.fit()
+    fvus = [row["fvu/layers.0"] for row in trainer.metrics]
+    for got, want in zip(fvus, t["fvu"].tolist()):
+        assert abs(got - want) < 5e-3 * max(1.0, abs(want)), (fvus, t["fvu"].tolist())
+    # the orthogonalised updates are bf16 iterations: compare the parameters loosely
+    for name, p in (("W_enc", sae.encoder.weight), ("W_dec", sae.W_dec), ("b_enc", sae.encoder.bias),
+                    ("b_dec", sae.b_dec)):
+        assert rel_l2(p.detach(), t[f"final.{name}"]) < 1e-2, (name, rel_l2(p.detach(), t[f"final.{name}"]))
