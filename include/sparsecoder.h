@@ -211,7 +211,11 @@ typedef struct sc_adam_hparams {
  *      row normalisation W /= ||W|| + norm_eps (sparse_coder.py:273-279, which
  *      the reference applies before the next forward), bf16 shadow refresh.
  * The dense [M,D] gradients are never materialised. D % 4 == 0, D <= 4096.
- * hpA / hpB are host pointers. shadow pointers may be NULL. parts selects the
+ * hpA / hpB are host pointers. shadow pointers may be NULL. extraA (fp32
+ * [n,D]) with extra_rank (int32 [M]: row of extraA for latent m, or -1) adds
+ * dense gradient rows to the decoder gradient - the AuxK term of
+ * sparsify/sparse_coder.py:231-249, which touches dead latents only; both NULL
+ * when unused. parts selects the
  * matrices a launch updates: 1 = decoder (A) only, 2 = encoder (B) only, 3 =
  * both (the decoder half can then run on a second stream under the next
  * forward's encoder GEMM, which does not read W_dec). max_ctas > 0 caps the
@@ -225,7 +229,8 @@ int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
                  void* shadowA_bf16, int projectA, int normalizeA,
                  float norm_eps, const sc_adam_hparams* hpA, float* pB,
                  float* mB, float* vB, void* shadowB_bf16,
-                 const sc_adam_hparams* hpB, int parts, int max_ctas,
+                 const sc_adam_hparams* hpB, const float* extraA,
+                 const int32_t* extra_rank, int parts, int max_ctas,
                  void* stream);
 
 /* ---- dense bf16 GEMM on tcgen05 ---------------------------------------------

@@ -65,7 +65,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_rows_adam": (
         c_int,
         [P, P, c_int, P, P, c_int, P, P, c_int, I64, I64, P, P, P, P, c_int, c_int, c_float, P,
-         P, P, P, P, P, c_int, c_int, P],
+         P, P, P, P, P, P, P, c_int, c_int, P],
     ),
 }
 

@@ -41,6 +41,8 @@ struct Args {
   const int32_t* entries;
   const float* coefA;
   const float* coefB;
+  const float* extraA;       // optional dense gradient rows added to the decoder gradient
+  const int32_t* extra_rank; // [M]: row of extraA for latent m, or -1
   float *pA, *mA, *vA, *pB, *mB, *vB;
   __nv_bfloat16 *shadowA, *shadowB;
   int64_t D, M;
@@ -113,6 +115,19 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
 
     // ---- decoder row: project, Adam, normalise ----
     gather_rows<TA>(a.entries, lo, hi, a.k, a.coefA, vecA, D, g);
+    if (a.extraA != nullptr) {
+      const int32_t r = a.extra_rank[m];
+      if (r >= 0) {
+#pragma unroll
+        for (int c = 0; c < kNV; ++c) {
+          const int col = (c * kThreads + threadIdx.x) * 4;
+          if (col < D) {
+            const float4 x = *reinterpret_cast<const float4*>(a.extraA + (int64_t)r * D + col);
+            g[c].x += x.x; g[c].y += x.y; g[c].z += x.z; g[c].w += x.w;
+          }
+        }
+      }
+    }
     float4 pw[kNV];
     float dot = 0.f;
 #pragma unroll
@@ -173,8 +188,8 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
                             int vecB_dtype, int64_t M, int64_t D, float* pA, float* mA, float* vA,
                             void* shadowA_bf16, int projectA, int normalizeA, float norm_eps,
                             const sc_adam_hparams* hpA, float* pB, float* mB, float* vB,
-                            void* shadowB_bf16, const sc_adam_hparams* hpB, int parts, int max_ctas,
-                            void* stream) {
+                            void* shadowB_bf16, const sc_adam_hparams* hpB, const float* extraA,
+                            const int32_t* extra_rank, int parts, int max_ctas, void* stream) {
   SC_REQUIRE(M > 0 && D > 0 && k > 0 && M <= 0x7fffffffLL, "sc_rows_adam: bad shape");
   SC_REQUIRE(parts >= 1 && parts <= 3, "sc_rows_adam: parts must be 1 (decoder), 2 (encoder) or 3 (both)");
   SC_REQUIRE(row_ptr && entries && coefA && vecA && coefB && vecB && pA && mA && vA && pB && mB && vB && hpA && hpB,
@@ -191,6 +206,9 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
   a.pA = pA; a.mA = mA; a.vA = vA; a.pB = pB; a.mB = mB; a.vB = vB;
   a.shadowA = static_cast<__nv_bfloat16*>(shadowA_bf16);
   a.shadowB = static_cast<__nv_bfloat16*>(shadowB_bf16);
+  SC_REQUIRE((extraA == nullptr) == (extra_rank == nullptr), "sc_rows_adam: extraA and extra_rank go together");
+  SC_REQUIRE(extraA == nullptr || sc::aligned(extraA, 16), "sc_rows_adam: extraA must be 16-byte aligned");
+  a.extraA = extraA; a.extra_rank = extra_rank;
   a.parts = parts;
   a.M = M;
   a.D = D; a.k = k; a.projectA = projectA; a.normalizeA = normalizeA; a.norm_eps = norm_eps;

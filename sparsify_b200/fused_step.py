@@ -4,8 +4,8 @@ FVU, with a hand-scheduled backward.
 It computes what SparseCoder.forward composes from `fused_encoder`,
 `decoder_impl` and elementwise torch ops (sparsify/sparse_coder.py:205-271 with
 sparsify/fused_encoder.py:52-87 and sparsify/xformers.py:139-185 behind it), for
-the common case - no skip connection, no dead latents in this batch, no
-Multi-TopK, inputs that need no gradient - in fewer passes over memory:
+the common case - no skip connection, no Multi-TopK, inputs that need no
+gradient; AuxK in the bf16 / mixed precisions - in fewer passes over memory:
 
 * `x - b_dec` and the bf16 cast are one kernel;
 * the residual e = y - out and its squared sum are one kernel; the gradient of
@@ -32,7 +32,7 @@ from . import ops
 class FusedSaeStep(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, y: Tensor | None, W_enc: Tensor, b_enc: Tensor, W_dec: Tensor,
-                b_dec: Tensor, sae):
+                b_dec: Tensor, sae, dead_mask: Tensor | None = None, num_dead: int = 0):
         cfg = sae.cfg
         lowp = sae._lowp()
         comp = torch.bfloat16 if lowp else torch.float32
@@ -59,6 +59,36 @@ class FusedSaeStep(torch.autograd.Function):
         sse, e = ops.sq_err(target, out, want_diff=True)
         fvu = sse / tv
 
+        # ---- AuxK (sparsify/sparse_coder.py:231-249) in compact dense form: the dead
+        # latents' pre-activations are one small GEMM over the gathered dead rows of
+        # W_enc, the auxiliary reconstruction another over the dead rows of W_dec.
+        auxk = fvu.new_zeros(())
+        ctx.aux = None
+        if num_dead > 0:
+            dead_idx = dead_mask.nonzero().squeeze(1)
+            nd = int(dead_idx.numel())
+            pad = (-nd) % 8  # the GEMM wants a multiple of 8 in its contraction dimension
+            k_aux = target.shape[-1] // 2
+            scale = min(nd / k_aux, 1.0)
+            k_aux = min(k_aux, nd)
+            We = w_enc_src[dead_idx].to(torch.bfloat16)
+            Wd = w_dec_src[dead_idx].to(torch.bfloat16)
+            be = b_enc.detach()[dead_idx].to(torch.float32)
+            if pad:
+                We = torch.cat([We, We.new_zeros(pad, D)])
+                Wd = torch.cat([Wd, Wd.new_zeros(pad, D)])
+                be = torch.cat([be, be.new_zeros(pad)])
+            xe_b = xe if xe.dtype == torch.bfloat16 else xe.to(torch.bfloat16)
+            P = ops.gemm_nt(xe_b, We, bias=be, relu=True, out_dtype=torch.float32)  # [N, nd + pad]
+            if nd > k_aux:  # keep each row's k_aux largest, zero the rest
+                vals, sel = ops.topk_rows(P, k_aux)
+                P = torch.zeros_like(P).scatter_(1, sel, vals)
+            Pb = P.to(torch.bfloat16)
+            e_hat = ops.gemm_nt(Pb, ops.transpose_bf16(Wd), bias=b_dec.detach(), out_dtype=torch.float32)
+            sse_aux, diff = ops.sq_err(e_hat, e, want_diff=True)  # diff = e_hat - e
+            auxk = scale * sse_aux / tv
+            ctx.aux = (Pb, diff, dead_idx, nd, scale)
+
         ctx.save_for_backward(xe, idx, acts, e, tv)
         ctx.w_enc_src, ctx.w_dec_src = w_enc_src, w_dec_src
         ctx.shape = (M, D, k)
@@ -66,10 +96,10 @@ class FusedSaeStep(torch.autograd.Function):
         ctx.sae = sae
         ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(idx)
-        return out, acts, idx, fvu
+        return out, acts, idx, fvu, auxk
 
     @staticmethod
-    def backward(ctx, g_out, g_acts, g_idx, g_fvu):
+    def backward(ctx, g_out, g_acts, g_idx, g_fvu, g_auxk):
         xe, idx, acts, e, tv = ctx.saved_tensors
         M, D, k = ctx.shape
         dev = e.device
@@ -84,6 +114,21 @@ class FusedSaeStep(torch.autograd.Function):
         gacts = ops.embedding_bag_bwd_acts(idx, gout, ctx.w_dec_src) * scale
         if g_acts is not None:
             gacts = gacts + g_acts
+        # ---- AuxK: dense gradient rows for the dead latents, and its share of b_dec ----
+        extra = None
+        g_b_dec_aux = None
+        if ctx.aux is not None and g_auxk is not None:
+            Pb, diff, dead_idx, nd, aux_scale = ctx.aux
+            coef = (2.0 * aux_scale * g_auxk / tv).to(torch.float32)
+            g_ehat = (diff * coef).to(torch.bfloat16)
+            N = g_ehat.shape[0]
+            if N % 8 == 0:
+                rows = ops.gemm_nt(ops.transpose_bf16(Pb), ops.transpose_bf16(g_ehat), out_dtype=torch.float32)
+            else:
+                rows = Pb.float().T @ g_ehat.float()
+            extra = (dead_idx, rows[:nd].contiguous())
+            g_b_dec_aux = ops.weighted_colsum(diff) * coef
+
         row_ptr, entries = ops.csr_build(idx, M)
         sae = ctx.sae
         if sae._pending is not None:
@@ -95,18 +140,22 @@ class FusedSaeStep(torch.autograd.Function):
             # exchanged) as bf16 like every other gathered operand
             vecA = ops.prep_input(gout, None, torch.bfloat16) if sae.precision == "bf16" else gout
             sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, idx=idx, coefA=acts * scale,
-                                vecA=vecA, coefB=gacts, vecB=xe)
+                                vecA=vecA, coefB=gacts, vecB=xe, extra=extra)
             g_W_dec = g_W_enc = None
             g_b_enc = ops.csr_segment_sum(row_ptr, entries, gacts, M)
         else:
             res = ops.rows_accumulate(row_ptr, entries, k, M, D, acts * scale, gout,
                                       coefB=gacts, vecB=xe, biasB=True)
             g_W_dec, g_W_enc, g_b_enc = res["gradA"], res["gradB"], res["gbiasB"]
+            if extra is not None:
+                g_W_dec.index_add_(0, extra[0], extra[1])
         g_b_dec = ops.weighted_colsum(gout) * scale
         if not ctx.transcode:
             # minus the column sum of the encoder's input gradient
             g_b_dec = g_b_dec - ops.weighted_colsum(ctx.w_enc_src, g_b_enc)
-        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None
+        if g_b_dec_aux is not None:
+            g_b_dec = g_b_dec + g_b_dec_aux
+        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None, None, None
 
 
 def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
@@ -117,7 +166,7 @@ def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
         and sae.W_dec is not None
         and sae.W_skip is None
         and not sae.cfg.multi_topk
-        and num_dead == 0
+        and (num_dead == 0 or (sae._lowp() and x.shape[-1] % 8 == 0))
         and not x.requires_grad
         and x.shape[-1] % 4 == 0
         and sae.dtype == torch.float32

@@ -233,7 +233,8 @@ def csr_segment_sum(row_ptr: Tensor, entries: Tensor, coef: Tensor, M: int) -> T
 def rows_adam_(row_ptr: Tensor, entries: Tensor, k: int, coefA: Tensor, vecA: Tensor, coefB: Tensor,
                vecB: Tensor, *, pA: Tensor, mA: Tensor, vA: Tensor, shadowA: Tensor | None, projectA: bool,
                normalizeA: bool, norm_eps: float, hpA: dict, pB: Tensor, mB: Tensor, vB: Tensor,
-               shadowB: Tensor | None, hpB: dict, parts: int = 3, max_ctas: int = 0) -> None:
+               shadowB: Tensor | None, hpB: dict, parts: int = 3, max_ctas: int = 0,
+               extraA: Tensor | None = None, extra_rank: Tensor | None = None) -> None:
     """Sparse gradients of the decoder (A) and encoder (B) applied straight to the
     parameters: projection, Adam, decoder normalisation and bf16 shadows in one pass.
     hpA / hpB: dict(lr, beta1, beta2, eps, step)."""
@@ -250,7 +251,7 @@ def rows_adam_(row_ptr: Tensor, entries: Tensor, k: int, coefA: Tensor, vecA: Te
         call("sc_rows_adam", ptr(row_ptr), ptr(entries), int(k), ptr(coefA), ptr(vecA), dtype_code(vecA),
              ptr(coefB), ptr(vecB), dtype_code(vecB), int(M), int(D), ptr(pA), ptr(mA), ptr(vA), ptr(shadowA),
              int(bool(projectA)), int(bool(normalizeA)), float(norm_eps), ctypes.byref(ha), ptr(pB), ptr(mB),
-             ptr(vB), ptr(shadowB), ctypes.byref(hb), int(parts), int(max_ctas), _stream(pA))
+             ptr(vB), ptr(shadowB), ctypes.byref(hb), ptr(extraA), ptr(extra_rank), int(parts), int(max_ctas), _stream(pA))
 
 
 def total_variance(y: Tensor) -> Tensor:

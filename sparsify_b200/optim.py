@@ -137,6 +137,17 @@ class FusedAdam(torch.optim.Optimizer):
                   hpB=hps[1])
         args = (pend["row_ptr"], pend["entries"], pend["k"], pend["coefA"], pend["vecA"], pend["coefB"],
                 pend["vecB"])
+        extra = pend.get("extra")
+        if extra is not None:
+            # AuxK: dense gradient rows of the dead latents; a rank map tells the kernel which
+            # latent owns which row (restricted to this rank's slice when sharded)
+            dead_idx, extra_rows = extra
+            if shard is not None:
+                dist.all_reduce(extra_rows)  # dead sets are identical on every rank
+                extra_rows /= shard[1]
+            rank_map = torch.full((W_dec.shape[0],), -1, dtype=torch.int32, device=W_dec.device)
+            rank_map[dead_idx] = torch.arange(dead_idx.numel(), dtype=torch.int32, device=W_dec.device)
+            kw.update(extraA=extra_rows, extra_rank=rank_map[rows].contiguous())
         if getattr(sae, "_overlap_decoder", False):
             # Encoder half now; decoder half on a side stream, where it can run under the
             # next forward's encoder GEMM. Consumers of W_dec wait on the recorded event.
@@ -213,7 +224,7 @@ class FusedAdam(torch.optim.Optimizer):
         local = idx_all.to(torch.int64) - rank * per
         row_ptr, entries = ops.csr_build(local, per)
         return dict(row_ptr=row_ptr, entries=entries, k=k, coefA=coefA_all, vecA=vecA_all, coefB=coefB_all,
-                    vecB=vecB_all)
+                    vecB=vecB_all, extra=pend.get("extra"))
 
     @torch.no_grad()
     def step(self, closure=None):

@@ -236,10 +236,9 @@ class SparseCoder(nn.Module):
     ) -> ForwardOutput:
         num_dead = int(dead_mask.sum()) if dead_mask is not None else 0
         if self.fused and fused_supported(self, x, num_dead):
-            sae_out, top_acts, top_indices, fvu = FusedSaeStep.apply(
-                x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self)
-            zero = fvu.new_tensor(0.0)
-            return ForwardOutput(sae_out, top_acts, top_indices, fvu, zero, zero)
+            sae_out, top_acts, top_indices, fvu, auxk_loss = FusedSaeStep.apply(
+                x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead)
+            return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_tensor(0.0))
         need_dense = self.cfg.multi_topk or num_dead > 0
         top_acts, top_indices, pre_acts = self.encode(x, need_pre_acts=need_dense)
 
@@ -331,6 +330,8 @@ class SparseCoder(nn.Module):
         M, D = self.encoder.weight.shape
         res = ops.rows_accumulate(pend["row_ptr"], pend["entries"], pend["k"], M, D, pend["coefA"],
                                   pend["vecA"], coefB=pend["coefB"], vecB=pend["vecB"])
+        if pend.get("extra") is not None:
+            res["gradA"].index_add_(0, pend["extra"][0], pend["extra"][1])
         for p, g in ((self.W_dec, res["gradA"]), (self.encoder.weight, res["gradB"])):
             p.grad = g if p.grad is None else p.grad + g
 

@@ -191,3 +191,69 @@ def test_transcoder_skip_bf16_vs_oracle(cuda_lib):
     assert rel_l2(out.sae_out.detach(), t["sae_out"]) < 2e-2
     assert rel_l2(sae.W_skip.grad, t["grad.W_skip"]) < 3e-2
     assert rel_l2(sae.W_dec.grad, t["grad.W_dec"]) < 3e-2
+
+
+@pytest.mark.parametrize("n_dead", [100, 300])
+def test_auxk_fused_bf16_vs_oracle(cuda_lib, n_dead):
+    """AuxK inside the fused step (dead pre-activations and the auxiliary
+    reconstruction as small tensor-core GEMMs) against the oracle on the same
+    bf16-rounded operands; n_dead below and above k_aux = D/2."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    torch.manual_seed(0)
+    N, D, M, k, alpha = 512, 256, 4096, 32, 1 / 32
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(N, D, generator=g)
+    dead = torch.zeros(M, dtype=torch.bool)
+    dead[torch.randperm(M, generator=g)[:n_dead]] = True
+    with torch.no_grad():
+        sae.b_dec.copy_(0.1 * torch.randn(D, generator=g))
+        sae.encoder.bias.copy_(0.05 * torch.randn(M, generator=g))
+    out = sae(x.cuda(), dead_mask=dead.cuda())
+    (out.fvu + alpha * out.auxk_loss).backward()
+    rnd = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    params = dict(W_enc=sae.encoder.weight.detach().cpu(), b_enc=sae.encoder.bias.detach().cpu(),
+                  W_dec=sae.W_dec.detach().cpu(), b_dec=sae.b_dec.detach().cpu())
+    ref = O.sae_forward_backward(params, x, dead_mask=dead, cfg=O.OracleCfg(k=k), auxk_alpha=alpha,
+                                 round_operands=rnd)
+    assert float(ref.auxk_loss) > 0
+    assert abs(float(out.auxk_loss) - float(ref.auxk_loss)) < 1e-2 * float(ref.auxk_loss)
+    assert abs(float(out.fvu) - float(ref.fvu)) < 1e-3 * float(ref.fvu)
+    for pname, gt in (("W_enc", sae.encoder.weight.grad), ("b_enc", sae.encoder.bias.grad),
+                      ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad)):
+        assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
+    # the dead rows carry the auxiliary term
+    assert rel_l2(sae.W_dec.grad[dead.cuda()], ref.grads["W_dec"][dead]) < 1e-2
+
+
+def test_auxk_sparse_update_matches_dense_path(cuda_lib):
+    """With dead latents, the sparse fused update (extra dense rows inside
+    sc_rows_adam) equals the dense-gradient path."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    from sparsify_b200.optim import FusedAdam
+    N, D, M, k = 512, 256, 2048, 16
+    g = torch.Generator().manual_seed(33)
+    x = torch.randn(N, D, generator=g).cuda()
+    dead = torch.zeros(M, dtype=torch.bool)
+    dead[torch.randperm(M, generator=g)[:64]] = True
+    dead = dead.cuda()
+    results = []
+    for sparse in (False, True):
+        torch.manual_seed(0)
+        sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+        sae.precision = "mixed"
+        opt = FusedAdam(sae.parameters(), lr=1e-3)
+        sae.attach_optimizer(opt)
+        if sparse:
+            opt.enable_sparse_update(sae)
+        for _ in range(2):
+            sae.set_decoder_norm_to_unit_norm()
+            out = sae(x, dead_mask=dead)
+            assert float(out.auxk_loss) > 0
+            (out.fvu + out.auxk_loss / 32).backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        sae.set_decoder_norm_to_unit_norm()
+        results.append({n: p.detach().clone() for n, p in sae.named_parameters()})
+    for n in results[0]:
+        assert rel_l2(results[1][n], results[0][n]) < 1e-5, n
