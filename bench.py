@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens per step of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dead-frac", type=float, default=0.0,
+                    help="mark this fraction of the latents dead (fixed seed) so that the AuxK branch is "
+                         "active in every step; 0 = the natural state (no latent dead yet)")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone on random inputs of the given sizes instead of the step: "
                          "encode | decode | bwd_acts | csr | rows | adam | normalize | all")
@@ -53,8 +56,9 @@ def parse_args():
 
 
 def workload_name(a) -> str:
+    aux = f"AuxK active on {a.dead_frac:.0%} dead latents" if a.dead_frac > 0 else "AuxK enabled"
     return (f"SAE train step d_in={a.d} latents={a.latents} k={a.k} tokens/rank/step={a.tokens} "
-            f"bf16 operands fp32 accumulate, fwd+bwd+Adam, AuxK enabled")
+            f"bf16 operands fp32 accumulate, fwd+bwd+Adam, {aux}")
 
 
 def measured_peaks() -> dict:
@@ -235,12 +239,20 @@ def run_ours(a):
     grads = [p for p in sae.parameters()]
 
     tokens_seen = 0
+    fixed_dead = None
+    if a.dead_frac > 0:
+        gd = torch.Generator(device="cpu").manual_seed(7)
+        fixed_dead = torch.zeros(M, dtype=torch.bool)
+        fixed_dead[torch.randperm(M, generator=gd)[: int(a.dead_frac * M)]] = True
+        fixed_dead = fixed_dead.to(dev)
 
     def step(x):
         nonlocal tokens_seen
         sae.set_decoder_norm_to_unit_norm()
         # as the Trainer does: the dead mask is only built once a counter can have passed the threshold
         dead = since_fired > dead_threshold if tokens_seen > dead_threshold else None
+        if fixed_dead is not None:
+            dead = fixed_dead
         tokens_seen += N
         out = sae(x, dead_mask=dead)
         loss = out.fvu + alpha * out.auxk_loss
