@@ -4,8 +4,8 @@ FVU, with a hand-scheduled backward.
 It computes what SparseCoder.forward composes from `fused_encoder`,
 `decoder_impl` and elementwise torch ops (sparsify/sparse_coder.py:205-271 with
 sparsify/fused_encoder.py:52-87 and sparsify/xformers.py:139-185 behind it), for
-the common case - no skip connection, no Multi-TopK, inputs that need no
-gradient; AuxK in the bf16 / mixed precisions - in fewer passes over memory:
+the common case - no Multi-TopK, inputs that need no gradient; AuxK and the
+skip connection in the bf16 / mixed precisions - in fewer passes over memory:
 
 * `x - b_dec` and the bf16 cast are one kernel;
 * the residual e = y - out and its squared sum are one kernel; the gradient of
@@ -32,7 +32,8 @@ from . import ops
 class FusedSaeStep(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, y: Tensor | None, W_enc: Tensor, b_enc: Tensor, W_dec: Tensor,
-                b_dec: Tensor, sae, dead_mask: Tensor | None = None, num_dead: int = 0):
+                b_dec: Tensor, sae, dead_mask: Tensor | None = None, num_dead: int = 0,
+                W_skip: Tensor | None = None):
         cfg = sae.cfg
         lowp = sae._lowp()
         comp = torch.bfloat16 if lowp else torch.float32
@@ -54,6 +55,13 @@ class FusedSaeStep(torch.autograd.Function):
         gather_lp = sae.precision == "bf16" and W_dec.dtype == torch.float32
         w_dec_src = sae.shadow("W_dec") if gather_lp else W_dec.detach()
         out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())
+        ctx.skip = None
+        if W_skip is not None:
+            # out += x W_skip^T (sparsify/sparse_coder.py:221-222): tensor-core GEMM that
+            # accumulates onto the decode output in its epilogue
+            x_b = x if x.dtype == torch.bfloat16 else ops.prep_input(x, None, torch.bfloat16)
+            out = ops.gemm_nt(x_b, W_skip.detach().to(torch.bfloat16), beta=1.0, Cin=out, out_dtype=torch.float32)
+            ctx.skip = x_b
         target = (x if y is None else y.detach()).to(torch.float32)
         tv = ops.total_variance(target)
         sse, e = ops.sq_err(target, out, want_diff=True)
@@ -129,6 +137,17 @@ class FusedSaeStep(torch.autograd.Function):
             extra = (dead_idx, rows[:nd].contiguous())
             g_b_dec_aux = ops.weighted_colsum(diff) * coef
 
+        g_W_skip = None
+        if ctx.skip is not None and ctx.needs_input_grad[9]:
+            # grad W_skip = gout^T x = scale * (e^T)(x^T)^T, both operands put into K-major form
+            x_b = ctx.skip
+            g_b = gout.to(torch.bfloat16)
+            if x_b.shape[0] % 8 == 0:
+                g_W_skip = ops.gemm_nt(ops.transpose_bf16(g_b), ops.transpose_bf16(x_b), out_dtype=torch.float32)
+            else:
+                g_W_skip = g_b.float().T @ x_b.float()
+            g_W_skip = g_W_skip * scale
+
         row_ptr, entries = ops.csr_build(idx, M)
         sae = ctx.sae
         if sae._pending is not None:
@@ -155,7 +174,7 @@ class FusedSaeStep(torch.autograd.Function):
             g_b_dec = g_b_dec - ops.weighted_colsum(ctx.w_enc_src, g_b_enc)
         if g_b_dec_aux is not None:
             g_b_dec = g_b_dec + g_b_dec_aux
-        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None, None, None
+        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None, None, None, g_W_skip
 
 
 def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
@@ -164,7 +183,7 @@ def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
     return (
         x.is_cuda
         and sae.W_dec is not None
-        and sae.W_skip is None
+        and (sae.W_skip is None or (sae._lowp() and x.shape[-1] % 8 == 0))
         and not sae.cfg.multi_topk
         and (num_dead == 0 or (sae._lowp() and x.shape[-1] % 8 == 0))
         and not x.requires_grad

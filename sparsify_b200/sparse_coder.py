@@ -237,7 +237,8 @@ class SparseCoder(nn.Module):
         num_dead = int(dead_mask.sum()) if dead_mask is not None else 0
         if self.fused and fused_supported(self, x, num_dead):
             sae_out, top_acts, top_indices, fvu, auxk_loss = FusedSaeStep.apply(
-                x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead)
+                x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead,
+                self.W_skip)
             return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_tensor(0.0))
         need_dense = self.cfg.multi_topk or num_dead > 0
         top_acts, top_indices, pre_acts = self.encode(x, need_pre_acts=need_dense)

@@ -257,3 +257,32 @@ def test_auxk_sparse_update_matches_dense_path(cuda_lib):
         results.append({n: p.detach().clone() for n, p in sae.named_parameters()})
     for n in results[0]:
         assert rel_l2(results[1][n], results[0][n]) < 1e-5, n
+
+
+def test_transcoder_skip_fused_vs_oracle(cuda_lib):
+    """Transcoder (y != x, no b_dec subtraction) with a dense skip connection on
+    the fused path, against the oracle on the same bf16-rounded operands."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    torch.manual_seed(0)
+    N, D, M, k = 512, 256, 4096, 64
+    cfg = SparseCoderConfig(num_latents=M, k=k, transcode=True, skip_connection=True)
+    sae = SparseCoder(D, cfg, device="cuda", dtype=torch.float32)
+    g = torch.Generator().manual_seed(41)
+    x, y = torch.randn(N, D, generator=g), torch.randn(N, D, generator=g)
+    with torch.no_grad():
+        sae.W_dec.copy_(0.1 * torch.randn(M, D, generator=g))
+        sae.W_skip.copy_(0.05 * torch.randn(D, D, generator=g))
+        sae.encoder.bias.copy_(0.05 * torch.randn(M, generator=g))
+    out = sae(x.cuda(), y.cuda())
+    out.fvu.backward()
+    rnd = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    params = dict(W_enc=sae.encoder.weight.detach().cpu(), b_enc=sae.encoder.bias.detach().cpu(),
+                  W_dec=sae.W_dec.detach().cpu(), b_dec=sae.b_dec.detach().cpu(),
+                  W_skip=rnd(sae.W_skip.detach().cpu()))
+    ref = O.sae_forward_backward(params, rnd(x), y, cfg=O.OracleCfg(k=k, transcode=True, skip_connection=True),
+                                 round_operands=rnd)
+    assert abs(float(out.fvu) - float(ref.fvu)) < 1e-3 * float(ref.fvu)
+    assert rel_l2(out.sae_out.detach(), ref.sae_out) < 1e-3
+    for pname, gt in (("W_enc", sae.encoder.weight.grad), ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad),
+                      ("W_skip", sae.W_skip.grad)):
+        assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
