@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens per step of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--transcode", action="store_true",
+                    help="transcoder workload: target y = W2 gelu(W1 layernorm(x)) with seeded W1 [3.5d, d], "
+                         "W2 [d, 3.5d], a learned dense skip connection, decoder initialised at zero")
     ap.add_argument("--dead-frac", type=float, default=0.0,
                     help="mark this fraction of the latents dead (fixed seed) so that the AuxK branch is "
                          "active in every step; 0 = the natural state (no latent dead yet)")
@@ -57,6 +60,9 @@ def parse_args():
 
 def workload_name(a) -> str:
     aux = f"AuxK active on {a.dead_frac:.0%} dead latents" if a.dead_frac > 0 else "AuxK enabled"
+    if a.transcode:
+        return (f"transcoder train step d_in={a.d} latents={a.latents} k={a.k} tokens/rank/step={a.tokens} "
+                f"dense skip connection, bf16 operands fp32 accumulate, fwd+bwd+Adam, {aux}")
     return (f"SAE train step d_in={a.d} latents={a.latents} k={a.k} tokens/rank/step={a.tokens} "
             f"bf16 operands fp32 accumulate, fwd+bwd+Adam, {aux}")
 
@@ -214,7 +220,8 @@ def run_ours(a):
 
     N, D, M, k = a.tokens, a.d, a.latents, a.k
     torch.manual_seed(0)  # identical replicas on every rank (sparsify/trainer.py:80-87)
-    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device=dev, dtype=torch.float32)
+    sae_cfg = SparseCoderConfig(num_latents=M, k=k, transcode=a.transcode, skip_connection=a.transcode)
+    sae = SparseCoder(D, sae_cfg, device=dev, dtype=torch.float32)
     lr = 2e-4 / (M / 2 ** 14) ** 0.5
     opt = FusedAdam(sae.parameters(), lr=lr)
     sae.attach_optimizer(opt)
@@ -229,13 +236,26 @@ def run_ours(a):
     pool = [gen.batch(N, batch_seed(t, rank, world), torch.bfloat16) for t in range(4)]
     del gen
     torch.cuda.empty_cache()
+    targets = None
+    if a.transcode:
+        # the module being transcoded: a seeded MLP applied to the layer-normed input
+        gw = torch.Generator(device=dev).manual_seed(2001)
+        H = int(3.5 * D)
+        W1 = (torch.randn(H, D, device=dev, generator=gw) / D ** 0.5).bfloat16()
+        W2 = (torch.randn(D, H, device=dev, generator=gw) / H ** 0.5).bfloat16()
+        ln = torch.nn.functional.layer_norm
+        targets = [(torch.nn.functional.gelu(ln(b.float(), (D,)).bfloat16() @ W1.T) @ W2.T).bfloat16() for b in pool]
+        del W1, W2
+        torch.cuda.empty_cache()
     host_pool = [b.cpu().pin_memory() for b in pool]
     with torch.no_grad():
-        mean = pool[0].float().mean(0)
+        mean = (targets[0] if a.transcode else pool[0]).float().mean(0)
         if world > 1:
             dist.all_reduce(mean)
             mean /= world
         sae.b_dec.copy_(mean)
+        if a.transcode:  # centre the pre-activations (sparsify/trainer.py:398-401)
+            sae.encoder.bias.copy_(-pool[0].float().mean(0) @ sae.encoder.weight.T)
     grads = [p for p in sae.parameters()]
 
     tokens_seen = 0
@@ -246,15 +266,16 @@ def run_ours(a):
         fixed_dead[torch.randperm(M, generator=gd)[: int(a.dead_frac * M)]] = True
         fixed_dead = fixed_dead.to(dev)
 
-    def step(x):
+    def step(x, y=None):
         nonlocal tokens_seen
-        sae.set_decoder_norm_to_unit_norm()
+        if not a.transcode:
+            sae.set_decoder_norm_to_unit_norm()
         # as the Trainer does: the dead mask is only built once a counter can have passed the threshold
         dead = since_fired > dead_threshold if tokens_seen > dead_threshold else None
         if fixed_dead is not None:
             dead = fixed_dead
         tokens_seen += N
-        out = sae(x, dead_mask=dead)
+        out = sae(x, y, dead_mask=dead)
         loss = out.fvu + alpha * out.auxk_loss
         loss.backward()
         if world > 1:
@@ -280,8 +301,9 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    tgt = (lambda t: targets[t % len(targets)]) if a.transcode else (lambda t: None)
     for t in range(max(a.warmup, 3)):
-        step(pool[t % len(pool)])
+        step(pool[t % len(pool)], tgt(t))
     sync()
 
     # ---- device-resident timing -------------------------------------------
@@ -294,7 +316,7 @@ def run_ours(a):
     sync()
     e0.record()
     for t in range(a.steps):
-        step(pool[t % len(pool)])
+        step(pool[t % len(pool)], tgt(t))
     e1.record()
     sync()
     clocks = sampler.stop() if rank == 0 else None
@@ -331,7 +353,7 @@ def run_ours(a):
         if t + 1 < a.steps:
             fetch(t + 1)
         main.wait_event(ready[t % 2])
-        fvu = step(bufs[t % 2])
+        fvu = step(bufs[t % 2], tgt(t))
         consumed[t % 2].record(main)
         float(fvu.cpu())
     f1.record()
