@@ -86,6 +86,20 @@ struct RowState {
 
 constexpr int kGroup = 8;
 
+// v[i] for a run-time i: a five-level select tree (registers cannot be indexed).
+__device__ __forceinline__ float pick32(const float (&v)[32], int i) {
+  float a[16], b[8], c[4], d[2];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) a[j] = (i & 1) ? v[2 * j + 1] : v[2 * j];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) b[j] = (i & 2) ? a[2 * j + 1] : a[2 * j];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) c[j] = (i & 4) ? b[2 * j + 1] : b[2 * j];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) d[j] = (i & 8) ? c[2 * j + 1] : c[2 * j];
+  return (i & 16) ? d[1] : d[0];
+}
+
 // Minimum of group g (entries g*8 .. g*8+7, those below k) with its position.
 // All eight loads are issued before the first comparison.
 __device__ __forceinline__ void group_min(const float* lv, int k, int g, float& best, int& pos) {
@@ -335,23 +349,25 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           for (int i = 0; i < 32; ++i) m |= (v[i] > st.thr_cmp ? 1u : 0u) << i;
           const int valid = ncols - c * 32;  // columns of this chunk inside the matrix
           if (valid < 32) m &= valid <= 0 ? 0u : ((1u << valid) - 1u);
-          const unsigned colmask = __reduce_or_sync(0xffffffffu, m);
-          if (colmask == 0) continue;
-          // Pass 2: rows with a marked column insert it into their own list.
+          // Pass 2: every row walks its own marked columns (ascending), so the loop
+          // runs as often as the busiest row has candidates, not once per marked column.
           const uint16_t rel0 = (uint16_t)(tile_col0 - strip_col0 + c * 32);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (((colmask >> i) & 1u) == 0) continue;  // warp-uniform skip
+          while (__any_sync(0xffffffffu, m != 0)) {
             ++n_cols;
-            if (((m >> i) & 1u) && v[i] > st.thr_cmp) {
-              if (st.cnt + 1 < k) {  // free slots left: append in line
-                lv[st.cnt * BM] = fmaxf(v[i], 0.f);
-                li[st.cnt * BM] = (uint16_t)(rel0 + i);
-                ++st.cnt;
-              } else {
-                st = list_insert(lv, li, gv, gp, k, v[i], (uint16_t)(rel0 + i), tau, st);
+            if (m != 0) {
+              const int i = __ffs(m) - 1;
+              m &= m - 1;
+              const float val = pick32(v, i);
+              if (val > st.thr_cmp) {
+                if (st.cnt + 1 < k) {  // free slots left: append in line
+                  lv[st.cnt * BM] = fmaxf(val, 0.f);
+                  li[st.cnt * BM] = (uint16_t)(rel0 + i);
+                  ++st.cnt;
+                } else {
+                  st = list_insert(lv, li, gv, gp, k, val, (uint16_t)(rel0 + i), tau, st);
+                }
+                ++n_ins;
               }
-              ++n_ins;
             }
           }
         }
