@@ -52,8 +52,8 @@ class FusedAdam(torch.optim.Optimizer):
         stream, so that it may overlap the next forward's encoder GEMM (which does
         not read W_dec); readers of W_dec inside this package wait for it, code
         that reads `sae.W_dec` directly must call `sae.wait_decoder()` first.
-        (Measured on B200 at d=4096, 131072 latents: 0.5 ms of 28 with the full
-        grid, a loss with a small persistent grid; off by default.)
+        (Measured on B200 at d=4096, 131072 latents: no gain - the background
+        kernel slows the encoder by more than it hides; off by default.)
         Returns whether it was enabled."""
         W = sae.encoder.weight
         ok = (sae.W_dec is not None and W.is_cuda and W.dtype == torch.float32 and W.shape[1] % 4 == 0

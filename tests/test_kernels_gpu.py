@@ -159,6 +159,9 @@ def test_topk_rows_masked(cuda_lib):
     (384, 1024, 4352, 32),   # ragged last column tile (4352 = 17 * 256)
     (130, 72, 520, 64),      # D not a multiple of 64, M not a multiple of 256
     (1024, 4096, 16384, 32), # config-1 width, reduced N and M
+    (77, 64, 300, 5),        # k not a multiple of the list group size
+    (256, 128, 2048, 128),   # largest k of the fused path (Multi-TopK of k=32)
+    (64, 64, 40, 40),        # k == M: every latent is selected
 ])
 def test_encoder_tc_vs_oracle(cuda_lib, N, D, M, k):
     from sparsify_b200 import ops
