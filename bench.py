@@ -383,9 +383,9 @@ def run_ours(a):
                     "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops"], "peak_source": peaks["source"],
                     "ms_per_launch": enc_ms,
-                    # dram__bytes_read + write of one launch: 359.5 MB measured by ncu on the
+                    # dram__bytes_read + write of one launch: 344.4 MB measured by ncu on the
                     # N=4096, M=32768 case (profiles/), scaled by the units of this launch
-                    "traffic": 359.5e6 * (N / 4096) * (M / 32768) if D == 4096 else None}
+                    "traffic": 344.4e6 * (N / 4096) * (M / 32768) if D == 4096 else None}
         gs_bytes = 3 * (N * k * D * 2) + 3 * N * D * 4 + N * k * 12 + 2 * M * D * 4 + 2 * N * D * 4 + N * k * 12
         step_roof_ms = max(flops / (peaks["tflops"] * 1e12), gs_bytes / (peaks["hbm"] * 1e9)) * 1e3
         line = {
