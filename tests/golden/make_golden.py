@@ -27,9 +27,9 @@ HERE = Path(__file__).resolve().parent
 
 
 def import_reference():
-    root = os.environ.get("SPARSIFY_REF", "/root/reference")
-    if not Path(root, "sparsify", "fused_encoder.py").exists():
-        raise SystemExit(f"reference tree not found at {root}; set SPARSIFY_REF")
+    root = os.environ.get("SPARSIFY_REF", "")
+    if not root or not Path(root, "sparsify", "fused_encoder.py").exists():
+        raise SystemExit("set SPARSIFY_REF to a checkout of EleutherAI/sparsify v1.3.0")
     os.environ["SPARSIFY_DISABLE_TRITON"] = "1"
     import transformers  # noqa: F401  (must precede the accelerate stub)
 
