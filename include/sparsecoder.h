@@ -103,11 +103,24 @@ int sc_embedding_bag_fwd(const int64_t* idx, const float* acts, const void* W,
                          int w_dtype, const float* bias, int64_t N, int64_t D,
                          int64_t M, int k, float* out, void* stream);
 
-/* grad_acts[n,j] = dot(grad_out[n,:], W[idx[n,j],:])
+/* grad_acts[n,j] = dot(grad_out[n,:], W[idx[n,j],:]); grad_out fp32 or bf16.
  * sparsify/xformers.py:125-131 (per_sample_weights_grad). */
-int sc_embedding_bag_bwd_acts(const int64_t* idx, const float* grad_out,
-                              const void* W, int w_dtype, int64_t N, int64_t D,
-                              int64_t M, int k, float* grad_acts, void* stream);
+int sc_embedding_bag_bwd_acts(const int64_t* idx, const void* grad_out,
+                              int g_dtype, const void* W, int w_dtype, int64_t N,
+                              int64_t D, int64_t M, int k, float* grad_acts,
+                              void* stream);
+
+/* Decode fused with the residual of the FVU loss: out = bias + sum_j acts W[idx],
+ * e = y - out, *sse = sum e^2 (device fp32 scalar, fixed summation order). Each
+ * of out (fp32), e_f32, e_bf16 is written when non-NULL. y is fp32 or bf16.
+ * D % 4 == 0. ws: sc_decode_residual_workspace_bytes(N) bytes.
+ * sparsify/sparse_coder.py:198-202,225,253 in one pass. */
+size_t sc_decode_residual_workspace_bytes(int64_t N);
+int sc_decode_residual(const int64_t* idx, const float* acts, const void* W,
+                       int w_dtype, const float* bias, const void* y,
+                       int y_dtype, int64_t N, int64_t D, int64_t M, int k,
+                       float* out, float* e_f32, void* e_bf16, float* sse,
+                       void* ws, size_t ws_bytes, void* stream);
 
 /* Latent-major CSR of the [N,k] index matrix: row_ptr[M+1], entries[N*k]
  * (flat position n*k+j, ascending inside each latent).
@@ -159,11 +172,11 @@ int sc_csr_segment_sum(const int32_t* row_ptr, const int32_t* entries,
 /* ---- losses -------------------------------------------------------------
  * sparsify/sparse_coder.py:225-228,253-254:
  *   total_variance = sum((y - mean_0(y))^2);  e = y - out;  l2 = sum(e^2).
- * sc_total_variance writes *tv (device fp32); ws holds
+ * sc_total_variance writes *tv (device fp32); y is fp32 or bf16; ws holds
  * sc_loss_workspace_bytes(D) bytes. */
 size_t sc_loss_workspace_bytes(int64_t D);
-int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv, void* ws,
-                      size_t ws_bytes, void* stream);
+int sc_total_variance(const void* y, int y_dtype, int64_t N, int64_t D,
+                      float* tv, void* ws, size_t ws_bytes, void* stream);
 /* sse[0] = sum((a - b)^2) over n elements (device fp32 scalar);
  * if diff != NULL also writes diff = a - b. */
 int sc_sq_err(const float* a, const float* b, int64_t n, float* diff,

@@ -41,7 +41,12 @@ SIGNATURES: dict[str, tuple] = {
     "sc_encode_topk_workspace_bytes": (c_size_t, [I64, I64, I64, c_int]),
     "sc_encode_topk": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, c_size_t, P, P]),
     "sc_embedding_bag_fwd": (c_int, [P, P, P, c_int, P, I64, I64, I64, c_int, P, P]),
-    "sc_embedding_bag_bwd_acts": (c_int, [P, P, P, c_int, I64, I64, I64, c_int, P, P]),
+    "sc_embedding_bag_bwd_acts": (c_int, [P, P, c_int, P, c_int, I64, I64, I64, c_int, P, P]),
+    "sc_decode_residual_workspace_bytes": (c_size_t, [I64]),
+    "sc_decode_residual": (
+        c_int,
+        [P, P, P, c_int, P, P, c_int, I64, I64, I64, c_int, P, P, P, P, P, c_size_t, P],
+    ),
     "sc_csr_workspace_bytes": (c_size_t, [I64]),
     "sc_csr_build": (c_int, [P, I64, c_int, I64, P, P, P, c_size_t, P]),
     "sc_csr_build_noalloc": (c_int, [P, I64, c_int, I64, P, P, P]),
@@ -50,7 +55,7 @@ SIGNATURES: dict[str, tuple] = {
         [P, P, c_int, P, P, c_int, P, P, P, P, c_int, P, P, I64, I64, I64, I64, P],
     ),
     "sc_loss_workspace_bytes": (c_size_t, [I64]),
-    "sc_total_variance": (c_int, [P, I64, I64, P, P, c_size_t, P]),
+    "sc_total_variance": (c_int, [P, c_int, I64, I64, P, P, c_size_t, P]),
     "sc_sq_err": (c_int, [P, P, I64, P, P, P, c_size_t, P]),
     "sc_weighted_colsum": (c_int, [P, c_int, P, I64, I64, P, P, c_size_t, P]),
     "sc_normalize_rows": (c_int, [P, I64, I64, c_float, P, P]),

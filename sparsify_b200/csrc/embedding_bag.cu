@@ -77,9 +77,86 @@ bag_fwd_kernel(const int64_t* __restrict__ idx, const float* __restrict__ acts,
   }
 }
 
-template <typename WT, int VEC>
+// Decode fused with the residual: out = bias + sum_j acts W[idx], e = y - out,
+// partial[n] = sum_d e^2. Writes whichever of out (fp32), e (fp32), e (bf16) is
+// non-null, so the forward needs no separate residual / squared-error / cast pass.
+template <typename WT, typename YT>
 __global__ void __launch_bounds__(kBagThreads)
-bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const float* __restrict__ gout,
+decode_residual_kernel(const int64_t* __restrict__ idx, const float* __restrict__ acts,
+                       const WT* __restrict__ W, const float* __restrict__ bias, const YT* __restrict__ y,
+                       int64_t D, int64_t M, int k, float* __restrict__ out, float* __restrict__ e32,
+                       __nv_bfloat16* __restrict__ e16, float* __restrict__ partial) {
+  extern __shared__ unsigned char smem_raw[];
+  int64_t* s_idx = reinterpret_cast<int64_t*>(smem_raw);
+  float* s_act = reinterpret_cast<float*>(s_idx + k);
+  __shared__ float scratch[33];
+  const int64_t n = blockIdx.x;
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    int64_t r = idx[n * k + j];
+    float a = acts[n * k + j];
+    if (r < 0 || r >= M) { r = 0; a = 0.f; }
+    s_idx[j] = r;
+    s_act[j] = a;
+  }
+  __syncthreads();
+  constexpr int NCH = 4;
+  const int64_t sweep = (int64_t)blockDim.x * 4 * NCH;
+  float sq = 0.f;
+  for (int64_t base = 0; base < D; base += sweep) {
+    float4 acc[NCH];
+    int64_t col[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      col[c] = base + ((int64_t)c * blockDim.x + threadIdx.x) * 4;
+      acc[c] = (bias != nullptr && col[c] < D) ? __ldg(reinterpret_cast<const float4*>(bias + col[c]))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll 4
+    for (int j = 0; j < k; ++j) {
+      const WT* row = W + s_idx[j] * D;
+      const float a = s_act[j];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        if (col[c] < D) {
+          const float4 w = sc::load4<WT>(row + col[c]);
+          acc[c].x = fmaf(a, w.x, acc[c].x); acc[c].y = fmaf(a, w.y, acc[c].y);
+          acc[c].z = fmaf(a, w.z, acc[c].z); acc[c].w = fmaf(a, w.w, acc[c].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (col[c] < D) {
+        const float4 t = sc::load4<YT>(y + n * D + col[c]);
+        const float4 e = make_float4(t.x - acc[c].x, t.y - acc[c].y, t.z - acc[c].z, t.w - acc[c].w);
+        sq += e.x * e.x + e.y * e.y + e.z * e.z + e.w * e.w;
+        if (out != nullptr) *reinterpret_cast<float4*>(out + n * D + col[c]) = acc[c];
+        if (e32 != nullptr) *reinterpret_cast<float4*>(e32 + n * D + col[c]) = e;
+        if (e16 != nullptr) {
+          uint2 pk;
+          pk.x = sc::pack_bf16x2(e.x, e.y);
+          pk.y = sc::pack_bf16x2(e.z, e.w);
+          *reinterpret_cast<uint2*>(e16 + n * D + col[c]) = pk;
+        }
+      }
+    }
+  }
+  sq = sc::block_sum(sq, scratch);
+  if (threadIdx.x == 0) partial[n] = sq;
+}
+
+__global__ void __launch_bounds__(1024)
+sum_partials_kernel(const float* __restrict__ partial, int64_t n, float* __restrict__ out) {
+  __shared__ float scratch[33];
+  float acc = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
+  acc = sc::block_sum(acc, scratch);
+  if (threadIdx.x == 0) *out = acc;
+}
+
+template <typename WT, typename GT, int VEC>
+__global__ void __launch_bounds__(kBagThreads)
+bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const GT* __restrict__ gout,
                     const WT* __restrict__ W, int64_t N, int64_t D, int64_t M, int k,
                     float* __restrict__ gacts) {
   extern __shared__ unsigned char smem_raw[];
@@ -91,7 +168,7 @@ bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const float* __restrict__ g
   const int64_t n = blockIdx.x;
 
   for (int64_t c = threadIdx.x; c < Dpad; c += blockDim.x)
-    s_g[c] = c < D ? __ldg(gout + n * D + c) : 0.f;
+    s_g[c] = c < D ? sc::load1<GT>(gout + n * D + c) : 0.f;
   __syncthreads();
 
   constexpr int JB = 4;  // rows in flight per iteration
@@ -165,10 +242,10 @@ extern "C" int sc_embedding_bag_fwd(const int64_t* idx, const float* acts, const
   return SC_OK;
 }
 
-extern "C" int sc_embedding_bag_bwd_acts(const int64_t* idx, const float* grad_out,
+extern "C" int sc_embedding_bag_bwd_acts(const int64_t* idx, const void* grad_out, int g_dtype,
                                          const void* W, int w_dtype, int64_t N, int64_t D,
                                          int64_t M, int k, float* grad_acts, void* stream) {
-  SC_REQUIRE(sc::valid_dtype(w_dtype), "sc_embedding_bag_bwd_acts: bad w_dtype %d", w_dtype);
+  SC_REQUIRE(sc::valid_dtype(w_dtype) && sc::valid_dtype(g_dtype), "sc_embedding_bag_bwd_acts: bad dtype");
   SC_REQUIRE(N >= 0 && D > 0 && M > 0 && k > 0, "sc_embedding_bag_bwd_acts: bad shape");
   if (N == 0) return SC_OK;
   SC_REQUIRE(idx && grad_out && W && grad_acts, "sc_embedding_bag_bwd_acts: null pointer");
@@ -180,19 +257,62 @@ extern "C" int sc_embedding_bag_bwd_acts(const int64_t* idx, const float* grad_o
   const bool vec = (D % 4 == 0) && sc::aligned(W, 16);
   dim3 grid((unsigned)N), block(kBagThreads);
   cudaStream_t st = sc::as_stream(stream);
-#define SC_LAUNCH_BWD(WT, VEC)                                                              \
+#define SC_LAUNCH_BWD(WT, GT, VEC)                                                          \
   do {                                                                                      \
-    auto kern = bag_bwd_acts_kernel<WT, VEC>;                                               \
+    auto kern = bag_bwd_acts_kernel<WT, GT, VEC>;                                           \
     if (smem > 48 * 1024)                                                                   \
       SC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    kern<<<grid, block, smem, st>>>(idx, grad_out, static_cast<const WT*>(W), N, D, M, k, grad_acts); \
+    kern<<<grid, block, smem, st>>>(idx, static_cast<const GT*>(grad_out), static_cast<const WT*>(W), N, D, M, k, grad_acts); \
+  } while (0)
+#define SC_LAUNCH_BWD_G(WT, VEC)                                                            \
+  do {                                                                                      \
+    if (g_dtype == SC_F32) SC_LAUNCH_BWD(WT, float, VEC); else SC_LAUNCH_BWD(WT, __nv_bfloat16, VEC); \
   } while (0)
   if (w_dtype == SC_F32) {
-    if (vec) SC_LAUNCH_BWD(float, 4); else SC_LAUNCH_BWD(float, 1);
+    if (vec) SC_LAUNCH_BWD_G(float, 4); else SC_LAUNCH_BWD_G(float, 1);
   } else {
-    if (vec) SC_LAUNCH_BWD(__nv_bfloat16, 4); else SC_LAUNCH_BWD(__nv_bfloat16, 1);
+    if (vec) SC_LAUNCH_BWD_G(__nv_bfloat16, 4); else SC_LAUNCH_BWD_G(__nv_bfloat16, 1);
   }
+#undef SC_LAUNCH_BWD_G
 #undef SC_LAUNCH_BWD
   SC_CHECK_LAUNCH("sc_embedding_bag_bwd_acts");
+  return SC_OK;
+}
+
+extern "C" size_t sc_decode_residual_workspace_bytes(int64_t N) {
+  return N > 0 ? (size_t)N * sizeof(float) : 0;
+}
+
+extern "C" int sc_decode_residual(const int64_t* idx, const float* acts, const void* W, int w_dtype,
+                                  const float* bias, const void* y, int y_dtype, int64_t N, int64_t D,
+                                  int64_t M, int k, float* out, float* e_f32, void* e_bf16, float* sse,
+                                  void* ws, size_t ws_bytes, void* stream) {
+  SC_REQUIRE(sc::valid_dtype(w_dtype) && sc::valid_dtype(y_dtype), "sc_decode_residual: bad dtype");
+  SC_REQUIRE(N > 0 && D > 0 && M > 0 && k > 0 && N <= 0x7fffffffLL, "sc_decode_residual: bad shape");
+  SC_REQUIRE(idx && acts && W && y && sse && ws, "sc_decode_residual: null pointer");
+  SC_REQUIRE(D % 4 == 0, "sc_decode_residual: D=%lld must be a multiple of 4", (long long)D);
+  const void* al[] = {W, y, out, e_f32, e_bf16, bias};
+  for (const void* q : al) SC_REQUIRE(q == nullptr || sc::aligned(q, 16), "sc_decode_residual: pointers must be 16-byte aligned");
+  if (ws_bytes < sc_decode_residual_workspace_bytes(N))
+    return sc::fail(SC_ERR_WORKSPACE, "sc_decode_residual: workspace %zu < %zu", ws_bytes,
+                    sc_decode_residual_workspace_bytes(N));
+  const size_t smem = (size_t)k * (sizeof(int64_t) + sizeof(float));
+  SC_REQUIRE(smem <= 40 * 1024, "sc_decode_residual: k=%d too large", k);
+  float* partial = static_cast<float*>(ws);
+  cudaStream_t st = sc::as_stream(stream);
+  dim3 grid((unsigned)N), block(kBagThreads);
+  using bf16 = __nv_bfloat16;
+  bf16* e16 = static_cast<bf16*>(e_bf16);
+#define SC_LAUNCH_DR(WT, YT)                                                                 \
+  decode_residual_kernel<WT, YT><<<grid, block, smem, st>>>(idx, acts, static_cast<const WT*>(W), bias, \
+      static_cast<const YT*>(y), D, M, k, out, e_f32, e16, partial)
+  if (w_dtype == SC_F32 && y_dtype == SC_F32) SC_LAUNCH_DR(float, float);
+  else if (w_dtype == SC_F32) SC_LAUNCH_DR(float, bf16);
+  else if (y_dtype == SC_F32) SC_LAUNCH_DR(bf16, float);
+  else SC_LAUNCH_DR(bf16, bf16);
+#undef SC_LAUNCH_DR
+  SC_CHECK_LAUNCH("sc_decode_residual");
+  sum_partials_kernel<<<1, 1024, 0, st>>>(partial, N, sse);
+  SC_CHECK_LAUNCH("sum_partials");
   return SC_OK;
 }

@@ -72,15 +72,15 @@ __global__ void colsum_finish_kernel(const float* __restrict__ partial, float sc
 }
 
 // block partials of sum((a[i] - b[i % D])^2) when BROADCAST, else sum((a[i]-b[i])^2)
-template <bool BROADCAST>
+template <bool BROADCAST, typename TA = float>
 __global__ void __launch_bounds__(256)
-sqdiff_partial_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t total,
+sqdiff_partial_kernel(const TA* __restrict__ a, const float* __restrict__ b, int64_t total,
                       int64_t D, float* __restrict__ diff, float* __restrict__ partial) {
   __shared__ float scratch[33];
   float acc = 0.f;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    float e = __ldg(a + i) - __ldg(b + (BROADCAST ? i % D : i));
+    float e = sc::load1<TA>(a + i) - __ldg(b + (BROADCAST ? i % D : i));
     if (diff != nullptr) diff[i] = e;
     acc = fmaf(e, e, acc);
   }
@@ -109,9 +109,10 @@ extern "C" size_t sc_loss_workspace_bytes(int64_t D) {
   return ((size_t)kSlices * D + (size_t)D + kRedBlocks) * sizeof(float);
 }
 
-extern "C" int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv, void* ws,
+extern "C" int sc_total_variance(const void* y, int y_dtype, int64_t N, int64_t D, float* tv, void* ws,
                                  size_t ws_bytes, void* stream) {
   SC_REQUIRE(N > 0 && D > 0, "sc_total_variance: bad shape");
+  SC_REQUIRE(sc::valid_dtype(y_dtype), "sc_total_variance: bad dtype");
   SC_REQUIRE(y && tv && ws, "sc_total_variance: null pointer");
   if (ws_bytes < sc_loss_workspace_bytes(D))
     return sc::fail(SC_ERR_WORKSPACE, "sc_total_variance: workspace %zu < %zu", ws_bytes,
@@ -120,12 +121,17 @@ extern "C" int sc_total_variance(const float* y, int64_t N, int64_t D, float* tv
   float* partial = static_cast<float*>(ws);
   float* mean = partial + (size_t)kSlices * D;
   float* red = mean + D;
-  launch_colsum<float>(y, nullptr, N, D, partial, st);
+  using bf16 = __nv_bfloat16;
+  if (y_dtype == SC_F32) launch_colsum<float>(static_cast<const float*>(y), nullptr, N, D, partial, st);
+  else launch_colsum<bf16>(static_cast<const bf16*>(y), nullptr, N, D, partial, st);
   SC_CHECK_LAUNCH("colsum_partial");
   colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f / (float)N, D, mean);
   SC_CHECK_LAUNCH("colsum_finish");
   const int blocks = flat_blocks(N * D);
-  sqdiff_partial_kernel<true><<<blocks, 256, 0, st>>>(y, mean, N * D, D, nullptr, red);
+  if (y_dtype == SC_F32)
+    sqdiff_partial_kernel<true, float><<<blocks, 256, 0, st>>>(static_cast<const float*>(y), mean, N * D, D, nullptr, red);
+  else
+    sqdiff_partial_kernel<true, bf16><<<blocks, 256, 0, st>>>(static_cast<const bf16*>(y), mean, N * D, D, nullptr, red);
   SC_CHECK_LAUNCH("sqdiff_partial");
   final_sum_kernel<<<1, 256, 0, st>>>(red, blocks, tv);
   SC_CHECK_LAUNCH("final_sum");

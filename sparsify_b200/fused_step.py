@@ -54,17 +54,28 @@ class FusedSaeStep(torch.autograd.Function):
         sae.wait_decoder()  # a decoder update may still be running under the encoder above
         gather_lp = sae.precision == "bf16" and W_dec.dtype == torch.float32
         w_dec_src = sae.shadow("W_dec") if gather_lp else W_dec.detach()
-        out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())
-        ctx.skip = None
-        if W_skip is not None:
-            # out += x W_skip^T (sparsify/sparse_coder.py:221-222): tensor-core GEMM that
-            # accumulates onto the decode output in its epilogue
-            x_b = x if x.dtype == torch.bfloat16 else ops.prep_input(x, None, torch.bfloat16)
-            out = ops.gemm_nt(x_b, W_skip.detach().to(torch.bfloat16), beta=1.0, Cin=out, out_dtype=torch.float32)
-            ctx.skip = x_b
-        target = (x if y is None else y.detach()).to(torch.float32)
+        target = (x if y is None else y.detach())
+        if target.dtype not in (torch.float32, torch.bfloat16):
+            target = target.to(torch.float32)
         tv = ops.total_variance(target)
-        sse, e = ops.sq_err(target, out, want_diff=True)
+        # In the bf16 configuration the residual is kept as bf16 only (it is gathered and
+        # exchanged in that form); AuxK and the other precisions need it in fp32.
+        e16_only = sae.precision == "bf16" and num_dead == 0
+        ctx.skip = None
+        if W_skip is None and D % 4 == 0:
+            # decode, residual and its squared sum in one pass
+            out, e, e16, sse = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target,
+                                                   want_e32=not e16_only, want_e16=sae.precision == "bf16")
+        else:
+            out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())
+            if W_skip is not None:
+                # out += x W_skip^T (sparsify/sparse_coder.py:221-222): tensor-core GEMM that
+                # accumulates onto the decode output in its epilogue
+                x_b = x if x.dtype == torch.bfloat16 else ops.prep_input(x, None, torch.bfloat16)
+                out = ops.gemm_nt(x_b, W_skip.detach().to(torch.bfloat16), beta=1.0, Cin=out, out_dtype=torch.float32)
+                ctx.skip = x_b
+            sse, e = ops.sq_err(target.to(torch.float32), out, want_diff=True)
+            e16 = ops.prep_input(e, None, torch.bfloat16) if sae.precision == "bf16" else None
         fvu = sse / tv
 
         # ---- AuxK (sparsify/sparse_coder.py:231-249) in compact dense form: the dead
@@ -97,7 +108,8 @@ class FusedSaeStep(torch.autograd.Function):
             auxk = scale * sse_aux / tv
             ctx.aux = (Pb, diff, dead_idx, nd, scale)
 
-        ctx.save_for_backward(xe, idx, acts, e, tv)
+        ctx.save_for_backward(xe, idx, acts, e if e is not None else e16, tv)
+        ctx.e16 = e16
         ctx.w_enc_src, ctx.w_dec_src = w_enc_src, w_dec_src
         ctx.shape = (M, D, k)
         ctx.transcode = cfg.transcode
@@ -114,7 +126,7 @@ class FusedSaeStep(torch.autograd.Function):
         # d fvu / d out = -2 e / tv
         s = (-2.0 * g_fvu / tv).to(torch.float32) if g_fvu is not None else torch.zeros((), device=dev)
         if g_out is not None:
-            gout = torch.addcmul(g_out.to(torch.float32), e, s)  # general case: materialise
+            gout = torch.addcmul(g_out.to(torch.float32), e.to(torch.float32), s)  # general case: materialise
             scale = torch.ones((), device=dev)
         else:
             gout, scale = e, s
@@ -157,7 +169,12 @@ class FusedSaeStep(torch.autograd.Function):
             # CSR and the coefficient / row tensors instead of two dense [M, D] gradients.
             # in the bf16 configuration the residual rows are gathered (and, across ranks,
             # exchanged) as bf16 like every other gathered operand
-            vecA = ops.prep_input(gout, None, torch.bfloat16) if sae.precision == "bf16" else gout
+            if sae.precision != "bf16":
+                vecA = gout
+            elif g_out is None and ctx.e16 is not None:
+                vecA = ctx.e16  # the forward already wrote the residual as bf16
+            else:
+                vecA = ops.prep_input(gout, None, torch.bfloat16)
             sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, idx=idx, coefA=acts * scale,
                                 vecA=vecA, coefB=gacts, vecB=xe, extra=extra)
             g_W_dec = g_W_enc = None

@@ -147,15 +147,41 @@ def embedding_bag_fwd(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None 
 def embedding_bag_bwd_acts(idx: Tensor, grad_out: Tensor, W: Tensor) -> Tensor:
     _check_cuda(idx, grad_out, W)
     idx = idx.contiguous()
-    grad_out = _f32(grad_out)
+    grad_out = grad_out.detach().contiguous()
+    if grad_out.dtype not in (torch.float32, torch.bfloat16):
+        grad_out = grad_out.to(torch.float32)
     W = W.detach().contiguous()
     N, k = idx.shape
     M, D = W.shape
     gacts = torch.empty(N, k, dtype=torch.float32, device=W.device)
     with torch.cuda.device(W.device):
-        call("sc_embedding_bag_bwd_acts", ptr(idx), ptr(grad_out), ptr(W), dtype_code(W), N, D, M,
-             int(k), ptr(gacts), _stream(W))
+        call("sc_embedding_bag_bwd_acts", ptr(idx), ptr(grad_out), dtype_code(grad_out), ptr(W),
+             dtype_code(W), N, D, M, int(k), ptr(gacts), _stream(W))
     return gacts
+
+
+def decode_residual(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None, y: Tensor, *,
+                    want_out: bool = True, want_e32: bool = False, want_e16: bool = False):
+    """(out, e_f32, e_bf16, sse): decode, residual e = y - out and sum(e^2) in one pass."""
+    _check_cuda(idx, acts, W, bias, y)
+    idx, acts = idx.contiguous(), _f32(acts)
+    W, y = W.detach().contiguous(), y.detach().contiguous()
+    if y.dtype not in (torch.float32, torch.bfloat16):
+        y = y.to(torch.float32)
+    N, k = idx.shape
+    M, D = W.shape
+    dev = W.device
+    out = torch.empty(N, D, dtype=torch.float32, device=dev) if want_out else None
+    e32 = torch.empty(N, D, dtype=torch.float32, device=dev) if want_e32 else None
+    e16 = torch.empty(N, D, dtype=torch.bfloat16, device=dev) if want_e16 else None
+    sse = torch.empty((), dtype=torch.float32, device=dev)
+    ws = _ws(_lib.lib().sc_decode_residual_workspace_bytes(N), dev)
+    bias32 = _f32(bias)
+    with torch.cuda.device(dev):
+        call("sc_decode_residual", ptr(idx), ptr(acts), ptr(W), dtype_code(W), ptr(bias32), ptr(y),
+             dtype_code(y), N, D, M, int(k), ptr(out), ptr(e32), ptr(e16), ptr(sse), ptr(ws), ws.numel(),
+             _stream(W))
+    return out, e32, e16, sse
 
 
 def csr_build(idx: Tensor, M: int) -> tuple[Tensor, Tensor]:
@@ -257,12 +283,14 @@ def rows_adam_(row_ptr: Tensor, entries: Tensor, k: int, coefA: Tensor, vecA: Te
 def total_variance(y: Tensor) -> Tensor:
     """sum((y - y.mean(0))**2) as a 0-d fp32 device tensor."""
     _check_cuda(y)
-    y = _f32(y)
+    y = y.detach().contiguous()
+    if y.dtype not in (torch.float32, torch.bfloat16):
+        y = y.to(torch.float32)
     N, D = y.shape
     tv = torch.empty((), dtype=torch.float32, device=y.device)
     ws = _ws(_lib.lib().sc_loss_workspace_bytes(D), y.device)
     with torch.cuda.device(y.device):
-        call("sc_total_variance", ptr(y), N, D, ptr(tv), ptr(ws), ws.numel(), _stream(y))
+        call("sc_total_variance", ptr(y), dtype_code(y), N, D, ptr(tv), ptr(ws), ws.numel(), _stream(y))
     return tv
 
 
