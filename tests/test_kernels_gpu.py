@@ -267,3 +267,31 @@ def test_newtonschulz_tc_vs_oracle(cuda_lib):
     assert rel_l2(X, ref) < 8e-2
     s = torch.linalg.svdvals(X)
     assert float(s.max()) < 1.6 and float(s.min()) > 0.3  # singular values pushed towards 1
+
+
+@pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
+def test_decode_residual(cuda_lib, ydtype):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(12)
+    N, D, M, k = 300, 768, 4096, 32
+    W = bf16_round(torch.randn(M, D, generator=g))
+    b = torch.randn(D, generator=g)
+    acts = torch.rand(N, k, generator=g)
+    idx = torch.stack([torch.randperm(M, generator=g)[:k] for _ in range(N)])
+    y = torch.randn(N, D, generator=g)
+    if ydtype == torch.bfloat16:
+        y = bf16_round(y)
+    out, e32, e16, sse = ops.decode_residual(idx.cuda(), acts.cuda(), W.cuda().bfloat16(), b.cuda(),
+                                             y.cuda().to(ydtype), want_e32=True, want_e16=True)
+    ref_out = O.decode(idx, acts, W, b)
+    ref_e = y - ref_out
+    assert rel_l2(out, ref_out) < F32_TOL
+    assert rel_l2(e32, ref_e) < F32_TOL
+    assert torch.equal(e16.cpu(), e32.cpu().bfloat16())
+    assert abs(float(sse) - float(ref_e.double().pow(2).sum())) < 1e-5 * float(sse)
+    tv = ops.total_variance(y.cuda().to(ydtype))
+    ref_tv = (y.double() - y.double().mean(0)).pow(2).sum()
+    assert abs(float(tv) - float(ref_tv)) < 1e-5 * float(ref_tv)
+    gacts16 = ops.embedding_bag_bwd_acts(idx.cuda(), e16, W.cuda().bfloat16())
+    _, gacts_ref = O.decode_backward(idx, acts, W, e16.float().cpu())
+    assert rel_l2(gacts16, gacts_ref) < F32_TOL
