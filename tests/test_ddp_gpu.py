@@ -32,7 +32,14 @@ def _build(device):
     return sae, opt
 
 
-def _worker(rank, world, port, out):
+def _dead_mask():
+    g = torch.Generator().manual_seed(5)
+    m = torch.zeros(M, dtype=torch.bool)
+    m[torch.randperm(M, generator=g)[:96]] = True
+    return m
+
+
+def _worker(rank, world, port, out, auxk):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -41,8 +48,8 @@ def _worker(rank, world, port, out):
         assert opt.enable_sparse_update(sae) and sae._shard == (rank, world)
         for step in range(STEPS):
             sae.set_decoder_norm_to_unit_norm()
-            out_ = sae(_data(rank, step).cuda())
-            out_.fvu.backward()
+            out_ = sae(_data(rank, step).cuda(), dead_mask=_dead_mask().cuda() if auxk else None)
+            (out_.fvu + out_.auxk_loss / 32).backward()
             for p in sae.parameters():
                 if p.grad is not None:
                     dist.all_reduce(p.grad)
@@ -57,19 +64,22 @@ def _worker(rank, world, port, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_sparse_update_matches_single_process(cuda_lib):
+@pytest.mark.parametrize("auxk", [False, True])
+def test_sharded_sparse_update_matches_single_process(cuda_lib, auxk):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, out, auxk), nprocs=2, join=True)
 
     # single process: both ranks' batches per step, losses averaged (DDP's mean of gradients)
     sae, opt = _build("cuda:0")
     for step in range(STEPS):
         sae.set_decoder_norm_to_unit_norm()
-        loss = sum(sae(_data(r, step).cuda()).fvu for r in range(2)) / 2
+        dead = _dead_mask().cuda() if auxk else None
+        outs = [sae(_data(r, step).cuda(), dead_mask=dead) for r in range(2)]
+        loss = sum(o.fvu + o.auxk_loss / 32 for o in outs) / 2
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
