@@ -292,6 +292,41 @@ def gen_trainer_muon(sparsify):
         save("trainer_muon", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=2e-3, warmup=2))
 
 
+def gen_trajectory200(sparsify):
+    """200 optimiser steps of the reference Trainer at the CPU configuration
+    (d_in=768, 24576 latents, k=32, 4096 tokens/step, fp32, Adam, AuxK enabled)
+    on the seeded synthetic activations of sparsify_b200.synthetic; only the FVU
+    of every step is frozen (the inputs are regenerated from their seeds)."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from sparsify_b200.synthetic import SyntheticActivations, batch_seed
+    from sparsify import SparseCoderConfig, TrainConfig, Trainer
+    steps, B, T, D, M, k = 200, 8, 512, 768, 24576, 32
+    gen = SyntheticActivations(D, 65536, 32, device="cpu")
+    torch.set_num_threads(8)
+    acts = torch.stack([gen.batch(B * T, batch_seed(t)).reshape(B, T, D) for t in range(steps)])
+    model = FakeModel(acts)
+    dataset = [{"input_ids": torch.zeros(T, dtype=torch.long)} for _ in range(steps * B)]
+    fvus = []
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="adam",
+                          lr_warmup_steps=10, auxk_alpha=1 / 32, hookpoints=["layers.0"], log_to_wandb=False,
+                          save_dir=tmp, run_name="golden", save_every=10**9)
+        trainer = Trainer(cfg, dataset, model)
+        sae = trainer.saes["layers.0"]
+        orig_forward = sae.forward
+
+        def recording_forward(*a, **kw):
+            out = orig_forward(*a, **kw)
+            fvus.append(float(out.fvu))
+            return out
+
+        sae.forward = recording_forward
+        trainer.fit()
+    save("trajectory200", dict(fvu=torch.tensor(fvus)),
+         dict(steps=steps, B=B, T=T, D=D, M=M, k=k, atoms=65536, active=32, warmup=10, auxk_alpha=1 / 32))
+    print("fvu first/last:", fvus[0], fvus[-1])
+
+
 def gen_muon(sparsify):
     from sparsify.muon import quintic_newtonschulz
     g = torch.Generator().manual_seed(3)
@@ -310,3 +345,5 @@ if __name__ == "__main__":
     gen_trainer(ref)
     gen_trainer_muon(ref)
     gen_muon(ref)
+    if "--trajectory" in sys.argv:  # about three minutes of CPU time on 8 threads
+        gen_trajectory200(ref)

@@ -104,3 +104,31 @@ def test_muon_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
     for name, p in (("W_enc", sae.encoder.weight), ("W_dec", sae.W_dec), ("b_enc", sae.encoder.bias),
                     ("b_dec", sae.b_dec)):
         assert rel_l2(p.detach(), t[f"final.{name}"]) < 1e-2, (name, rel_l2(p.detach(), t[f"final.{name}"]))
+
+
+def test_fvu_trajectory_200_steps(cuda_lib, tmp_path):
+    """200 steps at d_in=768, 24576 latents, k=32, 4096 tokens per step, bf16 operands:
+    the FVU of every step stays within 2 % of the reference Trainer's fp32 CPU run
+    (tests/golden/trajectory200.safetensors) on the same seeded inputs and the same
+    initial weights."""
+    from sparsify_b200.synthetic import SyntheticActivations, batch_seed
+    t, meta = load_golden("trajectory200")
+    steps, B, T, D, M = meta["steps"], meta["B"], meta["T"], meta["D"], meta["M"]
+    gen = SyntheticActivations(D, meta["atoms"], meta["active"], device="cpu")
+    acts = torch.stack([gen.batch(B * T, batch_seed(s)).reshape(B, T, D) for s in range(steps)])
+    full = dict(meta, lr=None, dead_feature_threshold=10_000_000)
+    trainer = make_trainer(tmp_path, full, acts, "bf16")
+    sae = trainer.saes["layers.0"]
+    # the reference initialises on the CPU generator: seed, then nn.Linear (sparse_coder.py:60-75)
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(D, M)
+    with torch.no_grad():
+        sae.encoder.weight.copy_(lin.weight); sae.encoder.bias.zero_()
+        sae.W_dec.copy_(torch.nn.functional.normalize(lin.weight, dim=1)); sae.b_dec.zero_()
+    trainer.fit()
+    fvus = [row["fvu/layers.0"] for row in trainer.metrics]
+    want = t["fvu"].tolist()
+    assert len(fvus) == steps
+    worst = max(abs(a - b) / b for a, b in zip(fvus, want))
+    assert worst < 0.02, (worst, fvus[::20], want[::20])
+    assert fvus[-1] < fvus[0] - 0.05  # it trained
