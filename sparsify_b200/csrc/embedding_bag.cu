@@ -8,29 +8,41 @@
 //
 // Backward w.r.t. acts: one CTA per token; the incoming gradient row is staged
 // in shared memory once and dotted against each of the k gathered rows.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int kBagThreads = 256;
+constexpr int kBagChunk = 1024;  // entries of one token staged in shared memory at a time
+
+// Stages entries [j0, j0 + kc) of token n; ids outside [0, M) contribute nothing.
+__device__ __forceinline__ void stage_entries(const int64_t* __restrict__ idx, const float* __restrict__ acts,
+                                              int64_t n, int k, int j0, int kc, int64_t M,
+                                              int64_t* s_idx, float* s_act) {
+  for (int j = threadIdx.x; j < kc; j += blockDim.x) {
+    int64_t r = idx[n * k + j0 + j];
+    float a = acts[n * k + j0 + j];
+    if (r < 0 || r >= M) { r = 0; a = 0.f; }
+    s_idx[j] = r;
+    s_act[j] = a;
+  }
+}
 
 template <typename WT, int VEC>
 __global__ void __launch_bounds__(kBagThreads)
 bag_fwd_kernel(const int64_t* __restrict__ idx, const float* __restrict__ acts,
                const WT* __restrict__ W, const float* __restrict__ bias, int64_t N,
                int64_t D, int64_t M, int k, float* __restrict__ out) {
-  extern __shared__ unsigned char smem_raw[];
-  int64_t* s_idx = reinterpret_cast<int64_t*>(smem_raw);
-  float* s_act = reinterpret_cast<float*>(s_idx + k);
+  __shared__ int64_t s_idx[kBagChunk];
+  __shared__ float s_act[kBagChunk];
   const int64_t n = blockIdx.x;
-  for (int j = threadIdx.x; j < k; j += blockDim.x) {
-    int64_t r = idx[n * k + j];
-    float a = acts[n * k + j];
-    if (r < 0 || r >= M) { r = 0; a = 0.f; }  // out-of-range ids contribute nothing
-    s_idx[j] = r;
-    s_act[j] = a;
+  const bool one_chunk = k <= kBagChunk;
+  if (one_chunk) {
+    stage_entries(idx, acts, n, k, 0, k, M, s_idx, s_act);
+    __syncthreads();
   }
-  __syncthreads();
 
   constexpr int NCH = 4;  // column groups per thread per sweep
   const int64_t sweep = (int64_t)blockDim.x * VEC * NCH;
@@ -44,21 +56,29 @@ bag_fwd_kernel(const int64_t* __restrict__ idx, const float* __restrict__ acts,
       for (int v = 0; v < VEC; ++v)
         acc[c][v] = (bias != nullptr && col[c] + v < D) ? __ldg(bias + col[c] + v) : 0.f;
     }
+    for (int j0 = 0; j0 < k; j0 += kBagChunk) {
+      const int kc = min(kBagChunk, k - j0);
+      if (!one_chunk) {
+        __syncthreads();
+        stage_entries(idx, acts, n, k, j0, kc, M, s_idx, s_act);
+        __syncthreads();
+      }
 #pragma unroll 4
-    for (int j = 0; j < k; ++j) {
-      const WT* row = W + s_idx[j] * D;
-      const float a = s_act[j];
+      for (int j = 0; j < kc; ++j) {
+        const WT* row = W + s_idx[j] * D;
+        const float a = s_act[j];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        if (col[c] < D) {
-          if constexpr (VEC == 4) {
-            float4 w = sc::load4<WT>(row + col[c]);
-            acc[c][0] = fmaf(a, w.x, acc[c][0]);
-            acc[c][1] = fmaf(a, w.y, acc[c][1]);
-            acc[c][2] = fmaf(a, w.z, acc[c][2]);
-            acc[c][3] = fmaf(a, w.w, acc[c][3]);
-          } else {
-            acc[c][0] = fmaf(a, sc::load1<WT>(row + col[c]), acc[c][0]);
+        for (int c = 0; c < NCH; ++c) {
+          if (col[c] < D) {
+            if constexpr (VEC == 4) {
+              float4 w = sc::load4<WT>(row + col[c]);
+              acc[c][0] = fmaf(a, w.x, acc[c][0]);
+              acc[c][1] = fmaf(a, w.y, acc[c][1]);
+              acc[c][2] = fmaf(a, w.z, acc[c][2]);
+              acc[c][3] = fmaf(a, w.w, acc[c][3]);
+            } else {
+              acc[c][0] = fmaf(a, sc::load1<WT>(row + col[c]), acc[c][0]);
+            }
           }
         }
       }
@@ -86,19 +106,15 @@ decode_residual_kernel(const int64_t* __restrict__ idx, const float* __restrict_
                        const WT* __restrict__ W, const float* __restrict__ bias, const YT* __restrict__ y,
                        int64_t D, int64_t M, int k, float* __restrict__ out, float* __restrict__ e32,
                        __nv_bfloat16* __restrict__ e16, float* __restrict__ partial) {
-  extern __shared__ unsigned char smem_raw[];
-  int64_t* s_idx = reinterpret_cast<int64_t*>(smem_raw);
-  float* s_act = reinterpret_cast<float*>(s_idx + k);
+  __shared__ int64_t s_idx[kBagChunk];
+  __shared__ float s_act[kBagChunk];
   __shared__ float scratch[33];
   const int64_t n = blockIdx.x;
-  for (int j = threadIdx.x; j < k; j += blockDim.x) {
-    int64_t r = idx[n * k + j];
-    float a = acts[n * k + j];
-    if (r < 0 || r >= M) { r = 0; a = 0.f; }
-    s_idx[j] = r;
-    s_act[j] = a;
+  const bool one_chunk = k <= kBagChunk;
+  if (one_chunk) {
+    stage_entries(idx, acts, n, k, 0, k, M, s_idx, s_act);
+    __syncthreads();
   }
-  __syncthreads();
   constexpr int NCH = 4;
   const int64_t sweep = (int64_t)blockDim.x * 4 * NCH;
   float sq = 0.f;
@@ -111,16 +127,24 @@ decode_residual_kernel(const int64_t* __restrict__ idx, const float* __restrict_
       acc[c] = (bias != nullptr && col[c] < D) ? __ldg(reinterpret_cast<const float4*>(bias + col[c]))
                                                : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    for (int j0 = 0; j0 < k; j0 += kBagChunk) {
+      const int kc = min(kBagChunk, k - j0);
+      if (!one_chunk) {
+        __syncthreads();
+        stage_entries(idx, acts, n, k, j0, kc, M, s_idx, s_act);
+        __syncthreads();
+      }
 #pragma unroll 4
-    for (int j = 0; j < k; ++j) {
-      const WT* row = W + s_idx[j] * D;
-      const float a = s_act[j];
+      for (int j = 0; j < kc; ++j) {
+        const WT* row = W + s_idx[j] * D;
+        const float a = s_act[j];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        if (col[c] < D) {
-          const float4 w = sc::load4<WT>(row + col[c]);
-          acc[c].x = fmaf(a, w.x, acc[c].x); acc[c].y = fmaf(a, w.y, acc[c].y);
-          acc[c].z = fmaf(a, w.z, acc[c].z); acc[c].w = fmaf(a, w.w, acc[c].w);
+        for (int c = 0; c < NCH; ++c) {
+          if (col[c] < D) {
+            const float4 w = sc::load4<WT>(row + col[c]);
+            acc[c].x = fmaf(a, w.x, acc[c].x); acc[c].y = fmaf(a, w.y, acc[c].y);
+            acc[c].z = fmaf(a, w.z, acc[c].z); acc[c].w = fmaf(a, w.w, acc[c].w);
+          }
         }
       }
     }
@@ -162,7 +186,7 @@ bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const GT* __restrict__ gout
   extern __shared__ unsigned char smem_raw[];
   float* s_g = reinterpret_cast<float*>(smem_raw);                 // [Dpad]
   const int64_t Dpad = (D + 3) & ~int64_t(3);
-  float* s_part = s_g + Dpad;                                      // [k][nwarps]
+  float* s_part = s_g + Dpad;                                      // [min(k, kBagChunk)][nwarps]
   const int nwarps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t n = blockIdx.x;
@@ -172,13 +196,15 @@ bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const GT* __restrict__ gout
   __syncthreads();
 
   constexpr int JB = 4;  // rows in flight per iteration
-  for (int j0 = 0; j0 < k; j0 += JB) {
+  for (int c0 = 0; c0 < k; c0 += kBagChunk) {
+  const int c1 = min(k, c0 + kBagChunk);
+  for (int j0 = c0; j0 < c1; j0 += JB) {
     float part[JB];
     const WT* rows[JB];
 #pragma unroll
     for (int jj = 0; jj < JB; ++jj) {
       part[jj] = 0.f;
-      int64_t r = (j0 + jj < k) ? idx[n * k + j0 + jj] : -1;
+      int64_t r = (j0 + jj < c1) ? idx[n * k + j0 + jj] : -1;
       rows[jj] = (r >= 0 && r < M) ? W + r * D : nullptr;
     }
     for (int64_t c = (int64_t)threadIdx.x * VEC; c < D; c += (int64_t)blockDim.x * VEC) {
@@ -201,14 +227,16 @@ bag_bwd_acts_kernel(const int64_t* __restrict__ idx, const GT* __restrict__ gout
 #pragma unroll
     for (int jj = 0; jj < JB; ++jj) {
       float s = sc::warp_sum(part[jj]);
-      if (lane == 0 && j0 + jj < k) s_part[(j0 + jj) * nwarps + warp] = s;
+      if (lane == 0 && j0 + jj < c1) s_part[(j0 + jj - c0) * nwarps + warp] = s;
     }
   }
   __syncthreads();
-  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+  for (int j = c0 + threadIdx.x; j < c1; j += blockDim.x) {
     float s = 0.f;
-    for (int w = 0; w < nwarps; ++w) s += s_part[j * nwarps + w];
+    for (int w = 0; w < nwarps; ++w) s += s_part[(j - c0) * nwarps + w];
     gacts[n * k + j] = s;
+  }
+  __syncthreads();
   }
 }
 
@@ -223,8 +251,7 @@ extern "C" int sc_embedding_bag_fwd(const int64_t* idx, const float* acts, const
   if (N == 0) return SC_OK;
   SC_REQUIRE(idx && acts && W && out, "sc_embedding_bag_fwd: null pointer");
   SC_REQUIRE(N <= 0x7fffffffLL, "sc_embedding_bag_fwd: N too large");
-  const size_t smem = (size_t)k * (sizeof(int64_t) + sizeof(float));
-  SC_REQUIRE(smem <= 48 * 1024, "sc_embedding_bag_fwd: k=%d too large", k);
+  const size_t smem = 0;  // the entry staging area is static
   const bool vec = (D % 4 == 0) && sc::aligned(W, 16) && sc::aligned(out, 16) &&
                    (bias == nullptr || sc::aligned(bias, 16));
   dim3 grid((unsigned)N), block(kBagThreads);
@@ -251,7 +278,7 @@ extern "C" int sc_embedding_bag_bwd_acts(const int64_t* idx, const void* grad_ou
   SC_REQUIRE(idx && grad_out && W && grad_acts, "sc_embedding_bag_bwd_acts: null pointer");
   SC_REQUIRE(N <= 0x7fffffffLL, "sc_embedding_bag_bwd_acts: N too large");
   const int nwarps = kBagThreads / 32;
-  const size_t smem = (size_t)(((D + 3) & ~int64_t(3)) + (int64_t)k * nwarps) * sizeof(float);
+  const size_t smem = (size_t)(((D + 3) & ~int64_t(3)) + (int64_t)std::min(k, kBagChunk) * nwarps) * sizeof(float);
   SC_REQUIRE(smem <= 200 * 1024, "sc_embedding_bag_bwd_acts: D=%lld, k=%d need %zu B of shared memory",
              (long long)D, k, smem);
   const bool vec = (D % 4 == 0) && sc::aligned(W, 16);
@@ -296,8 +323,7 @@ extern "C" int sc_decode_residual(const int64_t* idx, const float* acts, const v
   if (ws_bytes < sc_decode_residual_workspace_bytes(N))
     return sc::fail(SC_ERR_WORKSPACE, "sc_decode_residual: workspace %zu < %zu", ws_bytes,
                     sc_decode_residual_workspace_bytes(N));
-  const size_t smem = (size_t)k * (sizeof(int64_t) + sizeof(float));
-  SC_REQUIRE(smem <= 40 * 1024, "sc_decode_residual: k=%d too large", k);
+  const size_t smem = 0;
   float* partial = static_cast<float*>(ws);
   cudaStream_t st = sc::as_stream(stream);
   dim3 grid((unsigned)N), block(kBagThreads);

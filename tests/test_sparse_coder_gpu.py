@@ -286,3 +286,34 @@ def test_transcoder_skip_fused_vs_oracle(cuda_lib):
     for pname, gt in (("W_enc", sae.encoder.weight.grad), ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad),
                       ("W_skip", sae.W_skip.grad)):
         assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
+
+
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("bf16", 1e-2)])
+def test_large_k_forward_backward(cuda_lib, precision, tol):
+    """k far above the fused kernels' limit (the first steps of a k-decay schedule,
+    trainer.py:176-177,229-235): entries are staged in several chunks by the
+    gather kernels. k stays below the count of positive pre-activations so the
+    selected set is unique."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    torch.manual_seed(0)
+    N, D, M, k = 96, 256, 8192, 3000
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device="cuda", dtype=torch.float32)
+    sae.precision = precision
+    x = torch.randn(N, D, generator=torch.Generator().manual_seed(4))
+    out = sae(x.cuda())
+    out.fvu.backward()
+    rnd = (lambda t: t.to(torch.bfloat16).to(torch.float32)) if precision == "bf16" else None
+    params = dict(W_enc=sae.encoder.weight.detach().cpu(), b_enc=sae.encoder.bias.detach().cpu(),
+                  W_dec=sae.W_dec.detach().cpu(), b_dec=sae.b_dec.detach().cpu())
+    ref = O.sae_forward_backward(params, x, cfg=O.OracleCfg(k=k), round_operands=rnd)
+    assert float(ref.latent_acts.min()) > 0
+    # as sets (neighbours in value order swap under a different summation order)
+    got = torch.zeros(N, M, dtype=torch.bool).scatter_(1, out.latent_indices.cpu(), True)
+    want = torch.zeros(N, M, dtype=torch.bool).scatter_(1, ref.latent_indices, True)
+    assert int(got.sum()) == N * k  # no latent twice in a row
+    assert (got & want).sum() / (N * k) > (0.999 if rnd else 0.99999)
+    assert rel_l2(out.sae_out.detach(), ref.sae_out) < tol
+    assert abs(float(out.fvu) - float(ref.fvu)) < tol * float(ref.fvu)
+    for pname, gt in (("W_enc", sae.encoder.weight.grad), ("b_enc", sae.encoder.bias.grad),
+                      ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad)):
+        assert rel_l2(gt, ref.grads[pname]) < 10 * tol, (pname, rel_l2(gt, ref.grads[pname]))
