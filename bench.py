@@ -53,6 +53,8 @@ def parse_args():
                     help="1: run the step on a high-priority stream and the decoder half of the weight "
                          "update on a normal-priority side stream under the next encoder GEMM "
                          "(measured slower on B200: 25.7 vs 23.0 ms/step; off by default)")
+    ap.add_argument("--multi-topk", action="store_true",
+                    help="secondary workload: Multi-TopK loss (top 4k selected in the encoder kernel)")
     ap.add_argument("--dead-frac", type=float, default=0.0,
                     help="mark this fraction of the latents dead (fixed seed) so that the AuxK branch is "
                          "active in every step; 0 = the natural state (no latent dead yet)")
@@ -64,6 +66,8 @@ def parse_args():
 
 def workload_name(a) -> str:
     aux = f"AuxK active on {a.dead_frac:.0%} dead latents" if a.dead_frac > 0 else "AuxK enabled"
+    if getattr(a, "multi_topk", False):
+        aux += ", Multi-TopK loss"
     if a.transcode:
         return (f"transcoder train step d_in={a.d} latents={a.latents} k={a.k} tokens/rank/step={a.tokens} "
                 f"dense skip connection, bf16 operands fp32 accumulate, fwd+bwd+Adam, {aux}")
@@ -224,7 +228,8 @@ def run_ours(a):
 
     N, D, M, k = a.tokens, a.d, a.latents, a.k
     torch.manual_seed(0)  # identical replicas on every rank (sparsify/trainer.py:80-87)
-    sae_cfg = SparseCoderConfig(num_latents=M, k=k, transcode=a.transcode, skip_connection=a.transcode)
+    sae_cfg = SparseCoderConfig(num_latents=M, k=k, transcode=a.transcode, skip_connection=a.transcode,
+                                multi_topk=a.multi_topk)
     sae = SparseCoder(D, sae_cfg, device=dev, dtype=torch.float32)
     lr = 2e-4 / (M / 2 ** 14) ** 0.5
     opt = FusedAdam(sae.parameters(), lr=lr)
@@ -286,6 +291,8 @@ def run_ours(a):
         tokens_seen += N
         out = sae(x, y, dead_mask=dead)
         loss = out.fvu + alpha * out.auxk_loss
+        if a.multi_topk:
+            loss = loss + out.multi_topk_fvu / 8  # sparsify/trainer.py:444-447
         loss.backward()
         if world > 1:
             for p in grads:

@@ -43,13 +43,17 @@ def _autocast_bf16(t: Tensor) -> bool:
 class FusedEncoder(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, weight, bias, k: int, activation: Literal["groupmax", "topk"],
-                need_pre_acts: bool = True, weight_bf16: Tensor | None = None):
+                need_pre_acts: bool = True, weight_bf16: Tensor | None = None, wide_k: int = 0):
         """
         input:  (N, D)   weight: (M, D)   bias: (M,)
         need_pre_acts: materialise the dense (N, M) pre-activations (the
             reference always does); False returns an empty placeholder.
         weight_bf16: optional up-to-date bf16 copy of `weight` for the
             tensor-core path (saves the per-call cast).
+        wide_k: when > k, also return the top-`wide_k` set (values, indices;
+            no gradient, as the reference drops the gradient of `pre_acts`), of
+            which the top-k is the leading part. Multi-TopK uses it in place of
+            a second selection over dense pre-activations.
         """
         if activation not in ("topk", "groupmax"):
             raise ValueError(f"Unknown activation: {activation}")
@@ -62,12 +66,17 @@ class FusedEncoder(torch.autograd.Function):
         )
         x_c = input.detach().contiguous()
         preacts = None
-        if activation == "topk" and low_precision and not need_pre_acts and ops.tc_encode_supported(D, M, k):
+        wide = None
+        k_sel = max(k, wide_k)
+        if activation == "topk" and low_precision and not need_pre_acts and ops.tc_encode_supported(D, M, k_sel):
             xb = x_c if x_c.dtype == torch.bfloat16 else ops.prep_input(x_c, None, torch.bfloat16)
             if weight_bf16 is None:
                 w_c = weight.detach().contiguous()
                 weight_bf16 = w_c if w_c.dtype == torch.bfloat16 else ops.cast_bf16(w_c)
-            values, indices = ops.encode_topk_tc(xb, weight_bf16, bias, k)
+            values, indices = ops.encode_topk_tc(xb, weight_bf16, bias, k_sel)
+            if k_sel > k:  # descending order: the top-k is the leading part
+                wide = (values, indices)
+                values, indices = values[:, :k].contiguous(), indices[:, :k].contiguous()
             x_saved = xb
         else:
             if low_precision:
@@ -87,6 +96,8 @@ class FusedEncoder(torch.autograd.Function):
                 x_saved = x_c
             if activation == "topk":
                 values, indices = ops.topk_rows(preacts, k)
+                if wide_k > k:
+                    wide = ops.topk_rows(preacts, wide_k)
             else:
                 values, indices = ops.groupmax_rows(preacts, k)
         ctx.save_for_backward(x_saved, weight, indices)
@@ -95,14 +106,16 @@ class FusedEncoder(torch.autograd.Function):
         ctx.k = k
         ctx.in_dtype, ctx.w_dtype = input.dtype, weight.dtype
         ctx.b_dtype = bias.dtype if bias is not None else None
-        ctx.mark_non_differentiable(indices)
         if preacts is None:
             preacts = values.new_empty(0)
         values = values.to(weight.dtype) if not low_precision else values
-        return values, indices, preacts
+        if wide is None:
+            wide = (values.new_empty(0), indices.new_empty(0))
+        ctx.mark_non_differentiable(indices, *wide)
+        return values, indices, preacts, wide[0], wide[1]
 
     @staticmethod
-    def backward(ctx, grad_values, grad_indices, grad_preacts):
+    def backward(ctx, grad_values, grad_indices, grad_preacts, grad_wide_values=None, grad_wide_indices=None):
         x_saved, weight, indices = ctx.saved_tensors
         grad_input = grad_weight = grad_bias = None
         gv = grad_values.detach().to(torch.float32).contiguous()
@@ -125,7 +138,7 @@ class FusedEncoder(torch.autograd.Function):
             if want_b:
                 grad_bias = res["gbiasA"].to(ctx.b_dtype)
 
-        return grad_input, grad_weight, grad_bias, None, None, None, None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None
 
 
 def fused_encoder(
@@ -145,5 +158,5 @@ def fused_encoder(
     the dense ``pre_acts`` and reuse a bf16 weight copy.
     """
     return EncoderOutput(
-        *FusedEncoder.apply(input, weight, bias, k, activation, need_pre_acts, weight_bf16)  # type: ignore
+        *FusedEncoder.apply(input, weight, bias, k, activation, need_pre_acts, weight_bf16)[:3]  # type: ignore
     )

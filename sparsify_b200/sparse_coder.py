@@ -31,7 +31,7 @@ from torch import Tensor, nn
 from . import ops
 from .config import SparseCoderConfig
 from .dense import linear_nt
-from .fused_encoder import EncoderOutput, fused_encoder
+from .fused_encoder import EncoderOutput, FusedEncoder, fused_encoder
 from .fused_step import FusedSaeStep, fused_supported
 from .utils import decoder_impl
 
@@ -211,6 +211,10 @@ class SparseCoder(nn.Module):
     # ------------------------------------------------------------------ compute
     def encode(self, x: Tensor, *, need_pre_acts: bool = True) -> EncoderOutput:
         """Encode the input and select the top-k latents."""
+        return self._encode(x, need_pre_acts, 0)[0]
+
+    def _encode(self, x: Tensor, need_pre_acts: bool, wide_k: int):
+        """encode() that can also return the top-`wide_k` set (see FusedEncoder)."""
         if not self.cfg.transcode:
             x = x - self.b_dec
         lowp = self._lowp()
@@ -219,10 +223,9 @@ class SparseCoder(nn.Module):
         else:
             w_lp = None
             x = x.to(torch.float32)
-        return fused_encoder(
-            x, self.encoder.weight, self.encoder.bias, self.cfg.k, self.cfg.activation,
-            need_pre_acts=need_pre_acts, weight_bf16=w_lp,
-        )
+        res = FusedEncoder.apply(x, self.encoder.weight, self.encoder.bias, self.cfg.k, self.cfg.activation,
+                                 need_pre_acts, w_lp, wide_k)
+        return EncoderOutput(*res[:3]), res[3], res[4]
 
     def decode(self, top_acts: Tensor, top_indices: Tensor) -> Tensor:
         assert self.W_dec is not None, "Decoder weight was not initialized."
@@ -240,8 +243,13 @@ class SparseCoder(nn.Module):
                 x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead,
                 self.W_skip)
             return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_tensor(0.0))
-        need_dense = self.cfg.multi_topk or num_dead > 0
-        top_acts, top_indices, pre_acts = self.encode(x, need_pre_acts=need_dense)
+        # Multi-TopK alone needs no dense pre-activations: the encoder kernel selects
+        # the top 4k once and the top k is its leading part.
+        wide_k = 4 * self.cfg.k if self.cfg.multi_topk and self.cfg.activation == "topk" else 0
+        wide_on_chip = (wide_k > 0 and num_dead == 0 and self._lowp() and x.is_cuda
+                        and ops.tc_encode_supported(self.d_in, self.num_latents, wide_k))
+        need_dense = (self.cfg.multi_topk and not wide_on_chip) or num_dead > 0
+        (top_acts, top_indices, pre_acts), wide_acts, wide_indices = self._encode(x, need_dense, wide_k)
 
         # If we aren't given a distinct target, we're autoencoding
         if y is None:
@@ -280,7 +288,10 @@ class SparseCoder(nn.Module):
         fvu = l2_loss / total_variance
 
         if self.cfg.multi_topk:
-            top_acts, top_indices = ops.topk_rows(pre_acts, 4 * self.cfg.k)
+            if wide_k > 0:
+                top_acts, top_indices = wide_acts, wide_indices
+            else:
+                top_acts, top_indices = ops.topk_rows(pre_acts, 4 * self.cfg.k)
             sae_out = self.decode(top_acts, top_indices)
             multi_topk_fvu = (sae_out - y).pow(2).sum() / total_variance
         else:

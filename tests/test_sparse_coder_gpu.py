@@ -317,3 +317,31 @@ def test_large_k_forward_backward(cuda_lib, precision, tol):
     for pname, gt in (("W_enc", sae.encoder.weight.grad), ("b_enc", sae.encoder.bias.grad),
                       ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad)):
         assert rel_l2(gt, ref.grads[pname]) < 10 * tol, (pname, rel_l2(gt, ref.grads[pname]))
+
+
+def test_multi_topk_bf16_vs_oracle(cuda_lib):
+    """Multi-TopK in the bf16 configuration: one tensor-core selection of the top 4k,
+    whose leading k is the top-k (no dense pre-activations), against the oracle on
+    the same bf16-rounded operands (sparse_coder.py:256-262)."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    torch.manual_seed(0)
+    N, D, M, k = 384, 256, 4096, 16
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k, multi_topk=True), device="cuda", dtype=torch.float32)
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(N, D, generator=g)
+    out = sae(x.cuda())
+    (out.fvu + out.multi_topk_fvu / 8).backward()
+    rnd = lambda t: t.to(torch.bfloat16).to(torch.float32)
+    params = dict(W_enc=sae.encoder.weight.detach().cpu(), b_enc=sae.encoder.bias.detach().cpu(),
+                  W_dec=sae.W_dec.detach().cpu(), b_dec=sae.b_dec.detach().cpu())
+    ref = O.sae_forward_backward(params, x, cfg=O.OracleCfg(k=k, multi_topk=True), round_operands=rnd)
+    assert out.latent_indices.shape == (N, 4 * k)  # the returned set is the wide one
+    got = torch.zeros(N, M, dtype=torch.bool).scatter_(1, out.latent_indices.cpu(), True)
+    want = torch.zeros(N, M, dtype=torch.bool).scatter_(1, ref.latent_indices, True)
+    assert (got & want).sum() / (N * 4 * k) > 0.999
+    assert rel_l2(out.sae_out.detach(), ref.sae_out) < 2e-3
+    assert abs(float(out.fvu) - float(ref.fvu)) < 1e-3 * float(ref.fvu)
+    assert abs(float(out.multi_topk_fvu) - float(ref.multi_topk_fvu)) < 1e-3 * float(ref.multi_topk_fvu)
+    for pname, gt in (("W_enc", sae.encoder.weight.grad), ("b_enc", sae.encoder.bias.grad),
+                      ("W_dec", sae.W_dec.grad), ("b_dec", sae.b_dec.grad)):
+        assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
