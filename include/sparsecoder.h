@@ -264,6 +264,21 @@ int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M, int64_t N
  * into K-major form, sparsify/muon.py:36). */
 int sc_transpose_bf16(const void* in, int64_t R, int64_t C, void* out, void* stream);
 
+/* sparsify/sparse_coder.py:281-295 on its own: g[m,:] -= (g[m,:] . w[m,:]) w[m,:]
+ * in place, for optimisers that do not fold the projection into their update. */
+int sc_project_rows(float* g, const float* w, int64_t M, int64_t D, void* stream);
+
+/* optimizer="signum" of the reference Trainer (sparsify/trainer.py:146-161):
+ * SignSGD (sparsify/sign_sgd.py:18-26, p -= lr * sign(g)) inside the
+ * third-party schedulefree.ScheduleFreeWrapper(momentum=0.95), one fused pass.
+ * p holds y (training mode), z the wrapped optimiser's iterate, ckp1 the
+ * averaging weight of this step (weight / weight_sum, computed on the host):
+ *   x = y + (1 - 1/momentum)(z - y);  z -= lr * sign(g);
+ *   x += ckp1 (z - x);                y = x + (1 - momentum)(z - x).
+ * Optionally refreshes a bf16 shadow of p. */
+int sc_signum_schedulefree(float* p, float* z, const float* g, int64_t n, float lr,
+                           float momentum, float ckp1, void* shadow_bf16, void* stream);
+
 /* fp32 -> bf16 copy (shadow refresh). */
 int sc_cast_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
 

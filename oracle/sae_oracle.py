@@ -271,6 +271,117 @@ def quintic_newtonschulz(G: Tensor, steps: int = 5) -> Tensor:
     return X
 
 
+
+# ----------------------------------------------------------------------------- signum
+def default_signum_lr(num_latents: int) -> float:
+    """sparsify/trainer.py:152: lr = 5e-3 / sqrt(num_latents / 2**14)."""
+    return 5e-3 / (num_latents / 2 ** 14) ** 0.5
+
+
+def sign_sgd_step_(p: Tensor, g: Tensor, lr: float) -> None:
+    """sparsify/sign_sgd.py:18-26."""
+    p.add_(g.sign(), alpha=-lr)
+
+
+class ScheduleFreeWrapperPort:
+    """Restatement of ``schedulefree.ScheduleFreeWrapper`` (third-party package
+    "schedulefree", facebookresearch/schedule_free; the reference lists it
+    unpinned in pyproject.toml and it is not available offline, so this follows
+    the published algorithm of Defazio et al. 2024, "The Road Less Scheduled",
+    in the wrapper form the reference calls at sparsify/trainer.py:158-159,
+    652-654,675-677). PARITY UNPINNED for this class: there is no copy of the
+    package to check it against; SignSGD, the learning-rate rule and the
+    Trainer's use of train()/eval() are the reference's own code.
+
+    The wrapped optimiser's parameters hold y while training; state z is the
+    base optimiser's iterate; x = y + (1 - 1/beta)(z - y) is the average.
+    """
+
+    def __init__(self, base, weight_decay_at_y: float = 0.0, momentum: float = 0.9,
+                 weight_lr_power: float = 2.0, r: float = 0.0):
+        self.base = base
+        self.state: dict = {}
+        for group in self.param_groups:
+            group.update(weight_decay_at_y=weight_decay_at_y, momentum=momentum,
+                         weight_lr_power=weight_lr_power, r=r, k=0, lr_max=-1.0, weight_sum=0.0,
+                         train_mode=False)
+
+    @property
+    def param_groups(self):
+        return self.base.param_groups
+
+    def zero_grad(self, set_to_none: bool = True):
+        return self.base.zero_grad(set_to_none)
+
+    def state_dict(self):
+        return {"z": [self.state[p]["z"] for g in self.param_groups for p in g["params"] if p in self.state],
+                "groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+
+    @torch.no_grad()
+    def eval(self):
+        for group in self.param_groups:
+            if group["train_mode"]:
+                for p in group["params"]:
+                    if p in self.state:
+                        p.lerp_(end=self.state[p]["z"], weight=1 - 1 / group["momentum"])  # y -> x
+                group["train_mode"] = False
+
+    @torch.no_grad()
+    def train(self):
+        for group in self.param_groups:
+            if not group["train_mode"]:
+                for p in group["params"]:
+                    if p in self.state:
+                        p.lerp_(end=self.state[p]["z"], weight=1 - group["momentum"])      # x -> y
+                group["train_mode"] = True
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        assert closure is None
+        for group in self.param_groups:
+            assert group["train_mode"], "call .train() first"
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state.setdefault(p, {})
+                if "z" not in st:
+                    st["z"] = p.detach().clone()
+                z = st["z"]
+                if group["weight_decay_at_y"] != 0.0:
+                    wd = group["lr"] * group["weight_decay_at_y"]
+                    z.sub_(p, alpha=wd)
+                    p.sub_(p, alpha=wd * (1 - group["momentum"]))
+                p.lerp_(end=z, weight=1 - 1 / group["momentum"])       # y -> x
+                tmp = p.detach().clone()                                # p <- z, z-buffer <- x
+                p.copy_(z)
+                z.copy_(tmp)
+        self.base.step()                                                # the wrapped step acts on z
+        for group in self.param_groups:
+            k, lr = group["k"], group["lr"]
+            lr_max = group["lr_max"] = max(lr, group["lr_max"])
+            weight = ((k + 1) ** group["r"]) * (lr_max ** group["weight_lr_power"])
+            weight_sum = group["weight_sum"] = group["weight_sum"] + weight
+            ckp1 = weight / weight_sum if weight_sum != 0 else 0.0
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                z = self.state[p]["z"]
+                tmp = p.detach().clone()                                # p <- x, z-buffer <- new z
+                p.copy_(z)
+                z.copy_(tmp)
+                p.lerp_(end=z, weight=ckp1)                             # x <- x + c (z - x)
+                p.lerp_(end=z, weight=1 - group["momentum"])            # y
+            group["k"] = k + 1
+
+
+def signum_schedulefree_step_(y: Tensor, z: Tensor, g: Tensor, lr: float, momentum: float, ckp1: float) -> None:
+    """One step of ScheduleFreeWrapperPort(SignSGD) on a single tensor, in place on (y, z)."""
+    x = torch.lerp(y, z, 1 - 1 / momentum)
+    sign_sgd_step_(z, g, lr)
+    x.lerp_(z, ckp1)
+    y.copy_(torch.lerp(x, z, 1 - momentum))
+
+
 class OracleTrainer:
     """One SAE trained the way sparsify/trainer.py:340-447,510-538 does it with
     loss_fn="fvu" and Adam: step-0 b_dec init, decoder normalisation before each
@@ -279,11 +390,18 @@ class OracleTrainer:
 
     def __init__(self, params: dict, cfg: OracleCfg, *, lr: float | None = None, warmup: int = 1000,
                  total_steps: int = 1000, auxk_alpha: float = 0.0, dead_threshold: int = 10_000_000,
-                 round_operands=None):
+                 round_operands=None, optimizer: str = "adam", momentum: float = 0.95):
         self.p = params
         self.cfg = cfg
         M = params["W_enc"].shape[0]
-        self.base_lr = lr or default_adam_lr(M)
+        self.optimizer = optimizer
+        self.momentum = momentum
+        if optimizer == "signum":  # trainer.py:146-161: no scheduler, constant lr
+            self.base_lr = lr or default_signum_lr(M)
+            self.z = {n: None for n in params}
+            self.weight_sum = 0.0
+        else:
+            self.base_lr = lr or default_adam_lr(M)
         self.warmup, self.total = warmup, total_steps
         self.auxk_alpha = auxk_alpha
         self.dead_threshold = dead_threshold
@@ -306,9 +424,18 @@ class OracleTrainer:
                                    round_operands=self.rnd)
         if self.cfg.normalize_decoder and not self.cfg.transcode:
             project_out_parallel_(res.grads["W_dec"], self.p["W_dec"])     # trainer.py:513-515
-        lr = linear_warmup_lr(self.base_lr, self.global_step, self.warmup, self.total)
-        for n in self.p:
-            adam_step_(self.p[n], res.grads[n], self.m[n], self.v[n], self.global_step + 1, lr)
+        if self.optimizer == "signum":
+            lr = self.base_lr
+            self.weight_sum += lr ** 2          # weight_lr_power=2, r=0, constant lr
+            for n in self.p:
+                if self.z[n] is None:
+                    self.z[n] = self.p[n].clone()
+                signum_schedulefree_step_(self.p[n], self.z[n], res.grads[n], lr, self.momentum,
+                                          lr ** 2 / self.weight_sum)
+        else:
+            lr = linear_warmup_lr(self.base_lr, self.global_step, self.warmup, self.total)
+            for n in self.p:
+                adam_step_(self.p[n], res.grads[n], self.m[n], self.v[n], self.global_step + 1, lr)
         fired = torch.zeros_like(self.num_tokens_since_fired, dtype=torch.bool)
         fired[res.latent_indices.reshape(-1)] = True
         self.num_tokens_since_fired += x.shape[0]                          # trainer.py:529-533

@@ -26,6 +26,17 @@ normalize_rows_kernel(float* __restrict__ W, int64_t D, float eps,
   }
 }
 
+// g[m,:] -= (g[m,:] . w[m,:]) w[m,:]: the second pass re-reads the row from L1/L2.
+__global__ void __launch_bounds__(kRowThreads)
+project_rows_kernel(float* __restrict__ g, const float* __restrict__ w, int64_t D) {
+  __shared__ float scratch[33];
+  const int64_t off = (int64_t)blockIdx.x * D;
+  float dot = 0.f;
+  for (int64_t c = threadIdx.x; c < D; c += blockDim.x) dot = fmaf(g[off + c], w[off + c], dot);
+  dot = sc::block_sum(dot, scratch);
+  for (int64_t c = threadIdx.x; c < D; c += blockDim.x) g[off + c] -= dot * w[off + c];
+}
+
 struct AdamArgs {
   float lr, beta1, beta2, eps;
   float bc1;       // 1 - beta1^step
@@ -182,6 +193,52 @@ adam_flat_vec_kernel(float* __restrict__ p, const float* __restrict__ g, float* 
   }
 }
 
+// Schedule-free wrapper around sign descent, one fused elementwise pass. The
+// parameter buffer holds y (where the gradient was taken), `z` the base
+// optimiser's iterate. x is recovered from y and z, z takes the sign step, x
+// moves towards the new z by the averaging weight c, and y is re-extrapolated:
+//   x  = y + (1 - 1/beta)(z - y);  z' = z - lr sign(g);
+//   x' = x + c (z' - x);           y' = x' + (1 - beta)(z' - x').
+struct SignumArgs { float lr, beta, c; };
+
+__device__ __forceinline__ float signum_sf_update(float y, float& z, float g, const SignumArgs a) {
+  const float x = y + (1.f - 1.f / a.beta) * (z - y);
+  const float sgn = (g > 0.f) ? 1.f : ((g < 0.f) ? -1.f : 0.f);
+  z = z - a.lr * sgn;
+  const float xn = x + a.c * (z - x);
+  return xn + (1.f - a.beta) * (z - xn);
+}
+
+__global__ void __launch_bounds__(256)
+signum_sf_vec_kernel(float4* __restrict__ p, float4* __restrict__ z, const float4* __restrict__ g,
+                     int64_t n4, SignumArgs a, __nv_bfloat16* __restrict__ shadow) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float4 y = p[i], zz = z[i];
+    const float4 gg = g[i];
+    y.x = signum_sf_update(y.x, zz.x, gg.x, a);
+    y.y = signum_sf_update(y.y, zz.y, gg.y, a);
+    y.z = signum_sf_update(y.z, zz.z, gg.z, a);
+    y.w = signum_sf_update(y.w, zz.w, gg.w, a);
+    p[i] = y;
+    z[i] = zz;
+    if (shadow != nullptr) store_bf16x4(shadow + 4 * i, y);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+signum_sf_kernel(float* __restrict__ p, float* __restrict__ z, const float* __restrict__ g, int64_t n,
+                 SignumArgs a, __nv_bfloat16* __restrict__ shadow) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float zz = z[i];
+    const float y = signum_sf_update(p[i], zz, g[i], a);
+    p[i] = y;
+    z[i] = zz;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(y);
+  }
+}
+
 int flat_grid(int64_t total) {
   int64_t b = (total + 255) / 256;
   const int64_t cap = 148 * 32;
@@ -241,5 +298,35 @@ extern "C" int sc_cast_bf16(const float* src, void* dst_bf16, int64_t n, void* s
   cast_bf16_kernel<<<flat_grid(n), 256, 0, sc::as_stream(stream)>>>(
       src, static_cast<__nv_bfloat16*>(dst_bf16), n);
   SC_CHECK_LAUNCH("sc_cast_bf16");
+  return SC_OK;
+}
+
+extern "C" int sc_signum_schedulefree(float* p, float* z, const float* g, int64_t n, float lr,
+                                      float momentum, float ckp1, void* shadow_bf16, void* stream) {
+  SC_REQUIRE(n >= 0, "sc_signum_schedulefree: bad size");
+  if (n == 0) return SC_OK;
+  SC_REQUIRE(p && z && g, "sc_signum_schedulefree: null pointer");
+  SC_REQUIRE(momentum > 0.f && momentum <= 1.f, "sc_signum_schedulefree: momentum %g outside (0, 1]", (double)momentum);
+  SignumArgs a;
+  a.lr = lr; a.beta = momentum; a.c = ckp1;
+  __nv_bfloat16* shadow = static_cast<__nv_bfloat16*>(shadow_bf16);
+  cudaStream_t st = sc::as_stream(stream);
+  const bool vec = n % 4 == 0 && sc::aligned(p, 16) && sc::aligned(z, 16) && sc::aligned(g, 16) &&
+                   (shadow == nullptr || sc::aligned(shadow, 8));
+  if (vec)
+    signum_sf_vec_kernel<<<flat_grid(n / 4), 256, 0, st>>>(reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(z),
+                                                          reinterpret_cast<const float4*>(g), n / 4, a, shadow);
+  else
+    signum_sf_kernel<<<flat_grid(n), 256, 0, st>>>(p, z, g, n, a, shadow);
+  SC_CHECK_LAUNCH("sc_signum_schedulefree");
+  return SC_OK;
+}
+
+extern "C" int sc_project_rows(float* g, const float* w, int64_t M, int64_t D, void* stream) {
+  SC_REQUIRE(M >= 0 && D > 0 && M <= 0x7fffffffLL, "sc_project_rows: bad shape");
+  if (M == 0) return SC_OK;
+  SC_REQUIRE(g && w, "sc_project_rows: null pointer");
+  project_rows_kernel<<<(unsigned)M, kRowThreads, 0, sc::as_stream(stream)>>>(g, w, D);
+  SC_CHECK_LAUNCH("sc_project_rows");
   return SC_OK;
 }

@@ -347,6 +347,28 @@ def adam_rows_(p: Tensor, g: Tensor, m: Tensor, v: Tensor, *, lr: float, beta1: 
              float(beta2), float(eps), int(step), int(bool(project)), ptr(shadow), _stream(p))
 
 
+def project_rows_(g: Tensor, w: Tensor) -> None:
+    """g[m] -= (g[m] . w[m]) w[m] in place (sparsify/sparse_coder.py:281-295)."""
+    _check_cuda(g, w)
+    assert g.dtype == w.dtype == torch.float32 and g.is_contiguous() and w.is_contiguous() and g.shape == w.shape
+    M, D = g.shape
+    with torch.cuda.device(g.device):
+        call("sc_project_rows", ptr(g), ptr(w), M, D, _stream(g))
+
+
+def signum_schedulefree_(p: Tensor, z: Tensor, g: Tensor, lr: float, momentum: float, ckp1: float,
+                         shadow: Tensor | None = None) -> None:
+    """One schedule-free sign-descent step in place on (p, z); see sc_signum_schedulefree."""
+    _check_cuda(p, z, g, shadow)
+    for t in (p, z, g):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == p.numel()
+    if shadow is not None:
+        assert shadow.dtype == torch.bfloat16 and shadow.is_contiguous() and shadow.numel() == p.numel()
+    with torch.cuda.device(p.device):
+        call("sc_signum_schedulefree", ptr(p), ptr(z), ptr(g), p.numel(), float(lr), float(momentum),
+             float(ckp1), ptr(shadow), _stream(p))
+
+
 def cast_bf16(src: Tensor, dst: Tensor | None = None) -> Tensor:
     _check_cuda(src, dst)
     src = src.detach()

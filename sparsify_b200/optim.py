@@ -258,3 +258,90 @@ class FusedAdam(torch.optim.Optimizer):
                 )
                 if cb is not None:
                     cb()
+
+
+class ScheduleFreeSignum(torch.optim.Optimizer):
+    """optimizer="signum" of the reference Trainer (sparsify/trainer.py:146-161):
+    ``ScheduleFreeWrapper(SignSGD(params), momentum=0.95)`` as one optimiser
+    whose step is a single fused kernel per parameter.
+
+    SignSGD is the reference's own (sparsify/sign_sgd.py:18-26): p -= lr*sign(g).
+    The wrapper comes from the third-party ``schedulefree`` package (Defazio et
+    al., "The Road Less Scheduled", 2024; the reference does not pin a version),
+    restated here from its published algorithm: the parameter tensor holds the
+    gradient-evaluation point y while training, ``state["z"]`` the wrapped
+    optimiser's iterate, and the running average x is implied by the two:
+
+        x = y + (1 - 1/momentum)(z - y)            # un-extrapolate
+        z = z - lr * sign(grad(y))                 # the wrapped step
+        x = x + c_{k+1} (z - x),  c = w_k / sum w  # w_k = (k+1)^r * lr_max^weight_lr_power
+        y = x + (1 - momentum)(z - x)              # extrapolate
+
+    ``eval()`` turns the parameters into x (what a checkpoint stores), ``train()``
+    back into y. Gradients projected by ``project_rows`` lose their component
+    along the parameter rows before the sign is taken.
+    """
+
+    def __init__(self, params, lr: float = 1e-3, momentum: float = 0.9, weight_lr_power: float = 2.0,
+                 r: float = 0.0):
+        if lr <= 0.0:
+            raise ValueError(f"Invalid learning rate: {lr}")
+        if not 0.0 < momentum <= 1.0:
+            raise ValueError(f"Invalid momentum: {momentum}")
+        defaults = dict(lr=lr, momentum=momentum, weight_lr_power=weight_lr_power, r=r, k=0, lr_max=-1.0,
+                        weight_sum=0.0, train_mode=False)
+        super().__init__(params, defaults)
+        self._project: set[int] = set()
+        self._shadow: dict[int, tuple] = {}
+
+    project_rows = FusedAdam.project_rows
+    register_shadow = FusedAdam.register_shadow
+
+    @torch.no_grad()
+    def eval(self):
+        for group in self.param_groups:
+            if group["train_mode"]:
+                for p in group["params"]:
+                    if "z" in self.state[p]:
+                        p.lerp_(end=self.state[p]["z"], weight=1 - 1 / group["momentum"])  # y -> x
+                group["train_mode"] = False
+
+    @torch.no_grad()
+    def train(self):
+        for group in self.param_groups:
+            if not group["train_mode"]:
+                for p in group["params"]:
+                    if "z" in self.state[p]:
+                        p.lerp_(end=self.state[p]["z"], weight=1 - group["momentum"])  # x -> y
+                group["train_mode"] = True
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        assert closure is None, "Closure is not supported."
+        for group in self.param_groups:
+            if not group["train_mode"]:
+                raise RuntimeError("Not in train mode: call .train() before stepping (and .eval() to "
+                                   "read the averaged parameters)")
+            lr = group["lr"]
+            lr = float(lr) if not isinstance(lr, Tensor) else float(lr.item())
+            k = group["k"]
+            lr_max = group["lr_max"] = max(lr, group["lr_max"])
+            weight = ((k + 1) ** group["r"]) * (lr_max ** group["weight_lr_power"])
+            weight_sum = group["weight_sum"] = group["weight_sum"] + weight
+            ckp1 = weight / weight_sum if weight_sum != 0 else 0.0
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                state = self.state[p]
+                if "z" not in state:
+                    state["z"] = torch.clone(p.data, memory_format=torch.contiguous_format)
+                g = p.grad
+                if g.dtype != torch.float32 or not g.is_contiguous():
+                    g = g.to(torch.float32).contiguous()
+                if id(p) in self._project and p.dim() == 2:
+                    ops.project_rows_(g, p.data)
+                shadow, cb = self._shadow.get(id(p), (None, None))
+                ops.signum_schedulefree_(p.data, state["z"], g, lr, group["momentum"], ckp1, shadow)
+                if cb is not None:
+                    cb()
+            group["k"] = k + 1

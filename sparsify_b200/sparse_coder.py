@@ -365,8 +365,11 @@ class SparseCoder(nn.Module):
         assert self.W_dec is not None, "Decoder weight was not initialized."
         assert self.W_dec.grad is not None
         g, w = self.W_dec.grad, self.W_dec.data
-        parallel = (g * w).sum(dim=1, keepdim=True)
-        g -= parallel * w
+        if g.is_cuda and g.dtype == torch.float32 and g.is_contiguous() and w.is_contiguous():
+            ops.project_rows_(g, w)
+        else:  # host tensors (construction-time use only)
+            parallel = (g * w).sum(dim=1, keepdim=True)
+            g -= parallel * w
 
 
 # Allow for alternate naming conventions

@@ -36,7 +36,7 @@ from torch.utils.data import DataLoader
 from . import parallel
 from .config import TrainConfig
 from .muon import Muon
-from .optim import FusedAdam
+from .optim import FusedAdam, ScheduleFreeSignum
 from .sparse_coder import SparseCoder, natsorted
 from .utils import get_layer_list, resolve_widths
 
@@ -127,10 +127,17 @@ class Trainer:
                     linear_schedule_with_warmup(self.optimizers[1], cfg.lr_warmup_steps, num_batches),
                 ]
             case "signum":
-                raise NotImplementedError(
-                    "optimizer='signum' wraps SignSGD in the third-party schedulefree package, "
-                    "which this package does not provide; use 'adam' or 'muon'"
-                )
+                pgs = [dict(params=list(sae.parameters()),
+                            lr=cfg.lr or 5e-3 / (sae.num_latents / (2 ** 14)) ** 0.5)
+                       for sae in self.saes.values()]
+                lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
+                opt = ScheduleFreeSignum(pgs, momentum=0.95)
+                for sae in self.saes.values():
+                    sae.attach_optimizer(opt)
+                    sae.ragged_tokens = bool(cfg.exclude_tokens)
+                opt.train()
+                self.optimizers = [opt]
+                self.lr_schedulers = []
             case other:
                 raise ValueError(f"Unknown optimizer '{other}'")
 
@@ -398,6 +405,9 @@ class Trainer:
         and on rank 0 lr_scheduler_i.pt, optimizer_i.pt, state.pt, config.json; every
         saving rank writes rank_{r}_state.pt."""
         print("Saving checkpoint")
+        for optimizer in self.optimizers:
+            if isinstance(optimizer, ScheduleFreeSignum):
+                optimizer.eval()  # the checkpoint stores the averaged parameters (trainer.py:652-654)
         for name, sae in saes.items():
             assert isinstance(sae, SparseCoder)
             sae.save_to_disk(f"{path}/{name}")
@@ -414,6 +424,10 @@ class Trainer:
                 with open(f"{path}/metrics.jsonl", "w") as f:
                     for row in self.metrics:
                         f.write(json.dumps(row) + "\n")
+
+        for optimizer in self.optimizers:
+            if isinstance(optimizer, ScheduleFreeSignum):
+                optimizer.train()
 
         rank = 0 if rank_zero else dist.get_rank()
         os.makedirs(path, exist_ok=True)

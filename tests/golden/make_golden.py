@@ -5,8 +5,10 @@ with seeded inputs. Run once where the reference tree is available:
     SPARSIFY_REF=/path/to/sparsify python tests/golden/make_golden.py
 
 The reference's non-arithmetic dependencies that are not installed here
-(natsort, simple_parsing, accelerate, schedulefree) are replaced by small stub
-modules; none of them takes part in the arithmetic that is frozen. The fixtures
+(natsort, simple_parsing, accelerate) are replaced by small stub modules that
+take no part in the arithmetic that is frozen; schedulefree's wrapper class,
+which only the optimizer="signum" fixture uses, is replaced by the oracle's
+restatement of its published algorithm. The fixtures
 are what the oracle (oracle/sae_oracle.py) is pinned against.
 """
 
@@ -65,8 +67,13 @@ def import_reference():
     acc_utils.send_to_device = lambda obj, device: obj
     acc.utils = acc_utils
 
+    # schedulefree is not installed: its wrapper is replaced by the oracle's restatement of the
+    # published algorithm (only the optimizer="signum" fixture depends on it; that fixture pins
+    # SignSGD, the learning-rate rule and the Trainer's glue, not the wrapper itself)
+    sys.path.insert(0, str(HERE.parent.parent))
+    from oracle.sae_oracle import ScheduleFreeWrapperPort
     sf = types.ModuleType("schedulefree")
-    sf.ScheduleFreeWrapper = type("ScheduleFreeWrapper", (), {})
+    sf.ScheduleFreeWrapper = ScheduleFreeWrapperPort
 
     for name, mod in [("natsort", natsort), ("simple_parsing", sp), ("accelerate", acc),
                       ("accelerate.utils", acc_utils), ("schedulefree", sf)]:
@@ -292,6 +299,50 @@ def gen_trainer_muon(sparsify):
         save("trainer_muon", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=2e-3, warmup=2))
 
 
+def gen_trainer_signum(sparsify):
+    """The reference Trainer with optimizer="signum" (its SignSGD inside the
+    schedule-free wrapper, here the oracle's restatement of that third-party
+    class) for a few steps on stored activations; the final parameters are read
+    after the end-of-run checkpoint, i.e. back in training mode (y)."""
+    from sparsify import SparseCoderConfig, TrainConfig, Trainer
+    from safetensors.torch import load_file
+    steps, B, T, D, M, k = 5, 4, 16, 32, 256, 4
+    g = torch.Generator().manual_seed(8)
+    atoms = torch.nn.functional.normalize(torch.randn(512, D, generator=g), dim=1)
+    ids = torch.randint(0, 512, (steps, B, T, 6), generator=g)
+    coef = -torch.log1p(-torch.rand(steps, B, T, 6, generator=g))
+    acts = (atoms[ids] * coef.unsqueeze(-1)).sum(-2) + 0.05 * torch.randn(steps, B, T, D, generator=g)
+    model = FakeModel(acts)
+    dataset = [{"input_ids": torch.zeros(T, dtype=torch.long)} for _ in range(steps * B)]
+    fvus = []
+    with tempfile.TemporaryDirectory() as tmp:
+        cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="signum", lr=1e-3,
+                          hookpoints=["layers.0"], log_to_wandb=False, save_dir=tmp, run_name="golden",
+                          save_every=10**9)
+        trainer = Trainer(cfg, dataset, model)
+        sae = trainer.saes["layers.0"]
+        init = dict(W_enc=sae.encoder.weight.detach().clone(), b_enc=sae.encoder.bias.detach().clone(),
+                    W_dec=sae.W_dec.detach().clone(), b_dec=sae.b_dec.detach().clone())
+        orig_forward = sae.forward
+
+        def recording_forward(*a, **kw):
+            out = orig_forward(*a, **kw)
+            fvus.append(out.fvu.detach().clone())
+            return out
+
+        sae.forward = recording_forward
+        trainer.fit()
+        saved = load_file(f"{tmp}/golden/layers.0/sae.safetensors")  # averaged parameters (x)
+        t = dict(acts=acts, fvu=torch.stack(fvus))
+        for k_, v in init.items():
+            t[f"init.{k_}"] = v
+        for k_, v in dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec).items():
+            t[f"final.{k_}"] = v
+        for k_, name in dict(W_enc="encoder.weight", b_enc="encoder.bias", W_dec="W_dec", b_dec="b_dec").items():
+            t[f"saved.{k_}"] = saved[name]
+        save("trainer_signum", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=1e-3))
+
+
 def gen_trajectory200(sparsify):
     """200 optimiser steps of the reference Trainer at the CPU configuration
     (d_in=768, 24576 latents, k=32, 4096 tokens/step, fp32, Adam, AuxK enabled)
@@ -344,6 +395,7 @@ if __name__ == "__main__":
     gen_forward(ref)
     gen_trainer(ref)
     gen_trainer_muon(ref)
+    gen_trainer_signum(ref)
     gen_muon(ref)
     if "--trajectory" in sys.argv:  # about three minutes of CPU time on 8 threads
         gen_trajectory200(ref)

@@ -73,3 +73,48 @@ def test_compute_on_cpu_fails_loudly():
     sae = SparseCoder(16, SparseCoderConfig(num_latents=64, k=4), device="cpu")
     with pytest.raises(RuntimeError, match="no CPU path"):
         sae(torch.randn(4, 16))
+
+
+def test_trainer_construction_k_decay_and_lr_on_host(tmp_path):
+    """The Trainer builds its sparse coders, plan, learning rates and k schedule on
+    the host (trainer.py:63-145,176-177,229-235); only fit() needs the GPU."""
+    from sparsify_b200 import TrainConfig, Trainer
+    from tests.fake_model import FakeModel, dataset
+    acts = [torch.zeros(2, 2, 8, 16), torch.zeros(2, 2, 8, 16)]
+    cfg = TrainConfig(SparseCoderConfig(num_latents=64, k=4), batch_size=2, hookpoints=["layers.1", "layers.0"],
+                      k_decay_steps=10, log_to_wandb=False, save_dir=str(tmp_path), run_name="r")
+    tr = Trainer(cfg, dataset(2, 2, 8), FakeModel(acts))
+    assert list(tr.saes) == ["layers.0", "layers.1"]  # natural order
+    assert tr.initial_k == min(64, 16 * 10) and tr.final_k == 4
+    ks = []
+    for step in (0, 5, 10, 50):
+        tr.global_step = step
+        ks.append(tr.get_current_k())
+    assert ks == [64, round(64 * 0.5 + 4 * 0.5), 4, 4]
+    # the default optimiser is "signum": lr rule of trainer.py:152, no scheduler, training mode
+    assert tr.lr_schedulers == [] and len(tr.optimizers) == 1
+    for g in tr.optimizers[0].param_groups:
+        assert abs(g["lr"] - 5e-3 / (64 / 2 ** 14) ** 0.5) < 1e-12 and g["momentum"] == 0.95 and g["train_mode"]
+    cfg2 = TrainConfig(SparseCoderConfig(num_latents=64, k=4), batch_size=2, hookpoints=["layers.0"],
+                       optimizer="adam", log_to_wandb=False, save_dir=str(tmp_path), run_name="r")
+    tr2 = Trainer(cfg2, dataset(2, 2, 8), FakeModel(acts))
+    for g in tr2.optimizers[0].param_groups:  # trainer.py:109, scheduler starts at lr 0
+        assert abs(g["initial_lr"] - 2e-4 / (64 / 2 ** 14) ** 0.5) < 1e-12 and g["lr"] == 0.0
+    with pytest.raises(ValueError):
+        Trainer(TrainConfig(SparseCoderConfig(num_latents=64, k=4), batch_size=2, hookpoints=["layers.0"],
+                            optimizer="sgd", log_to_wandb=False), dataset(2, 2, 8), FakeModel(acts))
+
+
+def test_load_many_layers_and_pattern(tmp_path):
+    torch.manual_seed(0)
+    for name in ("layers.0", "layers.2", "layers.10", "other.1"):
+        SparseCoder(8, SparseCoderConfig(num_latents=16, k=2), device="cpu").save_to_disk(tmp_path / name)
+    all_ = SparseCoder.load_many(str(tmp_path), local=True)
+    assert list(all_) == ["layers.0", "layers.2", "layers.10", "other.1"]
+    some = SparseCoder.load_many(str(tmp_path), local=True, layers=["layers.10", "layers.2"])
+    assert list(some) == ["layers.2", "layers.10"]
+    # as in the reference (sparse_coder.py:87,99-103) the pattern gets "/*" appended for the hub
+    # download and is then matched against bare directory names, so locally it selects nothing
+    assert SparseCoder.load_many(str(tmp_path), local=True, pattern="layers.1*") == {}
+    with pytest.raises(NotImplementedError):
+        SparseCoder.load_many("someone/some-repo")

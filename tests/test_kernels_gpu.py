@@ -295,3 +295,34 @@ def test_decode_residual(cuda_lib, ydtype):
     gacts16 = ops.embedding_bag_bwd_acts(idx.cuda(), e16, W.cuda().bfloat16())
     _, gacts_ref = O.decode_backward(idx, acts, W, e16.float().cpu())
     assert rel_l2(gacts16, gacts_ref) < F32_TOL
+
+
+@pytest.mark.parametrize("n", [4096 * 3, 1001])
+def test_signum_schedulefree_kernel(cuda_lib, n):
+    """sc_signum_schedulefree against the oracle's restatement, several steps, with the bf16 copy."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    y = torch.randn(n, generator=g); z = y.clone()
+    yd, zd = y.cuda(), z.cuda()
+    shadow = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    lr, beta, wsum = 3e-3, 0.95, 0.0
+    for step in range(4):
+        grad = torch.randn(n, generator=g)
+        grad[::7] = 0.0  # sign(0) = 0
+        wsum += lr ** 2
+        c = lr ** 2 / wsum
+        O.signum_schedulefree_step_(y, z, grad, lr, beta, c)
+        ops.signum_schedulefree_(yd, zd, grad.cuda(), lr, beta, c, shadow)
+    assert rel_l2(yd, y) < 1e-6 and rel_l2(zd, z) < 1e-6
+    assert torch.equal(shadow, yd.bfloat16())
+
+
+def test_project_rows_kernel(cuda_lib):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    grad, w = torch.randn(37, 100, generator=g), torch.nn.functional.normalize(torch.randn(37, 100, generator=g), dim=1)
+    want = grad.clone()
+    O.project_out_parallel_(want, w)
+    gd = grad.cuda()
+    ops.project_rows_(gd, w.cuda())
+    assert rel_l2(gd, want) < 1e-6

@@ -90,6 +90,21 @@ def test_trainer_trajectory():
     assert torch.equal(tr.num_tokens_since_fired, t["num_tokens_since_fired"])
 
 
+def test_trainer_signum_trajectory():
+    """optimizer="signum": the reference Trainer's own SignSGD, learning-rate rule and
+    step order around the schedule-free wrapper (whose restatement both sides share)."""
+    t, meta = load_golden("trainer_signum")
+    params = _params(t, "init.")
+    tr = O.OracleTrainer(params, O.OracleCfg(k=meta["k"]), lr=meta["lr"], optimizer="signum")
+    fvus = [float(tr.step(t["acts"][s].reshape(-1, meta["D"])).fvu) for s in range(meta["steps"])]
+    for a, b in zip(fvus, t["fvu"].tolist()):
+        assert abs(a - b) < 5e-4 * max(1.0, abs(b)), (fvus, t["fvu"].tolist())
+    for pname in ("W_enc", "b_enc", "W_dec", "b_dec"):
+        assert rel_l2(params[pname], t[f"final.{pname}"]) < 5e-3, pname
+        x = torch.lerp(params[pname], tr.z[pname], 1 - 1 / 0.95)  # what eval() stores in the checkpoint
+        assert rel_l2(x, t[f"saved.{pname}"]) < 5e-3, pname
+
+
 def test_newtonschulz():
     for name in ("wide", "tall"):
         t, _ = load_golden(f"newtonschulz_{name}")

@@ -18,8 +18,8 @@ def make_trainer(tmp_path, meta, acts, precision, **over):
     SparseCoder.default_precision = precision
     try:
         cfg = TrainConfig(
-            SparseCoderConfig(num_latents=meta["M"], k=meta["k"]), batch_size=meta["B"], optimizer="adam",
-            lr=meta["lr"], lr_warmup_steps=meta["warmup"], auxk_alpha=meta["auxk_alpha"],
+            SparseCoderConfig(num_latents=meta["M"], k=meta["k"]), batch_size=meta["B"],
+            optimizer=over.pop("optimizer", "adam"), lr=meta["lr"], lr_warmup_steps=meta["warmup"], auxk_alpha=meta["auxk_alpha"],
             dead_feature_threshold=meta["dead_feature_threshold"], hookpoints=["layers.0"],
             log_to_wandb=False, save_dir=str(tmp_path), run_name="run", save_every=10 ** 9, **over)
         model = FakeModel(acts, device="cuda")
@@ -132,3 +132,31 @@ def test_fvu_trajectory_200_steps(cuda_lib, tmp_path):
     worst = max(abs(a - b) / b for a, b in zip(fvus, want))
     assert worst < 0.02, (worst, fvus[::20], want[::20])
     assert fvus[-1] < fvus[0] - 0.05  # it trained
+
+
+def test_signum_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
+    """optimizer="signum" (the reference's default): fused schedule-free sign-descent kernel
+    against the reference Trainer's trajectory (tests/golden/trainer_signum.safetensors)."""
+    from safetensors.torch import load_file
+    t, meta = load_golden("trainer_signum")
+    full = dict(meta, warmup=0, auxk_alpha=0.0, dead_feature_threshold=10_000_000)
+    trainer = make_trainer(tmp_path, full, t["acts"], "fp32", optimizer="signum")
+    assert trainer.lr_schedulers == []
+    sae = trainer.saes["layers.0"]
+    with torch.no_grad():
+        sae.encoder.weight.copy_(t["init.W_enc"]); sae.encoder.bias.copy_(t["init.b_enc"])
+        sae.W_dec.copy_(t["init.W_dec"]); sae.b_dec.copy_(t["init.b_dec"])
+    trainer.fit()
+    fvus = [row["fvu/layers.0"] for row in trainer.metrics]
+    for got, want in zip(fvus, t["fvu"].tolist()):
+        assert abs(got - want) < 1e-3 * max(1.0, abs(want)), (fvus, t["fvu"].tolist())
+    # after the end-of-run checkpoint the parameters are back at the training point y ...
+    live = dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec)
+    for name, p in live.items():
+        assert rel_l2(p.detach(), t[f"final.{name}"]) < 5e-3, name
+    # ... and the checkpoint holds the averaged parameters x (trainer.py:652-654)
+    saved = load_file(str(tmp_path / "run" / "layers.0" / "sae.safetensors"))
+    for name, key in dict(W_enc="encoder.weight", b_enc="encoder.bias", W_dec="W_dec", b_dec="b_dec").items():
+        assert rel_l2(saved[key], t[f"saved.{name}"]) < 5e-3, name
+    st = torch.load(tmp_path / "run" / "optimizer_0.pt")
+    assert st["param_groups"][0]["k"] == meta["steps"] and st["param_groups"][0]["train_mode"] is False
