@@ -60,7 +60,7 @@ def parse_args():
                          "active in every step; 0 = the natural state (no latent dead yet)")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone on random inputs of the given sizes instead of the step: "
-                         "encode | decode | bwd_acts | csr | rows | adam | normalize | all")
+                         "encode | decode | bwd_acts | csr | rows | adam | normalize | all | ns | gemm")
     return ap.parse_args()
 
 
@@ -445,6 +445,32 @@ def run_kernel(a):
 
     which = a.kernel
     results = []
+    if which in ("ns", "gemm"):
+        # Muon's Newton-Schulz on one [latents, d] matrix, and its three products
+        from sparsify_b200.muon import quintic_newtonschulz
+        del x
+        G = torch.randn(M, D, device=dev, generator=g)
+        if which == "ns":
+            ms = timed(lambda: quintic_newtonschulz(G, 5), reps=3)
+            flops = 5 * (2 * D * D * M * 2 + 2 * D * D * D)  # as a library computes it, no symmetry
+            results.append(dict(kernel="newtonschulz5", ms=ms, tflops_equiv=flops / ms / 1e9,
+                                frac=flops / ms / 1e9 / peaks["tflops"]))
+        else:
+            Wd = W.T.contiguous()                               # wide [D, M]
+            A = ops.gemm_nt(Wd, Wd)
+            for name, fn, fl in (
+                ("gemm_XXt", lambda: ops.gemm_nt(Wd, Wd), 2 * D * D * M),
+                ("gemm_XXt_symmetric", lambda: ops.gemm_nt(Wd, Wd, symmetric=True), 2 * D * D * M),
+                ("gemm_AA_symmetric", lambda: ops.gemm_nt(A, A, alpha=2.0, beta=-4.0, Cin=A, symmetric=True), 2 * D * D * D),
+                ("gemm_TB", lambda: ops.gemm_nt(W, A, beta=3.0, Cin=W), 2 * D * D * M),
+                ("gemm_TB_out_t", lambda: ops.gemm_nt(W, A, beta=3.0, Cin=W, out_t=Wd), 2 * D * D * M),
+            ):
+                ms = timed(fn)
+                results.append(dict(kernel=name, ms=ms, tflops_equiv=fl / ms / 1e9, frac=fl / ms / 1e9 / peaks["tflops"]))
+        for r in results:
+            r.update(D=D, M=M)
+            print(json.dumps(r), flush=True)
+        return
     vals, idx = ops.encode_topk_tc(x, W, b, k)
     if which in ("encode", "all"):
         ms = timed(lambda: ops.encode_topk_tc(x, W, b, k))

@@ -254,11 +254,18 @@ int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int k,
  * sparsify/muon.py:32-36 (A = X X^T, B = bA + cAA, X = aX + BX),
  * sparsify/sparse_coder.py:221-222 (skip connection) and
  * sparsify/fused_encoder.py:29 when the dense pre-activations are wanted.
+ * symmetric != 0 (needs A == B, M == N, no bias): the result is symmetric, so
+ * tiles wholly below the diagonal are not computed and are filled from their
+ * mirror images (X X^T and bA + cAA of Newton-Schulz: about half the work).
+ * out_t, when not NULL, receives the transposed result [N,M] as well (same
+ * dtype as out), so that an iteration can keep a matrix in both orientations
+ * without a transpose pass.
  * status_word as in sc_encode_topk (may be NULL). */
 int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M, int64_t N,
                     int64_t K, float alpha, float beta, const void* Cin,
                     int cin_dtype, const float* bias, int relu, void* out,
-                    int out_dtype, int32_t* status_word, void* stream);
+                    int out_dtype, int symmetric, void* out_t,
+                    int32_t* status_word, void* stream);
 
 /* out[c,r] = in[r,c] for a bf16 matrix (puts the right operand of X = aX + BX
  * into K-major form, sparsify/muon.py:36). */

@@ -66,7 +66,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_cast_bf16": (c_int, [P, P, I64, P]),
     "sc_project_rows": (c_int, [P, P, I64, I64, P]),
     "sc_signum_schedulefree": (c_int, [P, P, P, I64, c_float, c_float, c_float, P, P]),
-    "sc_gemm_bf16_nt": (c_int, [P, P, I64, I64, I64, c_float, c_float, P, c_int, P, c_int, P, c_int, P, P]),
+    "sc_gemm_bf16_nt": (c_int, [P, P, I64, I64, I64, c_float, c_float, P, c_int, P, c_int, P, c_int, c_int, P, P, P]),
     "sc_transpose_bf16": (c_int, [P, I64, I64, P, P]),
     "sc_csr_segment_sum": (c_int, [P, P, P, I64, P, P]),
     "sc_rows_adam": (

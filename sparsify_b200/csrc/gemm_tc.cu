@@ -32,9 +32,30 @@ struct Params {
   float alpha, beta;
   int out_bf16, cin_bf16, relu;
   int tiles_m, tiles_n;
+  int n_tiles;
+  int cin_aligned;  // Cin is 16-byte aligned
+  int symmetric;  // A and B are the same matrix: tiles wholly below the diagonal are not computed
+  void* out_t;    // optional second copy of the result, transposed ([N, M])
 };
 
+// Column tile j (256 wide) of a symmetric product needs the row tiles (128 high) that
+// reach the diagonal or lie above it: 128 i <= 256 j + 255, i.e. i <= 2 j + 1.
+__host__ __device__ __forceinline__ int sym_rows_in_col(int tiles_m, int j) {
+  return tiles_m < 2 * j + 2 ? tiles_m : 2 * j + 2;
+}
+
 __device__ __forceinline__ void tile_coords(const Params& p, int t, int& tm, int& tn) {
+  if (p.symmetric) {
+    int j = 0, acc = 0;
+    for (;; ++j) {
+      const int cnt = sym_rows_in_col(p.tiles_m, j);
+      if (t < acc + cnt) break;
+      acc += cnt;
+    }
+    tn = j;
+    tm = t - acc;
+    return;
+  }
   const int per_group = kGroupM * p.tiles_n;
   const int g = t / per_group, rem = t % per_group;
   const int gm = min(kGroupM, p.tiles_m - g * kGroupM);
@@ -54,10 +75,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint64_t* tfull = bars + 2 * kStages;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  float* tscratch = reinterpret_cast<float*>(smem + (size_t)kStages * kStageBytes + 256);  // 4 x [32][33]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kc_count = (int)((p.K + BK - 1) / BK);
-  const int n_tiles = p.tiles_m * p.tiles_n;
+  const int n_tiles = p.n_tiles;
 
   if (threadIdx.x == 0) {
     prefetch_tensor_map(&tmap_a);
@@ -151,14 +173,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.cin != nullptr && p.beta != 0.f) {
           if (p.cin_bf16) {
             const __nv_bfloat16* cr = static_cast<const __nv_bfloat16*>(p.cin) + gm * p.N + gc;
+            if (valid == 32 && (p.N % 8 == 0) && p.cin_aligned) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] = fmaf(p.beta, __bfloat162float(cr[i]), v[i]);
+              for (int i = 0; i < 32; i += 8) {
+                const uint4 pk = *reinterpret_cast<const uint4*>(cr + i);
+                const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  v[i + 2 * h] = fmaf(p.beta, __uint_as_float(w[h] << 16), v[i + 2 * h]);
+                  v[i + 2 * h + 1] = fmaf(p.beta, __uint_as_float(w[h] & 0xffff0000u), v[i + 2 * h + 1]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid) v[i] = fmaf(p.beta, __bfloat162float(cr[i]), v[i]);
+            }
           } else {
             const float* cr = static_cast<const float*>(p.cin) + gm * p.N + gc;
+            if (valid == 32 && (p.N % 4 == 0) && p.cin_aligned) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] = fmaf(p.beta, cr[i], v[i]);
+              for (int i = 0; i < 32; i += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(cr + i);
+                v[i] = fmaf(p.beta, c4.x, v[i]); v[i + 1] = fmaf(p.beta, c4.y, v[i + 1]);
+                v[i + 2] = fmaf(p.beta, c4.z, v[i + 2]); v[i + 3] = fmaf(p.beta, c4.w, v[i + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid) v[i] = fmaf(p.beta, cr[i], v[i]);
+            }
           }
         }
         if (p.bias != nullptr) {
@@ -197,6 +241,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (i < valid) orow[i] = v[i];
           }
         }
+        // Transposed copies: element (gm, gc+i) also goes to row gc+i, column gm - of `out`
+        // itself when the mirrored tile of a symmetric product is one that is not computed,
+        // of `out_t` when a transposed result was asked for. For a fixed i the 32 lanes of a
+        // warp write 32 consecutive elements.
+        void* tdst = p.out_t;
+        int64_t ldt = p.M;
+        if (p.symmetric && (((gm >> 8) << 8) + 255 < ((gc >> 7) << 7))) { tdst = p.out; ldt = p.N; }
+        if (tdst != nullptr) {
+          const int64_t gm0 = (int64_t)tm * BM + q * 32;  // first row of this warp
+          if (p.out_bf16 && valid == 32 && gm0 + 32 <= p.M && ldt % 8 == 0) {
+            // 32x32 block transposed through this warp's scratch: lane L then owns column
+            // gc + L and stores its 32 rows as 64 contiguous bytes
+            float* sw = tscratch + (warp - 2) * (32 * 33);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sw[i * 33 + lane] = v[i];
+            __syncwarp();
+            __nv_bfloat16* tp = static_cast<__nv_bfloat16*>(tdst) + (gc + lane) * ldt + gm0;
+            const float* sr = sw + lane * 33;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pk;
+              pk.x = sc::pack_bf16x2(sr[i], sr[i + 1]); pk.y = sc::pack_bf16x2(sr[i + 2], sr[i + 3]);
+              pk.z = sc::pack_bf16x2(sr[i + 4], sr[i + 5]); pk.w = sc::pack_bf16x2(sr[i + 6], sr[i + 7]);
+              *reinterpret_cast<uint4*>(tp + i) = pk;
+            }
+            __syncwarp();
+          } else if (p.out_bf16) {
+            __nv_bfloat16* tp = static_cast<__nv_bfloat16*>(tdst) + gc * ldt + gm;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) tp[i * ldt] = __float2bfloat16_rn(v[i]);
+          } else {
+            float* tp = static_cast<float*>(tdst) + gc * ldt + gm;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) tp[i * ldt] = v[i];
+          }
+        }
       }
       fence_before_sync();
       __syncwarp();
@@ -229,8 +311,12 @@ transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, int64_t R, int64_t C
 
 extern "C" int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M, int64_t N, int64_t K,
                                float alpha, float beta, const void* Cin, int cin_dtype, const float* bias,
-                               int relu, void* out, int out_dtype, int32_t* status_word, void* stream) {
+                               int relu, void* out, int out_dtype, int symmetric, void* out_t,
+                               int32_t* status_word, void* stream) {
   SC_REQUIRE(M > 0 && N > 0 && K > 0, "sc_gemm_bf16_nt: bad shape");
+  SC_REQUIRE(!symmetric || (A_bf16 == B_bf16 && M == N && out_t == nullptr && bias == nullptr),
+             "sc_gemm_bf16_nt: symmetric needs A == B, M == N, no bias and no out_t");
+  SC_REQUIRE(out_t == nullptr || (sc::aligned(out_t, 16) && out_t != out), "sc_gemm_bf16_nt: bad out_t");
   SC_REQUIRE(A_bf16 && B_bf16 && out, "sc_gemm_bf16_nt: null pointer");
   SC_REQUIRE(sc::valid_dtype(out_dtype) && (Cin == nullptr || sc::valid_dtype(cin_dtype)), "sc_gemm_bf16_nt: bad dtype");
   SC_REQUIRE(K % 8 == 0, "sc_gemm_bf16_nt: K=%lld must be a multiple of 8 (16-byte row stride for TMA)", (long long)K);
@@ -248,11 +334,20 @@ extern "C" int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M
   p.out_bf16 = out_dtype == SC_BF16; p.cin_bf16 = cin_dtype == SC_BF16; p.relu = relu;
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = (int)((N + BN - 1) / BN);
-  const size_t smem = (size_t)kStages * kStageBytes + 256 + 1024;
+  p.cin_aligned = sc::aligned(Cin, 16) ? 1 : 0;
+  p.symmetric = symmetric ? 1 : 0;
+  p.out_t = out_t;
+  int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  if (symmetric) {
+    tiles = 0;
+    for (int j = 0; j < p.tiles_n; ++j) tiles += sym_rows_in_col(p.tiles_m, j);
+  }
+  SC_REQUIRE(tiles < (int64_t(1) << 31), "sc_gemm_bf16_nt: too many tiles");
+  p.n_tiles = (int)tiles;
+  const size_t smem = (size_t)kStages * kStageBytes + 256 + 4 * 32 * 33 * sizeof(float) + 1024;
   SC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < sms ? tiles : sms);
   gemm_tc_kernel<<<grid, kThreads, smem, sc::as_stream(stream)>>>(tma, tmb, p);
   SC_CHECK_LAUNCH("sc_gemm_bf16_nt");

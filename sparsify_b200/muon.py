@@ -41,25 +41,30 @@ def quintic_newtonschulz(G: Tensor, steps: int) -> Tensor:
 
 
 def _newtonschulz_tc(G: Tensor, steps: int) -> Tensor:
-    """The same iteration with every product on the tcgen05 GEMM kernel. All
-    three products are written as P Q^T with both operands K-major:
-    A = X X^T, B = bA + c A A^T (A is symmetric), X = aX + B (X^T)^T, the last
-    one after an explicit transpose of X."""
+    """The same iteration with every product on the tcgen05 GEMM kernel, every
+    product written as P Q^T with both operands K-major. The iterate is kept in
+    both orientations, wide W = X [r, n] (r <= n) and tall T = X^T [n, r]:
+
+        A  = W W^T                      symmetric: upper tiles computed, rest mirrored
+        B  = b A + c A A^T              symmetric (A is)
+        T' = a T + T B^T (= T B)        written as T' and, transposed, as W'
+
+    so no transpose pass runs inside the loop, and the result is available in
+    the orientation of G without one."""
     from . import ops
     a, b, c = NS_COEFFS
     X = G.bfloat16()
-    transposed = G.size(-2) > G.size(-1)
-    if transposed:
-        X = ops.transpose_bf16(X)
     X = (X / (X.norm() + 1e-7)).contiguous()
+    tall_input = G.size(-2) > G.size(-1)
+    T = X if tall_input else ops.transpose_bf16(X)
+    W = ops.transpose_bf16(X) if tall_input else X
     for _ in range(steps):
-        A = ops.gemm_nt(X, X)
-        B = ops.gemm_nt(A, A, alpha=c, beta=b, Cin=A)
-        XT = ops.transpose_bf16(X)
-        X = ops.gemm_nt(B, XT, alpha=1.0, beta=a, Cin=X)
-    if transposed:
-        X = ops.transpose_bf16(X)
-    return X
+        A = ops.gemm_nt(W, W, symmetric=True)
+        B = ops.gemm_nt(A, A, alpha=c, beta=b, Cin=A, symmetric=True)
+        W_next = torch.empty_like(W)
+        T = ops.gemm_nt(T, B, alpha=1.0, beta=a, Cin=T, out_t=W_next)
+        W = W_next
+    return T if tall_input else W
 
 
 class Muon(torch.optim.Optimizer):

@@ -382,11 +382,17 @@ def cast_bf16(src: Tensor, dst: Tensor | None = None) -> Tensor:
 
 def gemm_nt(A: Tensor, B: Tensor, *, alpha: float = 1.0, beta: float = 0.0, Cin: Tensor | None = None,
             bias: Tensor | None = None, relu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
-            out: Tensor | None = None) -> Tensor:
-    """act(alpha * A @ B.T + beta * Cin + bias) on the tensor cores; A [M,K], B [N,K] bf16."""
-    _check_cuda(A, B, Cin, bias, out)
+            out: Tensor | None = None, symmetric: bool = False, out_t: Tensor | None = None) -> Tensor:
+    """act(alpha * A @ B.T + beta * Cin + bias) on the tensor cores; A [M,K], B [N,K] bf16.
+    symmetric: B is A and the result is symmetric (only the tiles reaching the upper
+    triangle are computed, the rest mirrored). out_t: also receives the result transposed."""
+    _check_cuda(A, B, Cin, bias, out, out_t)
     assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.shape[1] == B.shape[1]
-    A, B = A.contiguous(), B.contiguous()
+    if symmetric:
+        assert B is A or (B.data_ptr() == A.data_ptr() and B.shape == A.shape)
+        A = B = A.contiguous()
+    else:
+        A, B = A.contiguous(), B.contiguous()
     M, K = A.shape
     N = B.shape[0]
     if out is None:
@@ -395,12 +401,14 @@ def gemm_nt(A: Tensor, B: Tensor, *, alpha: float = 1.0, beta: float = 0.0, Cin:
     if Cin is not None:
         Cin = Cin.contiguous()
         assert Cin.shape == (M, N)
+    if out_t is not None:
+        assert out_t.shape == (N, M) and out_t.is_contiguous() and out_t.dtype == out.dtype
     bias32 = _f32(bias)
     status = torch.zeros(8, dtype=torch.int32, device=A.device)
     with torch.cuda.device(A.device):
         call("sc_gemm_bf16_nt", ptr(A), ptr(B), M, N, K, float(alpha), float(beta), ptr(Cin),
              dtype_code(Cin) if Cin is not None else 0, ptr(bias32), int(bool(relu)), ptr(out),
-             dtype_code(out), ptr(status), _stream(A))
+             dtype_code(out), int(bool(symmetric)), ptr(out_t), ptr(status), _stream(A))
     gemm_nt.last_status = status
     return out
 

@@ -253,6 +253,41 @@ def test_gemm_tc(cuda_lib, M, N, K):
     assert torch.equal(t.cpu(), A.bfloat16().T.contiguous())
 
 
+@pytest.mark.parametrize("M,K", [(640, 512), (1000, 264), (128, 64), (2048 + 128, 128)])
+def test_gemm_symmetric(cuda_lib, M, K):
+    """X X^T and bA + cAA with only the tiles that reach the upper triangle computed:
+    same values as the full product, and exactly symmetric."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(M + K)
+    X = torch.randn(M, K, generator=g).cuda().bfloat16()
+    full = ops.gemm_nt(X, X, out_dtype=torch.float32)
+    sym = ops.gemm_nt(X, X, out_dtype=torch.float32, symmetric=True)
+    torch.cuda.synchronize()
+    assert int(ops.gemm_nt.last_status[0]) == 0
+    assert torch.equal(sym, sym.T)
+    assert torch.equal(sym.triu(), full.triu())
+    assert rel_l2(sym, X.double() @ X.double().T) < 1e-5
+    if M % 8 == 0:
+        A = sym.bfloat16()
+        B = ops.gemm_nt(A, A, alpha=0.25, beta=-1.0, Cin=A, symmetric=True)
+        want = 0.25 * (A.double() @ A.double().T) - A.double()
+        assert torch.equal(B, B.T) and rel_l2(B.float(), want) < 4e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 520, 128), (1024, 256, 64)])
+def test_gemm_transposed_copy(cuda_lib, M, N, K):
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(M)
+    A = torch.randn(M, K, generator=g).cuda().bfloat16()
+    B = torch.randn(N, K, generator=g).cuda().bfloat16()
+    C = torch.randn(M, N, generator=g).cuda().bfloat16()
+    for dt in (torch.bfloat16, torch.float32):
+        out_t = torch.empty(N, M, dtype=dt, device="cuda")
+        out = ops.gemm_nt(A, B, alpha=1.0, beta=0.5, Cin=C, out_dtype=dt, out_t=out_t)
+        assert torch.equal(out_t, out.T)
+        assert rel_l2(out.float(), A.double() @ B.double().T + 0.5 * C.double()) < (4e-3 if dt == torch.bfloat16 else 1e-5)
+
+
 def test_newtonschulz_tc_vs_oracle(cuda_lib):
     from sparsify_b200.muon import quintic_newtonschulz
     for name in ("wide", "tall"):
