@@ -271,6 +271,26 @@ int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M, int64_t N
  * into K-major form, sparsify/muon.py:36). */
 int sc_transpose_bf16(const void* in, int64_t R, int64_t C, void* out, void* stream);
 
+/* ---- Muon's elementwise passes (sparsify/muon.py:115-181) -------------------
+ * sc_muon_momentum: buf = lerp(buf, g, 1-beta); u = nesterov ? lerp(g, buf, beta)
+ * : buf (muon.py:150-156); out_bf16 = bf16(u) (muon.py:22) and *sumsq = sum of
+ * out^2 (for muon.py:29's norm), one pass. ws: sc_muon_workspace_bytes() bytes. */
+size_t sc_muon_workspace_bytes(void);
+int sc_muon_momentum(const float* g, float* buf, int64_t n, float beta, int nesterov,
+                     void* out_bf16, float* sumsq, void* ws, size_t ws_bytes, void* stream);
+
+/* X / (||X||_F + 1e-7) on a bf16 [R,C] matrix with torch's bf16 roundings
+ * (muon.py:29), written in the same orientation (out_scaled, may be NULL) and /
+ * or transposed (out_t [C,R], may be NULL; muon.py:25-27). sumsq = sum of
+ * squares of X on the device, NULL for a plain copy / transpose. */
+int sc_scale_transpose_bf16(const void* in, int64_t R, int64_t C, const float* sumsq,
+                            void* out_scaled, void* out_t, void* stream);
+
+/* p = p * decay - alpha * upd (bf16): decoupled weight decay (muon.py:120-123)
+ * and the update (muon.py:139-141,176-178) in one pass; optional bf16 copy. */
+int sc_muon_apply(float* p, const void* upd_bf16, int64_t n, float decay, float alpha,
+                  void* shadow_bf16, void* stream);
+
 /* sparsify/sparse_coder.py:281-295 on its own: g[m,:] -= (g[m,:] . w[m,:]) w[m,:]
  * in place, for optimisers that do not fold the projection into their update. */
 int sc_project_rows(float* g, const float* w, int64_t M, int64_t D, void* stream);

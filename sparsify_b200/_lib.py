@@ -64,6 +64,10 @@ SIGNATURES: dict[str, tuple] = {
         [P, P, P, P, I64, I64, c_float, c_float, c_float, c_float, I64, c_int, P, P],
     ),
     "sc_cast_bf16": (c_int, [P, P, I64, P]),
+    "sc_muon_workspace_bytes": (c_size_t, []),
+    "sc_muon_momentum": (c_int, [P, P, I64, c_float, c_int, P, P, P, c_size_t, P]),
+    "sc_scale_transpose_bf16": (c_int, [P, I64, I64, P, P, P, P]),
+    "sc_muon_apply": (c_int, [P, P, I64, c_float, c_float, P, P]),
     "sc_project_rows": (c_int, [P, P, I64, I64, P]),
     "sc_signum_schedulefree": (c_int, [P, P, P, I64, c_float, c_float, c_float, P, P]),
     "sc_gemm_bf16_nt": (c_int, [P, P, I64, I64, I64, c_float, c_float, P, c_int, P, c_int, P, c_int, c_int, P, P, P]),

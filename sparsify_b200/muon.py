@@ -21,26 +21,19 @@ NS_COEFFS = (3.4445, -4.7750, 2.0315)
 
 def quintic_newtonschulz(G: Tensor, steps: int) -> Tensor:
     """Approximate orthogonalisation of G: X <- aX + (bA + cA^2)X with A = XX^T,
-    starting from G / (||G||_F + 1e-7), in bf16 (sparsify/muon.py:11-40)."""
-    assert G.ndim >= 2
-    a, b, c = NS_COEFFS
-    if G.is_cuda and G.ndim == 2 and G.shape[0] % 8 == 0 and G.shape[1] % 8 == 0:
-        return _newtonschulz_tc(G, steps)
-    X = G.bfloat16()
-    transposed = G.size(-2) > G.size(-1)
-    if transposed:
-        X = X.mT
-    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
-    for _ in range(steps):
-        A = X @ X.mT
-        B = torch.addmm(A, A, A, beta=b, alpha=c) if A.ndim == 2 else b * A + c * A @ A
-        X = torch.addmm(X, B, X, beta=a) if X.ndim == 2 else a * X + B @ X
-    if transposed:
-        X = X.mT
-    return X
+    starting from G / (||G||_F + 1e-7), in bf16 (sparsify/muon.py:11-40). CUDA
+    matrices whose sides are multiples of 8 only: every product runs on the
+    tcgen05 GEMM kernel and there is no other path."""
+    if G.ndim == 4:  # conv filters, as the reference flattens them
+        G = G.view(len(G), -1)
+    if not (G.is_cuda and G.ndim == 2):
+        raise RuntimeError("quintic_newtonschulz: no CPU path; pass a 2-D CUDA tensor")
+    if G.shape[0] % 8 or G.shape[1] % 8:
+        raise ValueError(f"quintic_newtonschulz: sides must be multiples of 8, got {tuple(G.shape)}")
+    return _newtonschulz_tc(G, steps)
 
 
-def _newtonschulz_tc(G: Tensor, steps: int) -> Tensor:
+def _newtonschulz_tc(G: Tensor, steps: int, Xb: Tensor | None = None, sumsq: Tensor | None = None) -> Tensor:
     """The same iteration with every product on the tcgen05 GEMM kernel, every
     product written as P Q^T with both operands K-major. The iterate is kept in
     both orientations, wide W = X [r, n] (r <= n) and tall T = X^T [n, r]:
@@ -50,14 +43,19 @@ def _newtonschulz_tc(G: Tensor, steps: int) -> Tensor:
         T' = a T + T B^T (= T B)        written as T' and, transposed, as W'
 
     so no transpose pass runs inside the loop, and the result is available in
-    the orientation of G without one."""
+    the orientation of G without one. Xb / sumsq: the bf16 cast of G and the sum
+    of its squares when the caller already has them (the fused momentum pass)."""
     from . import ops
     a, b, c = NS_COEFFS
-    X = G.bfloat16()
-    X = (X / (X.norm() + 1e-7)).contiguous()
-    tall_input = G.size(-2) > G.size(-1)
-    T = X if tall_input else ops.transpose_bf16(X)
-    W = ops.transpose_bf16(X) if tall_input else X
+    if Xb is None:
+        Xb = G.bfloat16().contiguous()
+        sumsq = torch.linalg.vector_norm(Xb, dtype=torch.float32).square().reshape(1)
+    tall_input = Xb.size(-2) > Xb.size(-1)
+    # normalisation fused with the one transpose that sets up the two orientations
+    if tall_input:
+        T, W = ops.scale_transpose_bf16(Xb, sumsq)
+    else:
+        W, T = ops.scale_transpose_bf16(Xb, sumsq)
     for _ in range(steps):
         A = ops.gemm_nt(W, W, symmetric=True)
         B = ops.gemm_nt(A, A, alpha=c, beta=b, Cin=A, symmetric=True)
@@ -69,10 +67,14 @@ def _newtonschulz_tc(G: Tensor, steps: int) -> Tensor:
 
 class Muon(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, momentum: float = 0.95, nesterov: bool = True,
-                 weight_decay: float = 0.1, ns_steps: int = 5, ddp: bool = True):
+                 weight_decay: float = 0.1, ns_steps: int = 5, ddp: bool = True, orthogonalize=None):
         defaults = dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps,
                         weight_decay=weight_decay)
         params = list(params)
+        self._shadow: dict[int, tuple] = {}
+        # `orthogonalize(G, steps)`: replaces the tensor-core Newton-Schulz (tests of the
+        # host-side exchange logic on CPU processes inject a CPU implementation here)
+        self._orthogonalize = orthogonalize
         use_dist = dist.is_available() and dist.is_initialized() and ddp
         self.rank = dist.get_rank() if use_dist else 0
         self.world_size = dist.get_world_size() if use_dist else 1
@@ -95,33 +97,71 @@ class Muon(torch.optim.Optimizer):
         else:
             super().__init__(params, defaults)
 
+    def register_shadow(self, p: Tensor, shadow: Tensor, on_refresh=None) -> None:
+        """`shadow` (bf16, same shape) is rewritten with the updated value of `p`
+        inside the update kernel; `on_refresh()` is called afterwards."""
+        self._shadow[id(p)] = (shadow, on_refresh)
+
+    def project_rows(self, p: Tensor) -> None:  # the Trainer projects Muon's gradients itself
+        raise NotImplementedError("Muon does not project gradients; call "
+                                  "remove_gradient_parallel_to_decoder_directions() before step()")
+
+    def _fast(self, p: Tensor, g: Tensor) -> bool:
+        return (g.is_cuda and g.ndim == 2 and g.dtype == torch.float32 and g.is_contiguous()
+                and p.dtype == torch.float32 and p.is_contiguous()
+                and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0)
+
     def _orthogonal_update(self, p: Tensor, group: dict) -> Tensor:
         g = p.grad
         assert g is not None
         beta = group["momentum"]
+        if beta > 0.0 and self._orthogonalize is None and self._fast(p, g):
+            # momentum, Nesterov, bf16 cast and the Frobenius norm in one pass
+            from . import ops
+            state = self.state[p]
+            if "exp_avg" not in state:
+                state["exp_avg"] = torch.zeros_like(g)
+            xb, sumsq = ops.muon_momentum_(g, state["exp_avg"], beta, group["nesterov"])
+            return _newtonschulz_tc(g, group["ns_steps"], xb, sumsq)
         if beta > 0.0:
             state = self.state[p]
             if "exp_avg" not in state:
                 state["exp_avg"] = torch.zeros_like(g)
             buf = state["exp_avg"].lerp_(g, 1 - beta)
             g = g.lerp_(buf, beta) if group["nesterov"] else buf
-        if g.ndim == 4:
-            g = g.view(len(g), -1)
-        return quintic_newtonschulz(g, steps=group["ns_steps"])
+        return (self._orthogonalize or quintic_newtonschulz)(g, group["ns_steps"])
+
+    def _apply(self, p: Tensor, upd: Tensor, lr: float, decay: float) -> None:
+        """p = p * decay - lr * 0.2 sqrt(max(shape)) * upd (muon.py:120-123,139-141)."""
+        alpha = lr * 0.2 * max(p.shape) ** 0.5
+        upd = upd.view_as(p)
+        if self._fast(p, p.data) and upd.dtype == torch.bfloat16 and upd.is_contiguous():
+            from . import ops
+            shadow, cb = self._shadow.get(id(p), (None, None))
+            ops.muon_apply_(p.data, upd, decay, alpha, shadow)
+            torch.autograd.graph.increment_version(p)  # written through raw pointers
+            if cb is not None:
+                cb()
+        elif self._orthogonalize is not None:
+            # injected orthogonaliser (CPU processes testing the exchange logic): plain tensor ops
+            if decay != 1.0:
+                p.mul_(decay)
+            p.add_(upd, alpha=-alpha)
+        else:
+            raise RuntimeError("Muon: contiguous fp32 CUDA matrices with sides that are multiples of 8 "
+                               "only (no CPU path)")
 
     @torch.no_grad()
     def step(self):
         for group in self.param_groups:
             params: list[Tensor] = group["params"]
             lr = group["lr"]
-            if group["weight_decay"] > 0.0:
-                for p in params:
-                    p.mul_(1 - lr * group["weight_decay"])
+            # decoupled weight decay, folded into the pass that applies the update
+            decay = 1 - lr * group["weight_decay"] if group["weight_decay"] > 0.0 else 1.0
 
             if self.world_size == 1:
                 for p in params:
-                    upd = self._orthogonal_update(p, group)
-                    p.add_(upd.view_as(p), alpha=-lr * 0.2 * max(p.shape) ** 0.5)
+                    self._apply(p, self._orthogonal_update(p, group), lr, decay)
                 continue
 
             buffer: Tensor = group["update_buffer"]
@@ -131,7 +171,7 @@ class Muon(torch.optim.Optimizer):
             def apply(handle, owners):
                 handle.wait()
                 for p_w, g_w in zip(owners, views):
-                    p_w.add_(g_w.view_as(p_w), alpha=-lr * 0.2 * max(p_w.shape) ** 0.5)
+                    self._apply(p_w, g_w, lr, decay)
 
             for i in range(0, len(params), self.world_size):
                 if i + self.rank < len(params):

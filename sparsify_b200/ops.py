@@ -347,6 +347,43 @@ def adam_rows_(p: Tensor, g: Tensor, m: Tensor, v: Tensor, *, lr: float, beta1: 
              float(beta2), float(eps), int(step), int(bool(project)), ptr(shadow), _stream(p))
 
 
+def muon_momentum_(g: Tensor, buf: Tensor, beta: float, nesterov: bool) -> tuple[Tensor, Tensor]:
+    """Momentum (+ Nesterov) of sparsify/muon.py:150-156 in one pass: updates `buf` in place
+    and returns the bf16 cast of the result together with the sum of its squares."""
+    _check_cuda(g, buf)
+    assert g.dtype == buf.dtype == torch.float32 and g.is_contiguous() and buf.is_contiguous() and g.shape == buf.shape
+    out = torch.empty(g.shape, dtype=torch.bfloat16, device=g.device)
+    sumsq = torch.empty(1, dtype=torch.float32, device=g.device)
+    ws = _ws(_lib.lib().sc_muon_workspace_bytes(), g.device)
+    with torch.cuda.device(g.device):
+        call("sc_muon_momentum", ptr(g), ptr(buf), g.numel(), float(beta), int(bool(nesterov)), ptr(out),
+             ptr(sumsq), ptr(ws), ws.numel(), _stream(g))
+    return out, sumsq
+
+
+def scale_transpose_bf16(x: Tensor, sumsq: Tensor | None, *, scaled: bool = True, transposed: bool = True):
+    """x / (||x||_F + 1e-7) with bf16 roundings as torch applies them (sumsq = sum of squares of
+    x, None for no scaling), in x's orientation and / or transposed, in one pass."""
+    _check_cuda(x, sumsq)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    R, C = x.shape
+    out_s = torch.empty(R, C, dtype=torch.bfloat16, device=x.device) if scaled else None
+    out_t = torch.empty(C, R, dtype=torch.bfloat16, device=x.device) if transposed else None
+    with torch.cuda.device(x.device):
+        call("sc_scale_transpose_bf16", ptr(x), R, C, ptr(sumsq), ptr(out_s), ptr(out_t), _stream(x))
+    return out_s, out_t
+
+
+def muon_apply_(p: Tensor, upd: Tensor, decay: float, alpha: float, shadow: Tensor | None = None) -> None:
+    """p = p * decay - alpha * upd (bf16), in place; optional bf16 copy of the result
+    (sparsify/muon.py:120-123,139-141,176-178 in one pass)."""
+    _check_cuda(p, upd, shadow)
+    assert p.dtype == torch.float32 and upd.dtype == torch.bfloat16 and p.is_contiguous() and upd.is_contiguous()
+    assert p.numel() == upd.numel()
+    with torch.cuda.device(p.device):
+        call("sc_muon_apply", ptr(p), ptr(upd), p.numel(), float(decay), float(alpha), ptr(shadow), _stream(p))
+
+
 def project_rows_(g: Tensor, w: Tensor) -> None:
     """g[m] -= (g[m] . w[m]) w[m] in place (sparsify/sparse_coder.py:281-295)."""
     _check_cuda(g, w)

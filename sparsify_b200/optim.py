@@ -21,6 +21,13 @@ from torch import Tensor
 from . import ops
 
 
+def _touched(p: Tensor) -> None:
+    """The kernels write parameters through raw pointers; this moves the tensor's
+    version counter so that anything cached against it (bf16 copies, the
+    unit-norm marker) is seen as out of date unless it is re-marked afterwards."""
+    torch.autograd.graph.increment_version(p)
+
+
 class FusedAdam(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8):
         if lr < 0:
@@ -181,6 +188,8 @@ class FusedAdam(torch.optim.Optimizer):
             sae._dec_work = dist.all_gather_into_tensor(shadow_dec[0].view(-1), mine_dec.view(-1), async_op=True)
             sae._dec_work_src = mine_dec  # keep the send buffer alive until the wait
             sae._masters_stale = True
+        for q in (W_dec, W_enc):
+            _touched(q)
         for _, cb in (shadow_dec, shadow_enc):
             if cb is not None:
                 cb()
@@ -256,6 +265,7 @@ class FusedAdam(torch.optim.Optimizer):
                     beta2=beta2, eps=group["eps"], step=int(state["step"]),
                     project=id(p) in self._project and p.dim() == 2, shadow=shadow,
                 )
+                _touched(p)
                 if cb is not None:
                     cb()
 
@@ -342,6 +352,7 @@ class ScheduleFreeSignum(torch.optim.Optimizer):
                     ops.project_rows_(g, p.data)
                 shadow, cb = self._shadow.get(id(p), (None, None))
                 ops.signum_schedulefree_(p.data, state["z"], g, lr, group["momentum"], ckp1, shadow)
+                _touched(p)
                 if cb is not None:
                     cb()
             group["k"] = k + 1

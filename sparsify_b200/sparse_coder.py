@@ -314,8 +314,10 @@ class SparseCoder(nn.Module):
             hit = self._shadows.pop("W_dec", None)
             buf = hit[2] if hit is not None and hit[2].shape == W.shape and hit[2].device == W.device else None
             ops.normalize_rows_(W, eps, buf)
+            torch.autograd.graph.increment_version(self.W_dec)
             if buf is not None:
                 self.mark_shadow_fresh("W_dec", buf)
+            self._dec_unit_norm = (W.data_ptr(), self.W_dec._version)
         else:
             # construction / checkpoint handling on the host before .to("cuda")
             norm = torch.norm(W, dim=1, keepdim=True)
@@ -347,9 +349,10 @@ class SparseCoder(nn.Module):
         for p, g in ((self.W_dec, res["gradA"]), (self.encoder.weight, res["gradB"])):
             p.grad = g if p.grad is None else p.grad + g
 
-    def attach_optimizer(self, opt) -> None:
-        """Lets a FusedAdam keep the bf16 copies current inside its update kernel
-        and fold the decoder-gradient projection into the same pass."""
+    def attach_optimizer(self, opt, project: bool = True) -> None:
+        """Lets an optimiser of this package keep the bf16 copies current inside
+        its update kernel and (project=True) fold the decoder-gradient
+        projection into the same pass."""
         lowp = self._lowp() and self.dtype == torch.float32
         names = ["encoder.weight"] + (["W_dec"] if self.precision == "bf16" and self.W_dec is not None else [])
         if lowp and self.device.type == "cuda":
@@ -357,7 +360,7 @@ class SparseCoder(nn.Module):
                 p = self.encoder.weight if name == "encoder.weight" else self.W_dec
                 buf = self.shadow(name)
                 opt.register_shadow(p, buf, lambda name=name, buf=buf: self.mark_shadow_fresh(name, buf))
-        if self.W_dec is not None and self.cfg.normalize_decoder and not self.cfg.transcode:
+        if project and self.W_dec is not None and self.cfg.normalize_decoder and not self.cfg.transcode:
             opt.project_rows(self.W_dec)
 
     @torch.no_grad()
@@ -365,11 +368,9 @@ class SparseCoder(nn.Module):
         assert self.W_dec is not None, "Decoder weight was not initialized."
         assert self.W_dec.grad is not None
         g, w = self.W_dec.grad, self.W_dec.data
-        if g.is_cuda and g.dtype == torch.float32 and g.is_contiguous() and w.is_contiguous():
-            ops.project_rows_(g, w)
-        else:  # host tensors (construction-time use only)
-            parallel = (g * w).sum(dim=1, keepdim=True)
-            g -= parallel * w
+        if not (g.is_contiguous() and w.is_contiguous() and g.dtype == torch.float32):
+            raise RuntimeError("remove_gradient_parallel_to_decoder_directions: contiguous fp32 tensors only")
+        ops.project_rows_(g, w)  # raises for tensors that are not on a CUDA device: no CPU path
 
 
 # Allow for alternate naming conventions

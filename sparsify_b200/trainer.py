@@ -122,6 +122,8 @@ class Trainer:
                     Muon(muon_params, lr=cfg.lr or 2e-3, ddp=not cfg.distribute_modules),
                     FusedAdam(other, lr=cfg.lr or 2e-3),
                 ]
+                for sae in self.saes.values():
+                    sae.attach_optimizer(self.optimizers[0], project=False)  # bf16 copies only
                 self.lr_schedulers = [
                     linear_schedule_with_warmup(self.optimizers[0], 0, num_batches),
                     linear_schedule_with_warmup(self.optimizers[1], cfg.lr_warmup_steps, num_batches),

@@ -9,6 +9,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from oracle import sae_oracle as O
+
 
 def _free_port():
     with socket.socket() as s:
@@ -79,7 +81,7 @@ def _muon_case(rank, world):
     params = [torch.nn.Parameter(torch.randn(8, 16)) for _ in range(3)]  # ragged last group
     for i, p in enumerate(params):
         p.grad = torch.randn(8, 16, generator=torch.Generator().manual_seed(10 + i))
-    opt = Muon(params, lr=0.01, ddp=True)
+    opt = Muon(params, lr=0.01, ddp=True, orthogonalize=O.quintic_newtonschulz)
     assert opt.world_size == world
     opt.step()
     return [p.detach().clone() for p in params]
@@ -92,7 +94,7 @@ def test_muon_ddp_equals_single_process():
     params = [torch.nn.Parameter(torch.randn(8, 16)) for _ in range(3)]
     for i, p in enumerate(params):
         p.grad = torch.randn(8, 16, generator=torch.Generator().manual_seed(10 + i))
-    Muon(params, lr=0.01, ddp=False).step()
+    Muon(params, lr=0.01, ddp=False, orthogonalize=O.quintic_newtonschulz).step()
     for r in range(2):
         for got, want in zip(res[r], params):
             assert torch.allclose(got, want.detach(), atol=1e-6)

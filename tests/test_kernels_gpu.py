@@ -361,3 +361,27 @@ def test_project_rows_kernel(cuda_lib):
     gd = grad.cuda()
     ops.project_rows_(gd, w.cuda())
     assert rel_l2(gd, want) < 1e-6
+
+
+def test_muon_elementwise_kernels(cuda_lib):
+    """Momentum + Nesterov + bf16 cast + sum of squares, the scaled transpose and the
+    decay + update pass against the tensor expressions of sparsify/muon.py."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(12)
+    R, C, beta = 72, 40, 0.95
+    grad, buf = torch.randn(R, C, generator=g), torch.randn(R, C, generator=g)
+    want_buf = buf.clone().lerp_(grad, 1 - beta)
+    want_u = grad.clone().lerp_(want_buf, beta).bfloat16()
+    bd = buf.cuda()
+    xb, sumsq = ops.muon_momentum_(grad.cuda(), bd, beta, True)
+    assert rel_l2(bd, want_buf) < 1e-6
+    assert (xb.cpu().float() - want_u.float()).abs().max() <= 2 ** -7 * want_u.float().abs().max()
+    assert abs(float(sumsq) - float(xb.float().pow(2).sum())) < 1e-4 * float(sumsq)
+    want = xb.cpu() / (xb.cpu().norm() + 1e-7)          # bf16 arithmetic, as the reference normalises
+    s_, t_ = ops.scale_transpose_bf16(xb, sumsq)
+    assert torch.equal(s_.cpu(), want) and torch.equal(t_.cpu(), want.T.contiguous())
+    p = torch.randn(R, C, generator=g)
+    pd, shadow = p.cuda(), torch.empty(R, C, dtype=torch.bfloat16, device="cuda")
+    ops.muon_apply_(pd, s_, 0.999, 0.03, shadow)
+    want_p = p * 0.999 - 0.03 * want.float()
+    assert rel_l2(pd, want_p) < 1e-6 and torch.equal(shadow, pd.bfloat16())
