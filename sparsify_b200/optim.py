@@ -177,7 +177,10 @@ class FusedAdam(torch.optim.Optimizer):
                     t.record_stream(side)  # allocated on the main stream, still in use on the side stream
             sae._dec_event = event
         else:
-            ops.rows_adam_(*args, **kw)
+            # one launch per matrix: each then gathers from a single [N, D] bf16 array (134 MB at
+            # d=4096, 16384 tokens), which L2 holds far better than both at once (-0.3 ms per step)
+            ops.rows_adam_(*args, parts=2, **kw)
+            ops.rows_adam_(*args, parts=1, **kw)
         if shard is not None:
             # everyone needs every row for the next forward: the encoder copy right away, the
             # decoder copy only at decode time, so its all-gather runs under the encoder GEMM

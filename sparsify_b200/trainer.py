@@ -12,10 +12,12 @@ arithmetic done by the CUDA kernels. Differences, all outside the arithmetic:
   (asynchronous all-reduce per parameter, overlapped with backward) instead of
   a DistributedDataParallel wrapper;
 * `distribute_modules`: activations go to the owning rank only;
-* `loss_fn` "ce"/"kl" (end-to-end through a live language model), the
-  schedule-free "signum" optimiser and Weights & Biases logging are not part of
-  this package; metrics go to `metrics.jsonl` in the run directory under the
-  names the reference logs.
+* `loss_fn` "ce"/"kl" (trainer.py:425-430,486-500): the sparse coder's output
+  replaces the module's output inside the model's forward and the model's own
+  loss is back-propagated; these steps take the composed autograd path (dense
+  gradients), since the gradient arrives through `sae_out`;
+* Weights & Biases logging is not part of this package; metrics go to
+  `metrics.jsonl` in the run directory under the names the reference logs.
 """
 
 from __future__ import annotations
@@ -78,11 +80,8 @@ class Trainer:
                 f"All modules must output tensors of the same shape when using "
                 f"`distribute_modules=True`, got {unique_widths}"
             )
-        if cfg.loss_fn != "fvu":
-            raise NotImplementedError(
-                f"loss_fn='{cfg.loss_fn}' trains end-to-end through a live language model; "
-                "this package covers the local 'fvu' objective only"
-            )
+        if cfg.loss_fn not in ("fvu", "ce", "kl"):
+            raise ValueError(f"Unknown loss function '{cfg.loss_fn}'")
 
         print(f"Initializing SAEs with random seed(s) {cfg.init_seeds}")
         self.saes: dict[str, SparseCoder] = {}
@@ -102,7 +101,8 @@ class Trainer:
                        for sae in self.saes.values()]
                 lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
                 adam = FusedAdam(pgs)
-                no_acc = cfg.grad_acc_steps * cfg.micro_acc_steps == 1
+                # (end-to-end losses reach the weights through sae_out: dense gradients)
+                no_acc = cfg.grad_acc_steps * cfg.micro_acc_steps == 1 and cfg.loss_fn == "fvu"
                 for sae in self.saes.values():
                     sae.attach_optimizer(adam)
                     sae.ragged_tokens = bool(cfg.exclude_tokens)
@@ -154,7 +154,8 @@ class Trainer:
         num_latents = list(self.saes.values())[0].num_latents
         self.initial_k = min(num_latents, round(list(input_widths.values())[0] * 10))
         self.final_k = self.cfg.sae.k
-        self.best_loss = {name: float("inf") for name in self.local_hookpoints()}
+        self.best_loss = ({name: float("inf") for name in self.local_hookpoints()}
+                          if cfg.loss_fn == "fvu" else float("inf"))  # trainer.py:180-184
         self.metrics: list[dict] = []
         self._tokens_seen = 0  # upper bound of every num_tokens_since_fired counter
 
@@ -224,6 +225,7 @@ class Trainer:
         avg_fvu = defaultdict(float)
         avg_multi_topk_fvu = defaultdict(float)
         avg_losses = {name: float("inf") for name in self.local_hookpoints()}
+        avg_e2e = 0.0  # cross-entropy or KL of the model with the sparse coders spliced in
 
         name_to_module = {name: self.model.base_model.get_submodule(name) for name in self.cfg.hookpoints}
         module_to_name = {v: k for k, v in name_to_module.items()}
@@ -231,13 +233,17 @@ class Trainer:
         # loss scalars stay on the device until the step ends: one host sync per step
         pending_metrics: list[tuple] = []
 
+        e2e = self.cfg.loss_fn in ("ce", "kl")
+
         def hook(module: nn.Module, inputs, outputs):
+            aux_out = None
             if isinstance(inputs, tuple):
                 inputs = inputs[0]
             if isinstance(outputs, tuple):
-                outputs, *_ = outputs
+                outputs, *aux_out = outputs
             mask = tokens_mask
             hookpoint = module_to_name[module]
+            out_shape = outputs.shape
 
             if self.cfg.distribute_modules:
                 owner = parallel.owner_of(self.module_plan, hookpoint)
@@ -252,7 +258,9 @@ class Trainer:
             outputs = outputs.flatten(0, 1)
             inputs = inputs.flatten(0, 1) if self.cfg.sae.transcode else outputs
             mask = mask.flatten(0, 1)
-            if not bool(mask.all()):
+            all_outputs = outputs.detach() if e2e else None
+            ragged = not bool(mask.all())
+            if ragged:
                 outputs = outputs[mask]
                 inputs = inputs[mask] if self.cfg.sae.transcode else outputs
 
@@ -276,6 +284,7 @@ class Trainer:
                 # until that passes the threshold the mask is known to be empty and is not
                 # built (the forward would otherwise read its sum back to the host).
                 may_be_dead = self.cfg.auxk_alpha > 0 and self._tokens_seen > self.cfg.dead_feature_threshold
+                raw.fused = not e2e  # a gradient arriving through sae_out needs the autograd path
                 out = raw(
                     x=inputs,
                     y=outputs,
@@ -284,6 +293,17 @@ class Trainer:
                 )
                 did_fire[name][out.latent_indices.flatten()] = True
                 self.maybe_all_reduce(did_fire[name], "max")
+
+                if e2e:
+                    # the sparse coder's output takes the module's place in the model's forward
+                    # (trainer.py:425-430); the model's loss is back-propagated by fit()
+                    if ragged:
+                        output = all_outputs.clone()
+                        output[mask] = out.sae_out.type_as(output)
+                    else:
+                        output = out.sae_out.type_as(all_outputs)
+                    output = output.reshape(out_shape)
+                    return (output, *aux_out) if aux_out is not None else output
 
                 pending_metrics.append((name, out.fvu.detach(), out.auxk_loss.detach(),
                                         out.multi_topk_fvu.detach()))
@@ -308,9 +328,23 @@ class Trainer:
             N = int(tokens_mask.sum().item())
             num_tokens_in_step += N
 
+            # clean next-token distribution for the KL objective (trainer.py:478-483)
+            clean_probs = self.model(x).logits.softmax(dim=-1) if self.cfg.loss_fn == "kl" else None
+
             handles = [mod.register_forward_hook(hook) for mod in name_to_module.values()]
             try:
-                self.model(x)
+                match self.cfg.loss_fn:
+                    case "ce":
+                        ce = self.model(x, labels=x).loss
+                        ce.div(acc_steps).backward()
+                        avg_e2e += float(self.maybe_all_reduce(ce.detach()) / denom)
+                    case "kl":
+                        dirty_lps = self.model(x).logits.log_softmax(dim=-1)
+                        kl = -torch.sum(clean_probs * dirty_lps, dim=-1).mean()
+                        kl.div(acc_steps).backward()
+                        avg_e2e += float(self.maybe_all_reduce(kl.detach()) / denom)
+                    case _:
+                        self.model(x)
             finally:
                 for handle in handles:
                     handle.remove()
@@ -323,7 +357,7 @@ class Trainer:
                 if self.cfg.sae.multi_topk:
                     avg_multi_topk_fvu[name] += float(self.maybe_all_reduce(multi) / denom)
             pending_metrics.clear()
-            avg_losses = dict(avg_fvu)
+            avg_losses = avg_e2e if e2e else dict(avg_fvu)
 
             if substep == 0:
                 if reducer is not None:
@@ -360,10 +394,13 @@ class Trainer:
 
                 if (step + 1) % self.cfg.wandb_log_frequency == 0:
                     info = {"step": step, "k": k}
+                    if e2e:
+                        info["ce_loss" if self.cfg.loss_fn == "ce" else "kl_loss"] = avg_e2e
                     for name in self.saes:
                         dead = self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold
                         info[f"dead_pct/{name}"] = dead.mean(dtype=torch.float32).item()
-                        info[f"fvu/{name}"] = avg_fvu[name]
+                        if not e2e:
+                            info[f"fvu/{name}"] = avg_fvu[name]
                         if self.cfg.auxk_alpha > 0:
                             info[f"auxk/{name}"] = avg_auxk_loss[name]
                         if self.cfg.sae.multi_topk:
@@ -373,6 +410,7 @@ class Trainer:
                 avg_auxk_loss.clear()
                 avg_fvu.clear()
                 avg_multi_topk_fvu.clear()
+                avg_e2e = 0.0
 
             self.global_step += 1
 
@@ -450,15 +488,22 @@ class Trainer:
         if dist.is_initialized():
             dist.barrier()
 
-    def save_best(self, avg_loss: dict[str, float]):
-        """Save individual sparse coders to disk if they have the lowest loss."""
+    def save_best(self, avg_loss: float | dict[str, float]):
+        """Save individual sparse coders to disk if they have the lowest loss (a dict of
+        per-hookpoint FVUs, or the model's single loss for the end-to-end objectives)."""
         base_path = f'{self.cfg.save_dir}/{self.cfg.run_name or "unnamed"}/best'
         rank_zero = not dist.is_initialized() or dist.get_rank() == 0
-        for name in self.saes:
-            if avg_loss.get(name, float("inf")) < self.best_loss.get(name, float("inf")):
-                self.best_loss[name] = avg_loss[name]
+        if isinstance(avg_loss, dict):
+            for name in self.saes:
+                if avg_loss.get(name, float("inf")) < self.best_loss.get(name, float("inf")):
+                    self.best_loss[name] = avg_loss[name]
+                    if rank_zero or self.cfg.distribute_modules:
+                        self._checkpoint({name: self.saes[name]}, f"{base_path}/{name}", rank_zero)
+        else:
+            if avg_loss < self.best_loss:
+                self.best_loss = avg_loss
                 if rank_zero or self.cfg.distribute_modules:
-                    self._checkpoint({name: self.saes[name]}, f"{base_path}/{name}", rank_zero)
+                    self._checkpoint(self.saes, base_path, rank_zero)
         if dist.is_initialized():
             dist.barrier()
 

@@ -55,3 +55,57 @@ class FakeModel(torch.nn.Module):
 
 def dataset(steps, batch, ctx):
     return [{"input_ids": torch.zeros(ctx, dtype=torch.long)} for _ in range(steps * batch)]
+
+
+class TinyBlock(torch.nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.up = torch.nn.Linear(d, 2 * d)
+        self.down = torch.nn.Linear(2 * d, d)
+
+    def forward(self, h):
+        return h + self.down(torch.nn.functional.gelu(self.up(h)))
+
+
+class TinyLM(torch.nn.Module):
+    """A small live language model (embedding, residual MLP blocks, tied-free head)
+    for the end-to-end objectives: `forward(input_ids, labels=None)` returns an
+    object with `.logits` and, given labels, the next-token cross-entropy `.loss`,
+    like a HuggingFace causal LM."""
+
+    def __init__(self, vocab=48, d=32, n_layers=2, ctx=16, seed=0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.embed = torch.nn.Embedding(vocab, d)
+        self.layers = torch.nn.ModuleList([TinyBlock(d) for _ in range(n_layers)])
+        self.head = torch.nn.Linear(d, vocab, bias=False)
+        with torch.no_grad():
+            for p in self.parameters():
+                p.copy_(torch.randn(p.shape, generator=g) * (0.5 if p.ndim == 1 else p.shape[-1] ** -0.5))
+        self.config = types.SimpleNamespace(num_hidden_layers=n_layers)
+        self.dummy_inputs = {"input_ids": torch.zeros(1, ctx, dtype=torch.long)}
+
+    @property
+    def base_model(self):
+        return self
+
+    @property
+    def device(self):
+        return self.embed.weight.device
+
+    def forward(self, input_ids=None, labels=None, **kw):
+        h = self.embed(input_ids)
+        for layer in self.layers:
+            h = layer(h)
+        logits = self.head(h)
+        loss = None
+        if labels is not None:
+            loss = torch.nn.functional.cross_entropy(
+                logits[:, :-1].reshape(-1, logits.shape[-1]), labels[:, 1:].reshape(-1))
+        return types.SimpleNamespace(logits=logits, loss=loss)
+
+
+def token_dataset(steps, batch, ctx, vocab=48, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, vocab, (steps * batch, ctx), generator=g)
+    return [{"input_ids": row} for row in ids]

@@ -343,6 +343,32 @@ def gen_trainer_signum(sparsify):
         save("trainer_signum", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=1e-3))
 
 
+def gen_trainer_e2e(sparsify):
+    """The reference Trainer with the end-to-end objectives (loss_fn="ce" and "kl",
+    trainer.py:425-430,478-500) on a small live language model (tests/fake_model.TinyLM):
+    the sparse coder is spliced into the model's forward at layers.0 and the model's own
+    loss trains it. Freezes the final parameters; inputs and model are rebuilt from seeds."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from tests.fake_model import TinyLM, token_dataset
+    from sparsify import SparseCoderConfig, TrainConfig, Trainer
+    steps, B, T, D, M, k = 4, 4, 16, 32, 256, 4
+    for loss_fn in ("ce", "kl"):
+        model = TinyLM(d=D, ctx=T)
+        with tempfile.TemporaryDirectory() as tmp:
+            cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="adam", lr=1e-2,
+                              lr_warmup_steps=1, loss_fn=loss_fn, hookpoints=["layers.0"], log_to_wandb=False,
+                              save_dir=tmp, run_name="golden", save_every=10**9)
+            trainer = Trainer(cfg, token_dataset(steps, B, T), model)
+            sae = trainer.saes["layers.0"]
+            t = {f"init.{n}": p.detach().clone() for n, p in
+                 dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec).items()}
+            trainer.fit()
+            for n, p in dict(W_enc=sae.encoder.weight, b_enc=sae.encoder.bias, W_dec=sae.W_dec, b_dec=sae.b_dec).items():
+                t[f"final.{n}"] = p
+            t["best_loss"] = torch.tensor(float(trainer.best_loss))
+            save(f"trainer_{loss_fn}", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=1e-2, warmup=1))
+
+
 def gen_trajectory200(sparsify):
     """200 optimiser steps of the reference Trainer at the CPU configuration
     (d_in=768, 24576 latents, k=32, 4096 tokens/step, fp32, Adam, AuxK enabled)
@@ -396,6 +422,7 @@ if __name__ == "__main__":
     gen_trainer(ref)
     gen_trainer_muon(ref)
     gen_trainer_signum(ref)
+    gen_trainer_e2e(ref)
     gen_muon(ref)
     if "--trajectory" in sys.argv:  # about three minutes of CPU time on 8 threads
         gen_trajectory200(ref)

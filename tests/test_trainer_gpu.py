@@ -160,3 +160,34 @@ def test_signum_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
         assert rel_l2(saved[key], t[f"saved.{name}"]) < 5e-3, name
     st = torch.load(tmp_path / "run" / "optimizer_0.pt")
     assert st["param_groups"][0]["k"] == meta["steps"] and st["param_groups"][0]["train_mode"] is False
+
+
+@pytest.mark.parametrize("loss_fn", ["ce", "kl"])
+def test_end_to_end_losses_match_reference_trainer(cuda_lib, tmp_path, loss_fn):
+    """loss_fn="ce"/"kl": the sparse coder spliced into a small live language model and
+    trained by the model's own loss, against the reference Trainer's final parameters
+    (tests/golden/trainer_{ce,kl}.safetensors; model and tokens are rebuilt from seeds)."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig, TrainConfig, Trainer
+    from tests.fake_model import TinyLM, token_dataset
+    t, meta = load_golden(f"trainer_{loss_fn}")
+    SparseCoder.default_precision = "fp32"
+    try:
+        cfg = TrainConfig(SparseCoderConfig(num_latents=meta["M"], k=meta["k"]), batch_size=meta["B"],
+                          optimizer="adam", lr=meta["lr"], lr_warmup_steps=meta["warmup"], loss_fn=loss_fn,
+                          hookpoints=["layers.0"], log_to_wandb=False, save_dir=str(tmp_path), run_name="run",
+                          save_every=10 ** 9)
+        model = TinyLM(d=meta["D"], ctx=meta["T"]).cuda()
+        trainer = Trainer(cfg, token_dataset(meta["steps"], meta["B"], meta["T"]), model)
+    finally:
+        SparseCoder.default_precision = "bf16"
+    sae = trainer.saes["layers.0"]
+    with torch.no_grad():
+        sae.encoder.weight.copy_(t["init.W_enc"]); sae.encoder.bias.copy_(t["init.b_enc"])
+        sae.W_dec.copy_(t["init.W_dec"]); sae.b_dec.copy_(t["init.b_dec"])
+    trainer.fit()
+    key = "ce_loss" if loss_fn == "ce" else "kl_loss"
+    assert len(trainer.metrics) == meta["steps"] and all(key in row and row[key] > 0 for row in trainer.metrics)
+    unit = lambda w: w / w.norm(dim=1, keepdim=True)
+    for name, p in (("W_enc", sae.encoder.weight), ("b_enc", sae.encoder.bias), ("b_dec", sae.b_dec)):
+        assert rel_l2(p.detach(), t[f"final.{name}"]) < 5e-3, (name, rel_l2(p.detach(), t[f"final.{name}"]))
+    assert rel_l2(unit(sae.W_dec.detach().cpu()), unit(t["final.W_dec"])) < 5e-3
