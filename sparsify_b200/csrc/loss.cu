@@ -88,6 +88,27 @@ sqdiff_partial_kernel(const TA* __restrict__ a, const float* __restrict__ b, int
   if (threadIdx.x == 0) partial[blockIdx.x] = acc;
 }
 
+// Row-wise form of the broadcast case for D % 4 == 0: a block walks whole rows, every thread
+// keeps its columns' means in registers (no index arithmetic per element, 8/16-byte loads).
+template <typename TA>
+__global__ void __launch_bounds__(256)
+sqdiff_rows_kernel(const TA* __restrict__ a, const float* __restrict__ mean, int64_t N, int64_t D,
+                   float* __restrict__ partial) {
+  __shared__ float scratch[33];
+  float acc = 0.f;
+  for (int64_t c0 = (int64_t)threadIdx.x * 4; c0 < D; c0 += 1024) {
+    const float4 mu = __ldg(reinterpret_cast<const float4*>(mean + c0));
+#pragma unroll 4
+    for (int64_t r = blockIdx.x; r < N; r += gridDim.x) {
+      const float4 v = sc::load4<TA>(a + r * D + c0);
+      const float ex = v.x - mu.x, ey = v.y - mu.y, ez = v.z - mu.z, ew = v.w - mu.w;
+      acc = fmaf(ex, ex, acc); acc = fmaf(ey, ey, acc); acc = fmaf(ez, ez, acc); acc = fmaf(ew, ew, acc);
+    }
+  }
+  acc = sc::block_sum(acc, scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
 __global__ void __launch_bounds__(256)
 final_sum_kernel(const float* __restrict__ partial, int n, float* __restrict__ out) {
   __shared__ float scratch[33];
@@ -127,11 +148,18 @@ extern "C" int sc_total_variance(const void* y, int y_dtype, int64_t N, int64_t 
   SC_CHECK_LAUNCH("colsum_partial");
   colsum_finish_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(partial, 1.f / (float)N, D, mean);
   SC_CHECK_LAUNCH("colsum_finish");
-  const int blocks = flat_blocks(N * D);
-  if (y_dtype == SC_F32)
+  int blocks = flat_blocks(N * D);
+  if (D % 4 == 0 && sc::aligned(y, 16)) {
+    blocks = (int)(N < kRedBlocks ? N : kRedBlocks);
+    if (y_dtype == SC_F32)
+      sqdiff_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(y), mean, N, D, red);
+    else
+      sqdiff_rows_kernel<bf16><<<blocks, 256, 0, st>>>(static_cast<const bf16*>(y), mean, N, D, red);
+  } else if (y_dtype == SC_F32) {
     sqdiff_partial_kernel<true, float><<<blocks, 256, 0, st>>>(static_cast<const float*>(y), mean, N * D, D, nullptr, red);
-  else
+  } else {
     sqdiff_partial_kernel<true, bf16><<<blocks, 256, 0, st>>>(static_cast<const bf16*>(y), mean, N * D, D, nullptr, red);
+  }
   SC_CHECK_LAUNCH("sqdiff_partial");
   final_sum_kernel<<<1, 256, 0, st>>>(red, blocks, tv);
   SC_CHECK_LAUNCH("final_sum");
