@@ -86,22 +86,67 @@ def measured_peaks() -> dict:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
-    region runs."""
+    """Samples SM clocks and clock-event reasons while the timed region runs: NVML
+    queries (read-only) from a thread every 20 ms; `nvidia-smi -lms` as the fallback when
+    the NVML binding is missing. Only samples taken after mark() are reported."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines: list[str] = []
+        self.thread = None
+        self.stop_flag = threading.Event()
+        self.samples: list[tuple[float, float, float, tuple[str, ...]]] = []  # (t, sm, max, reasons)
+        self.t_mark = 0.0
+        self.error: str | None = None
+
+    def mark(self):
+        """Start of the timed region: samples that arrived earlier (warm-up) are dropped."""
+        self.t_mark = time.monotonic()
+
+    def physical_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                return int(vis.split(",")[self.index])
+            except (ValueError, IndexError):
+                pass
+        return self.index
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.physical_index())
+            bits = [(pynvml.nvmlClocksEventReasonHwSlowdown, "hw_slowdown"),
+                    (pynvml.nvmlClocksEventReasonHwThermalSlowdown, "hw_thermal_slowdown"),
+                    (pynvml.nvmlClocksEventReasonSwThermalSlowdown, "sw_thermal_slowdown"),
+                    (pynvml.nvmlClocksEventReasonSwPowerCap, "sw_power_cap")]
+            mx = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+            def poll():
+                while not self.stop_flag.is_set():
+                    try:
+                        sm = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        self.samples.append((time.monotonic(), sm, mx, tuple(n for b, n in bits if mask & b)))
+                    except pynvml.NVMLError as exc:
+                        self.error = str(exc)
+                        return
+                    self.stop_flag.wait(0.02)
+
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception as exc:  # no NVML binding or no permission: fall back to nvidia-smi
+            self.error = f"nvml: {exc}"
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                ["nvidia-smi", f"--id={self.physical_index()}", f"--query-gpu={self.FIELDS}",
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
@@ -111,32 +156,33 @@ class ClockSampler:
     def _pump(self):
         assert self.proc is not None and self.proc.stdout is not None
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
+                sm, mx = float(parts[0]), float(parts[1])
             except ValueError:
                 continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            reasons = tuple(n for n, v in zip(self.NAMES, parts[2:6]) if v.lower().startswith("active"))
+            self.samples.append((time.monotonic(), sm, mx, reasons))
+
+    def stop(self) -> dict:
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.thread is None and self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source: " + str(self.error)]}
+        used = [smp for smp in self.samples if smp[0] >= self.t_mark]
+        sm = [smp[1] for smp in used]
+        reasons = sorted({r for smp in used for r in smp[3]})
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": used[-1][2] if used else None, "reasons": reasons, "samples": len(sm)}
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -317,6 +363,11 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the sampler starts before the warm-up so that nvidia-smi is already reporting when the
+    # timed region begins; only samples taken after mark() are used
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     tgt = (lambda t: targets[t % len(targets)]) if a.transcode else (lambda t: None)
     for t in range(max(a.warmup, 3)):
         step(pool[t % len(pool)], tgt(t))
@@ -325,11 +376,9 @@ def run_ours(a):
     # ---- device-resident timing -------------------------------------------
     counter = LaunchCounter()
     ops.timers = {}
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
+    sampler.mark()
     e0.record()
     for t in range(a.steps):
         step(pool[t % len(pool)], tgt(t))
