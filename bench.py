@@ -58,6 +58,10 @@ def parse_args():
     ap.add_argument("--dead-frac", type=float, default=0.0,
                     help="mark this fraction of the latents dead (fixed seed) so that the AuxK branch is "
                          "active in every step; 0 = the natural state (no latent dead yet)")
+    ap.add_argument("--modules", type=int, default=0,
+                    help="secondary workload: this many hookpoints per rank, each with its own sparse coder "
+                         "trained by Muon on activations gathered from every rank (distribute_modules); "
+                         "--tokens is then the tokens per hookpoint per step over all ranks")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone on random inputs of the given sizes instead of the step: "
                          "encode | decode | bwd_acts | csr | rows | adam | normalize | all | ns | gemm")
@@ -236,7 +240,8 @@ def run_reference(a):
 
 # --------------------------------------------------------------------------- GPU arm
 LAUNCHES_PER_CALL = {  # kernels each C-ABI entry point enqueues
-    "sc_encode_topk": 3, "sc_csr_build": 4, "sc_total_variance": 4, "sc_sq_err": 2, "sc_weighted_colsum": 2,
+    "sc_encode_topk": 3, "sc_csr_build": 6, "sc_total_variance": 4, "sc_sq_err": 2, "sc_weighted_colsum": 2,
+    "sc_decode_residual": 2, "sc_muon_momentum": 2,
 }
 
 
@@ -466,6 +471,108 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def run_modules(a):
+    """Hookpoints sharded over ranks, no gradient exchange, Muon (sparsify/trainer.py:358-380,
+    123-145): every rank holds a slice of each hookpoint's tokens, the owner gathers them,
+    trains its coder, and orthogonalises its own matrices."""
+    import torch.distributed as dist
+
+    from sparsify_b200 import SparseCoder, SparseCoderConfig, parallel
+    from sparsify_b200.muon import Muon
+    from sparsify_b200.optim import FusedAdam
+    from sparsify_b200.synthetic import SyntheticActivations, batch_seed
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H, D, M, k = a.modules, a.d, a.latents, a.k
+    n_local = a.tokens // world
+    saes = []
+    for h in range(H):
+        torch.manual_seed(rank * H + h)
+        saes.append(SparseCoder(D, SparseCoderConfig(num_latents=M, k=k), device=dev, dtype=torch.float32))
+    mats = [p for s_ in saes for p in s_.parameters() if p.ndim >= 2]
+    vecs = [p for s_ in saes for p in s_.parameters() if p.ndim < 2]
+    muon, adam = Muon(mats, lr=2e-3, ddp=False), FusedAdam(vecs, lr=2e-3)
+    for s_ in saes:
+        s_.attach_optimizer(muon, project=False)
+    gen = SyntheticActivations(D, a.atoms, a.active, device=dev)
+    pool = [gen.batch(n_local, batch_seed(t, rank, world, hookpoint=t), torch.bfloat16) for t in range(4)]
+    del gen
+    torch.cuda.empty_cache()
+    with torch.no_grad():
+        for s_ in saes:
+            s_.b_dec.copy_(pool[0].float().mean(0))
+
+    def step(t):
+        for g in range(H * world):            # every hookpoint of the model, in order
+            owner = g // H
+            x = pool[(t + g) % len(pool)]
+            if world > 1:
+                x = parallel.gather_to_owner(x, owner)
+            if rank != owner:
+                continue
+            sae = saes[g % H]
+            sae.set_decoder_norm_to_unit_norm()
+            out = sae(x)
+            (out.fvu + out.auxk_loss / 32).backward()
+        for sae in saes:
+            sae.remove_gradient_parallel_to_decoder_directions()
+        for opt in (muon, adam):
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for t in range(max(a.warmup, 3)):
+        step(t)
+    sync()
+    counter = LaunchCounter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark()
+    e0.record()
+    for t in range(a.steps):
+        step(t)
+    e1.record()
+    sync()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    if rank == 0:
+        peaks = measured_peaks()
+        ns_flops = 2 * H * 5 * (2 * D * D * M * 2 + 2 * D * D * D)   # per rank, as a library computes them
+        enc_flops = 2.0 * H * a.tokens * D * M
+        print(json.dumps({
+            "metric": METRIC, "value": H * world * a.tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{H * world} hookpoints of width {D} sharded over {world} rank(s) "
+                                   f"({H} per rank, distribute_modules), {M} latents, k={k}, {a.tokens} tokens per "
+                                   f"hookpoint per step, Muon (5 Newton-Schulz steps on W_enc and W_dec) + Adam on "
+                                   f"the biases, bf16 operands", "parallelism": f"modules{world}"},
+            "gpu_launches": counter.n, "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel + encode_topk_tc_kernel",
+                         "achieved": (ns_flops + enc_flops) / (ms * 1e-3) / 1e12, "peak": peaks["tflops"],
+                         "unit": "TFLOP/s", "frac": (ns_flops + enc_flops) / (ms * 1e-3) / 1e12 / peaks["tflops"],
+                         "peak_source": peaks["source"], "traffic": None,
+                         "note": "whole step; FLOPs counted as a library computes Newton-Schulz (no symmetry)"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_kernel(a):
     """Times single entry points in isolation (CUDA events on the launching
     stream, 2 warm-up + 5 timed launches) and prints one JSON line per kernel."""
@@ -568,6 +675,8 @@ if __name__ == "__main__":
     args = parse_args()
     if args.kernel:
         run_kernel(args)
+    elif args.modules:
+        run_modules(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -93,6 +93,16 @@ int sc_encode_topk(const void* x_bf16, const void* W_bf16, const float* bias,
                    int64_t* top_idx, void* ws, size_t ws_bytes,
                    int32_t* status_word, void* stream);
 
+/* The same kernel with the groupmax activation of sparsify/fused_encoder.py:34-43:
+ * the M latents form k groups of M/k consecutive latents; per row and group the
+ * largest post-ReLU pre-activation and its latent index (ties: lowest index),
+ * written in group order to top_vals / top_idx [N,k]. bf16 operands, D % 8 == 0;
+ * group size 32, 64, 128 or a multiple of 256 (SC_ERR_UNSUPPORTED otherwise: use
+ * sc_preacts_dense + sc_groupmax_rows). No workspace. status_word as above. */
+int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const float* bias,
+                       int64_t N, int64_t D, int64_t M, int k, float* top_vals,
+                       int64_t* top_idx, int32_t* status_word, void* stream);
+
 /* ---- sparse decode (embedding bag) --------------------------------------
  * out[n,:] = (bias ? bias : 0) + sum_j acts[n,j] * W[idx[n,j],:]
  * sparsify/xformers.py:9-53 (embedding_bag_k), sparsify/utils.py:81-90,

@@ -40,6 +40,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_groupmax_rows": (c_int, [P, I64, I64, c_int, P, P, P]),
     "sc_encode_topk_workspace_bytes": (c_size_t, [I64, I64, I64, c_int]),
     "sc_encode_topk": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, c_size_t, P, P]),
+    "sc_encode_groupmax": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, P]),
     "sc_embedding_bag_fwd": (c_int, [P, P, P, c_int, P, I64, I64, I64, c_int, P, P]),
     "sc_embedding_bag_bwd_acts": (c_int, [P, P, c_int, P, c_int, I64, I64, I64, c_int, P, P]),
     "sc_decode_residual_workspace_bytes": (c_size_t, [I64]),

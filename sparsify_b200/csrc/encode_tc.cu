@@ -54,6 +54,12 @@ struct Params {
   int64_t N, D, M;
   int k, n_rb, n_ct, n_strips, stages, units;
   int row_group;  // row blocks per scheduling group
+  // groupmax mode (group_cols > 0): the M columns form k groups of group_cols consecutive
+  // latents and every row keeps the largest post-ReLU value of each group; results go
+  // straight to gm_vals / gm_idx ([N, k]), strips hold whole groups, no lists, no merge.
+  int group_cols;
+  float* gm_vals;
+  int64_t* gm_idx;
   int debug;  // diagnostics: bit 0 = epilogue only drains (no bias / top-k work)
   uint32_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
@@ -307,11 +313,18 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       float published = -1.f;  // last bound this thread pushed to p.tau
       unsigned n_ins = 0, n_cols = 0;  // diagnostics (debug bit 1)
       // rows past N are padding: an infinite bound keeps them out of the lists
-      float tau = (grow < p.N) ? __ldcg(p.tau + grow) : INFINITY;
+      float tau = (grow < p.N && p.group_cols == 0) ? __ldcg(p.tau + grow) : INFINITY;
       // Threshold the raw (pre-ReLU) value is compared with: max(thr, tau), or
       // -inf while that is still negative (list not full and no bound known), so
       // that every value, clamped to >= 0 on insertion, is taken.
       st.thr_cmp = tau < 0.f ? -INFINITY : tau;
+      // groupmax state: current group, position inside it, best value so far and its offset
+      int gm_group = 0, gm_pos = 0, gm_arg = 0;
+      float gm_best = -1.f;
+      if (p.group_cols > 0) {
+        gm_group = (int)(strip_col0 / p.group_cols);
+        gm_pos = (int)(strip_col0 % p.group_cols);
+      }
 
       for (int t = t0; t < t1 && ok; ++t) {
         __syncwarp();
@@ -344,10 +357,31 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             v[4 * i4 + 2] = __uint_as_float(r[4 * i4 + 2]) + b4.z;
             v[4 * i4 + 3] = __uint_as_float(r[4 * i4 + 3]) + b4.w;
           }
+          const int valid = ncols - c * 32;  // columns of this chunk inside the matrix
+          if (p.group_cols > 0) {
+            // a chunk of 32 columns lies inside one group (group_cols % 32 == 0)
+            if (valid <= 0) continue;
+            float best = fmaxf(v[0], 0.f);
+            int bi = 0;
+#pragma unroll
+            for (int i = 1; i < 32; ++i) {
+              const float xv = fmaxf(v[i], 0.f);
+              if (i < valid && xv > best) { best = xv; bi = i; }  // strict: ties keep the lowest index
+            }
+            if (best > gm_best) { gm_best = best; gm_arg = gm_pos + bi; }
+            gm_pos += 32;
+            if (gm_pos >= p.group_cols) {
+              if (grow < p.N) {
+                p.gm_vals[grow * k + gm_group] = gm_best;
+                p.gm_idx[grow * k + gm_group] = (int64_t)gm_group * p.group_cols + gm_arg;
+              }
+              ++gm_group; gm_pos = 0; gm_best = -1.f;
+            }
+            continue;
+          }
           unsigned m = 0;
 #pragma unroll
           for (int i = 0; i < 32; ++i) m |= (v[i] > st.thr_cmp ? 1u : 0u) << i;
-          const int valid = ncols - c * 32;  // columns of this chunk inside the matrix
           if (valid < 32) m &= valid <= 0 ? 0u : ((1u << valid) - 1u);
           // Pass 2: every row walks its own marked columns (ascending), so the loop
           // runs as often as the busiest row has candidates, not once per marked column.
@@ -373,7 +407,7 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         }
         // Exchange the row's lower bound with the CTAs working on other strips of
         // the same rows: push ours when it grew, pull theirs for the next tile.
-        if (grow < p.N) {
+        if (grow < p.N && p.group_cols == 0) {
           if (st.cnt == k && st.thr > published) {
             atomicMax(reinterpret_cast<int*>(p.tau + grow), __float_as_int(st.thr));
             published = st.thr;
@@ -395,7 +429,7 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         if (lane == 0) atomicAdd(p.status + 2, (int)n_cols);
       }
       // write this strip's candidates and publish the row's lower bound
-      if (grow < p.N) {
+      if (grow < p.N && p.group_cols == 0) {
         float* cv = p.cand_vals + (grow * p.n_strips + strip) * k;
         int32_t* ci = p.cand_idx + (grow * p.n_strips + strip) * k;
         for (int j = 0; j < k; ++j) {
@@ -460,9 +494,12 @@ topk_merge_kernel(const float* __restrict__ cand_vals, const int32_t* __restrict
   }
 }
 
-int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
+int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols = 0) {
   pl->n_rb = (int)((N + BM - 1) / BM);
   pl->n_ct = (int)((M + BN - 1) / BN);
+  // groupmax with groups of whole tiles: a strip must hold whole groups, i.e. the strip count
+  // divides the group count k
+  const bool whole_groups = group_cols >= BN;
   // Strips per row block: the fewest (longest strips, fewest list insertions)
   // that keep the persistent grid of 148 CTAs busy; strips hold at most 255
   // tiles so that a strip-relative column fits 16 bits.
@@ -471,6 +508,7 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
   int best = -1;
   double best_eff = -1.0;
   for (int s = min_strips; s <= pl->n_ct; ++s) {
+    if (whole_groups && (s > k || k % s != 0)) continue;
     const long units = (long)pl->n_rb * s;
     const long waves = (units + sms - 1) / sms;
     const double eff = (double)units / (double)(waves * sms);
@@ -480,9 +518,10 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl) {
   }
   pl->n_strips = best < 1 ? 1 : best;
   pl->units = pl->n_rb * pl->n_strips;
-  const size_t lists_val = (size_t)BM * k * sizeof(float);
-  const size_t lists_idx = (size_t)BM * k * sizeof(uint16_t);
-  const size_t groups = (size_t)(k + 7) / 8;
+  const int kl = group_cols > 0 ? 1 : k;  // groupmax keeps no lists
+  const size_t lists_val = (size_t)BM * kl * sizeof(float);
+  const size_t lists_idx = (size_t)BM * kl * sizeof(uint16_t);
+  const size_t groups = (size_t)(kl + 7) / 8;
   const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
   const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
   const size_t budget = 227 * 1024;
@@ -550,6 +589,7 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   p.debug = dbg ? atoi(dbg) : 0;
   const char* rg_env = getenv("SC_ENCODE_ROWGROUP");
   p.row_group = rg_env && atoi(rg_env) > 0 ? atoi(rg_env) : kRowGroupDefault;
+  p.group_cols = 0; p.gm_vals = nullptr; p.gm_idx = nullptr;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
   p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
   p.off_gmin = (uint32_t)pl.off_gmin; p.off_gpos = (uint32_t)pl.off_gpos;
@@ -568,5 +608,49 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   const int ncand = pl.n_strips * k;
   topk_merge_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(cand_vals, cand_idx, N, ncand, k, top_vals, top_idx);
   SC_CHECK_LAUNCH("topk_merge");
+  return SC_OK;
+}
+
+extern "C" int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const float* bias, int64_t N,
+                                  int64_t D, int64_t M, int k, float* top_vals, int64_t* top_idx,
+                                  int32_t* status_word, void* stream) {
+  SC_REQUIRE(N >= 0 && D > 0 && M > 0 && k > 0, "sc_encode_groupmax: bad shape");
+  if (N == 0) return SC_OK;
+  SC_REQUIRE(x_bf16 && W_bf16 && bias && top_vals && top_idx, "sc_encode_groupmax: null pointer");
+  SC_REQUIRE(M % k == 0, "sc_encode_groupmax: M=%lld must be divisible by k=%d", (long long)M, k);
+  const int64_t g = M / k;
+  if (g % 32 != 0 || !(g % BN == 0 || BN % g == 0) || g >= (int64_t(1) << 31))
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_encode_groupmax: group size %lld must be 32, 64, 128 or a multiple of 256",
+                    (long long)g);
+  SC_REQUIRE(D % 8 == 0, "sc_encode_groupmax: D=%lld must be a multiple of 8", (long long)D);
+  SC_REQUIRE(sc::aligned(x_bf16, 16) && sc::aligned(W_bf16, 16), "sc_encode_groupmax: operands must be 16-byte aligned");
+  SC_REQUIRE(N < (int64_t(1) << 31) && M < (int64_t(1) << 31), "sc_encode_groupmax: N, M must be below 2^31");
+  Plan pl;
+  if (make_plan(N, D, M, k, &pl, (int)g) != SC_OK || pl.n_strips < 1)
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_encode_groupmax: no plan for this shape");
+  if (g >= BN && (k % pl.n_strips != 0))
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_encode_groupmax: no strip count divides k=%d", k);
+  CUtensorMap tmx, tmw;
+  int rc = make_tensor_map_bf16(&tmx, x_bf16, (uint64_t)N, (uint64_t)D, BM);
+  if (rc != SC_OK) return rc;
+  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN);
+  if (rc != SC_OK) return rc;
+  Params p;
+  p.bias = bias; p.cand_vals = nullptr; p.cand_idx = nullptr; p.tau = nullptr; p.status = status_word;
+  p.N = N; p.D = D; p.M = M; p.k = k;
+  p.debug = 0;
+  p.row_group = kRowGroupDefault;
+  p.group_cols = (int)g; p.gm_vals = top_vals; p.gm_idx = top_idx;
+  p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
+  p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
+  p.off_gmin = (uint32_t)pl.off_gmin; p.off_gpos = (uint32_t)pl.off_gpos;
+  p.off_bias = (uint32_t)pl.off_bias; p.off_bars = (uint32_t)pl.off_bars;
+  cudaStream_t st = sc::as_stream(stream);
+  SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = pl.units < sms ? pl.units : sms;
+  encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
+  SC_CHECK_LAUNCH("encode_groupmax_tc");
   return SC_OK;
 }

@@ -78,6 +78,14 @@ class FusedEncoder(torch.autograd.Function):
                 wide = (values, indices)
                 values, indices = values[:, :k].contiguous(), indices[:, :k].contiguous()
             x_saved = xb
+        elif (activation == "groupmax" and low_precision and not need_pre_acts
+              and ops.tc_groupmax_supported(D, M, k)):
+            xb = x_c if x_c.dtype == torch.bfloat16 else ops.prep_input(x_c, None, torch.bfloat16)
+            if weight_bf16 is None:
+                w_c = weight.detach().contiguous()
+                weight_bf16 = w_c if w_c.dtype == torch.bfloat16 else ops.cast_bf16(w_c)
+            values, indices = ops.encode_groupmax_tc(xb, weight_bf16, bias, k)
+            x_saved = xb
         else:
             if low_precision:
                 # same operand rounding as the tensor-core path, fp32 accumulation

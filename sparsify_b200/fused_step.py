@@ -44,6 +44,8 @@ class FusedSaeStep(torch.autograd.Function):
         w_enc_src = sae.shadow("encoder.weight") if lowp else W_enc.detach()
         if cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
             acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), k)
+        elif cfg.activation == "groupmax" and lowp and ops.tc_groupmax_supported(D, M, k):
+            acts, idx = ops.encode_groupmax_tc(xe, w_enc_src, b_enc.detach(), k)
         else:
             if lowp and D % 8 == 0:
                 pre = ops.gemm_nt(xe, w_enc_src, bias=b_enc.detach(), relu=True, out_dtype=torch.float32)

@@ -129,6 +129,33 @@ def encode_topk_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tupl
     return vals, idx
 
 
+def tc_groupmax_supported(D: int, M: int, k: int) -> bool:
+    if D % 8 or k <= 0 or M % k:
+        return False
+    g = M // k
+    return g % 32 == 0 and (g % 256 == 0 or 256 % g == 0)
+
+
+def encode_groupmax_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tuple[Tensor, Tensor]:
+    """Tensor-core encoder with the groupmax activation: per row, the largest post-ReLU
+    pre-activation of each of the k groups of M/k consecutive latents, in group order."""
+    _check_cuda(x_bf16, W_bf16, bias)
+    assert x_bf16.dtype == torch.bfloat16 and W_bf16.dtype == torch.bfloat16
+    x_bf16, W_bf16 = x_bf16.contiguous(), W_bf16.contiguous()
+    N, D = x_bf16.shape
+    M = W_bf16.shape[0]
+    dev = x_bf16.device
+    vals = torch.empty(N, k, dtype=torch.float32, device=dev)
+    idx = torch.empty(N, k, dtype=torch.int64, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    bias32 = _f32(bias)
+    with torch.cuda.device(dev):
+        call("sc_encode_groupmax", ptr(x_bf16), ptr(W_bf16), ptr(bias32), N, D, M, int(k),
+             ptr(vals), ptr(idx), ptr(status), _stream(x_bf16))
+    encode_groupmax_tc.last_status = status
+    return vals, idx
+
+
 def embedding_bag_fwd(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None = None) -> Tensor:
     """out[n] = bias + sum_j acts[n, j] * W[idx[n, j]], fp32."""
     _check_cuda(idx, acts, W, bias)

@@ -385,3 +385,28 @@ def test_muon_elementwise_kernels(cuda_lib):
     ops.muon_apply_(pd, s_, 0.999, 0.03, shadow)
     want_p = p * 0.999 - 0.03 * want.float()
     assert rel_l2(pd, want_p) < 1e-6 and torch.equal(shadow, pd.bfloat16())
+
+
+@pytest.mark.parametrize("N,D,M,k", [(200, 128, 4096, 8), (130, 64, 2048, 32), (300, 256, 3072, 4),
+                                      (128, 64, 192, 3), (1000, 128, 16384, 64)])
+def test_encode_groupmax_tc(cuda_lib, N, D, M, k):
+    """Groupmax in the tensor-core encoder against the oracle on the same bf16-rounded
+    operands (fused_encoder.py:34-43): group sizes below, equal to and above one tile."""
+    from sparsify_b200 import ops
+    assert ops.tc_groupmax_supported(D, M, k)
+    g = torch.Generator().manual_seed(N + M)
+    x = bf16_round(torch.randn(N, D, generator=g))
+    W = bf16_round(torch.randn(M, D, generator=g) / D ** 0.5)
+    b = 0.1 * torch.randn(M, generator=g)
+    vals, idx = ops.encode_groupmax_tc(x.cuda().bfloat16(), W.cuda().bfloat16(), b.cuda(), k)
+    torch.cuda.synchronize()
+    assert int(ops.encode_groupmax_tc.last_status[0]) == 0
+    pre = O.preacts(x, W, b)
+    rv, ri = O.groupmax(pre, k)
+    vals, idx = vals.cpu(), idx.cpu()
+    assert rel_l2(vals, rv) < 1e-5
+    # the chosen latent lies in its group and holds (up to accumulation order) the group's maximum
+    gsz = M // k
+    assert torch.equal(idx // gsz, torch.arange(k).expand(N, k))
+    assert (pre.gather(1, idx) - rv).abs().max() < 1e-4
+    assert (idx == ri).float().mean() > 0.999
