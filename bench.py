@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--dead-frac", type=float, default=0.0,
                     help="mark this fraction of the latents dead (fixed seed) so that the AuxK branch is "
                          "active in every step; 0 = the natural state (no latent dead yet)")
+    ap.add_argument("--reserve-sms", type=int, default=-1,
+                    help="SMs the persistent kernels leave free for NCCL's kernels "
+                         "(default: 0 on one GPU, the measured best with several)")
     ap.add_argument("--modules", type=int, default=0,
                     help="secondary workload: this many hookpoints per rank, each with its own sparse coder "
                          "trained by Muon on activations gathered from every rank (distribute_modules); "
@@ -278,6 +281,7 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
 
     N, D, M, k = a.tokens, a.d, a.latents, a.k
+    ops.set_reserved_sms(max(a.reserve_sms, 0) if world > 1 else 0)
     torch.manual_seed(0)  # identical replicas on every rank (sparsify/trainer.py:80-87)
     sae_cfg = SparseCoderConfig(num_latents=M, k=k, transcode=a.transcode, skip_connection=a.transcode,
                                 multi_topk=a.multi_topk)
@@ -490,6 +494,8 @@ def run_modules(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     H, D, M, k = a.modules, a.d, a.latents, a.k
+    from sparsify_b200 import ops as _ops
+    _ops.set_reserved_sms(max(a.reserve_sms, 0) if world > 1 else 0)
     n_local = a.tokens // world
     saes = []
     for h in range(H):
@@ -508,18 +514,33 @@ def run_modules(a):
         for s_ in saes:
             s_.b_dec.copy_(pool[0].float().mean(0))
 
+    # as the Trainer does it: activations travel on one side stream, the owner trains on another,
+    # and the stream that stands for the model's forward only records "activation ready"
+    gather_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    sae_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+
+    def train_one(sae, x):
+        sae.set_decoder_norm_to_unit_norm()
+        out = sae(x)
+        (out.fvu + out.auxk_loss / 32).backward()
+
     def step(t):
+        main = torch.cuda.current_stream(dev)
         for g in range(H * world):            # every hookpoint of the model, in order
             owner = g // H
             x = pool[(t + g) % len(pool)]
-            if world > 1:
-                x = parallel.gather_to_owner(x, owner)
-            if rank != owner:
+            if world == 1:
+                train_one(saes[g % H], x)
                 continue
-            sae = saes[g % H]
-            sae.set_decoder_norm_to_unit_norm()
-            out = sae(x)
-            (out.fvu + out.auxk_loss / 32).backward()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(sae_stream):
+                sae_stream.wait_event(ready)
+                x = parallel.gather_to_owner(x, owner, stream=gather_stream, after=ready)
+                if rank == owner:
+                    train_one(saes[g % H], x)
+        if world > 1:
+            main.wait_stream(sae_stream)
         for sae in saes:
             sae.remove_gradient_parallel_to_decoder_directions()
         for opt in (muon, adam):

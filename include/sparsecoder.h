@@ -44,6 +44,13 @@ enum { SC_ACT_TOPK = 0, SC_ACT_GROUPMAX = 1 };
 
 /* ---- diagnostics ------------------------------------------------------- */
 int sc_version(void);
+
+/* The persistent tensor-core kernels (sc_encode_topk, sc_encode_groupmax,
+ * sc_gemm_bf16_nt) launch one CTA per SM with nearly all of its shared memory,
+ * so no other kernel can start beside them. n > 0 makes them leave n SMs free
+ * (0 <= n <= 64), e.g. for the kernels of a communication library that should
+ * run concurrently. Process-wide; set it before sizing workspaces. */
+int sc_set_reserved_sms(int n);
 /* Copies the last error message (NUL-terminated) into buf; returns its length. */
 size_t sc_last_error(char* buf, size_t cap);
 const char* sc_status_string(int status);

@@ -32,6 +32,7 @@ I64 = c_int64
 # name -> (restype, argtypes); mirrors include/sparsecoder.h one to one.
 SIGNATURES: dict[str, tuple] = {
     "sc_version": (c_int, []),
+    "sc_set_reserved_sms": (c_int, [c_int]),
     "sc_last_error": (c_size_t, [c_char_p, c_size_t]),
     "sc_status_string": (c_char_p, [c_int]),
     "sc_prep_input": (c_int, [P, c_int, P, I64, I64, P, c_int, P]),

@@ -2,6 +2,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -11,7 +12,13 @@ std::mutex g_err_mutex;
 char g_err[512] = "";
 }  // namespace
 
+namespace {
+std::atomic<int> g_reserved_sms{0};
+}  // namespace
+
 namespace sc {
+int reserved_sms() { return g_reserved_sms.load(std::memory_order_relaxed); }
+
 int fail(int status, const char* fmt, ...) {
   std::lock_guard<std::mutex> lock(g_err_mutex);
   va_list ap;
@@ -23,6 +30,12 @@ int fail(int status, const char* fmt, ...) {
 }  // namespace sc
 
 extern "C" int sc_version(void) { return 100; }
+
+extern "C" int sc_set_reserved_sms(int n) {
+  SC_REQUIRE(n >= 0 && n <= 64, "sc_set_reserved_sms: %d outside [0, 64]", n);
+  g_reserved_sms.store(n, std::memory_order_relaxed);
+  return SC_OK;
+}
 
 extern "C" size_t sc_last_error(char* buf, size_t cap) {
   std::lock_guard<std::mutex> lock(g_err_mutex);

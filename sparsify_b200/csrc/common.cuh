@@ -13,6 +13,10 @@ namespace sc {
 // Records the message returned by sc_last_error(); returns `status`.
 int fail(int status, const char* fmt, ...);
 
+// SMs the persistent kernels leave free (sc_set_reserved_sms), e.g. for a
+// communication library's kernels that have to run beside them.
+int reserved_sms();
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Checks the launch of the kernel just enqueued (no synchronisation).

@@ -503,7 +503,7 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols =
   // Strips per row block: the fewest (longest strips, fewest list insertions)
   // that keep the persistent grid of 148 CTAs busy; strips hold at most 255
   // tiles so that a strip-relative column fits 16 bits.
-  const int sms = 148;
+  const int sms = 148 - sc::reserved_sms();
   int min_strips = (pl->n_ct + 254) / 255;
   int best = -1;
   double best_eff = -1.0;
@@ -602,6 +602,7 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   int sms = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  sms -= sc::reserved_sms();
   const int grid = pl.units < sms ? pl.units : sms;
   encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
   SC_CHECK_LAUNCH("encode_topk_tc");
@@ -649,6 +650,7 @@ extern "C" int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const 
   SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  sms -= sc::reserved_sms();
   const int grid = pl.units < sms ? pl.units : sms;
   encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
   SC_CHECK_LAUNCH("encode_groupmax_tc");

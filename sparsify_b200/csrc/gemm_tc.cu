@@ -348,6 +348,7 @@ extern "C" int sc_gemm_bf16_nt(const void* A_bf16, const void* B_bf16, int64_t M
   SC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  sms -= sc::reserved_sms();
   const int grid = (int)(tiles < sms ? tiles : sms);
   gemm_tc_kernel<<<grid, kThreads, smem, sc::as_stream(stream)>>>(tma, tmb, p);
   SC_CHECK_LAUNCH("sc_gemm_bf16_nt");

@@ -100,6 +100,12 @@ def groupmax_rows(pre: Tensor, k: int) -> tuple[Tensor, Tensor]:
     return vals, idx
 
 
+def set_reserved_sms(n: int) -> None:
+    """Leaves `n` SMs free of the persistent tensor-core kernels (for collectives that
+    should run beside them); see sc_set_reserved_sms."""
+    call("sc_set_reserved_sms", int(n))
+
+
 def tc_encode_supported(D: int, M: int, k: int) -> bool:
     return D % 8 == 0 and 0 < k <= 128 and k <= M
 

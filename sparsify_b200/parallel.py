@@ -38,18 +38,42 @@ def owner_of(plan: list[list[str]], name: str) -> int:
     raise KeyError(name)
 
 
-def gather_to_owner(t: Tensor, owner: int, group=None) -> Tensor | None:
+def gather_to_owner(t: Tensor, owner: int, group=None, stream=None, after=None) -> Tensor | None:
     """Concatenates `t` from all ranks along dim 0 on rank `owner` (rank-major,
-    the layout of all_gather_into_tensor); other ranks get None."""
+    the layout of all_gather_into_tensor); other ranks get None.
+
+    stream: a CUDA stream to run the exchange on. The calling stream then does
+    not wait for the collective unless this rank is the owner, so a rank that
+    only contributes its slice is not held back by the owner's queued work, and
+    the owners of different hookpoints compute side by side. after: the event
+    that marks `t` as complete (default: everything queued on the calling stream)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     t = t.contiguous()
-    if rank == owner:
-        out = t.new_empty(world * t.shape[0], *t.shape[1:])
-        parts = list(out.chunk(world, dim=0))
-        dist.gather(t, parts, dst=owner, group=group)
-        return out
-    dist.gather(t, None, dst=owner, group=group)
-    return None
+    if stream is None or not t.is_cuda:
+        if rank == owner:
+            out = t.new_empty(world * t.shape[0], *t.shape[1:])
+            parts = list(out.chunk(world, dim=0))
+            dist.gather(t, parts, dst=owner, group=group)
+            return out
+        dist.gather(t, None, dst=owner, group=group)
+        return None
+    cur = torch.cuda.current_stream(t.device)
+    if after is not None:
+        stream.wait_event(after)
+    else:
+        stream.wait_stream(cur)  # the slice is complete
+    out = None
+    with torch.cuda.stream(stream):
+        if rank == owner:
+            out = t.new_empty(world * t.shape[0], *t.shape[1:])
+            dist.gather(t, list(out.chunk(world, dim=0)), dst=owner, group=group)
+        else:
+            dist.gather(t, None, dst=owner, group=group)
+    t.record_stream(stream)
+    if out is not None:
+        cur.wait_stream(stream)
+        out.record_stream(cur)
+    return out
 
 
 def all_reduce_(x: Tensor, op: str = "mean", group=None) -> Tensor:

@@ -234,8 +234,25 @@ class Trainer:
         pending_metrics: list[tuple] = []
 
         e2e = self.cfg.loss_fn in ("ce", "kl")
+        # activations travel to their owners on a stream of their own, so a rank that only
+        # contributes its slice is not held back by the owner's queued work
+        gather_stream = (torch.cuda.Stream(device=device)
+                         if self.cfg.distribute_modules and torch.device(device).type == "cuda" else None)
+        # ... and the owner trains its coder on a second stream, so that the model's forward
+        # (and with it the hooks of later layers, on every rank) is not queued behind it
+        sae_stream = torch.cuda.Stream(device=device) if gather_stream is not None else None
+        ragged_possible = bool(self.cfg.exclude_tokens)
 
         def hook(module: nn.Module, inputs, outputs):
+            if sae_stream is None:
+                return hook_body(module, inputs, outputs, None)
+            ready = torch.cuda.Event()
+            ready.record()  # the module's output is complete at this point of the model's stream
+            with torch.cuda.stream(sae_stream):
+                sae_stream.wait_event(ready)
+                return hook_body(module, inputs, outputs, ready)
+
+        def hook_body(module: nn.Module, inputs, outputs, ready):
             aux_out = None
             if isinstance(inputs, tuple):
                 inputs = inputs[0]
@@ -247,10 +264,10 @@ class Trainer:
 
             if self.cfg.distribute_modules:
                 owner = parallel.owner_of(self.module_plan, hookpoint)
-                outputs = parallel.gather_to_owner(outputs, owner)
+                outputs = parallel.gather_to_owner(outputs, owner, stream=gather_stream, after=ready)
                 if self.cfg.sae.transcode:
-                    inputs = parallel.gather_to_owner(inputs, owner)
-                mask = parallel.gather_to_owner(mask.to(torch.uint8), owner)
+                    inputs = parallel.gather_to_owner(inputs, owner, stream=gather_stream, after=ready)
+                mask = parallel.gather_to_owner(mask.to(torch.uint8), owner, stream=gather_stream)
                 if dist.get_rank() != owner:
                     return
                 mask = mask.bool()
@@ -259,7 +276,8 @@ class Trainer:
             inputs = inputs.flatten(0, 1) if self.cfg.sae.transcode else outputs
             mask = mask.flatten(0, 1)
             all_outputs = outputs.detach() if e2e else None
-            ragged = not bool(mask.all())
+            # without excluded tokens the mask is all ones by construction: no read-back
+            ragged = ragged_possible and not bool(mask.all())
             if ragged:
                 outputs = outputs[mask]
                 inputs = inputs[mask] if self.cfg.sae.transcode else outputs
@@ -348,6 +366,8 @@ class Trainer:
             finally:
                 for handle in handles:
                     handle.remove()
+            if sae_stream is not None:
+                torch.cuda.current_stream(device).wait_stream(sae_stream)  # the coders' work joins here
 
             # metric reads (one sync for all hookpoints of this batch)
             for name, fvu, auxk, multi in pending_metrics:
