@@ -243,6 +243,12 @@ class Trainer:
         sae_stream = torch.cuda.Stream(device=device) if gather_stream is not None else None
         ragged_possible = bool(self.cfg.exclude_tokens)
 
+        # Owners do not train inside the hook: they only start the exchange there and train once
+        # the model's forward has returned. A rank's contribution to later hookpoints is then
+        # issued at the pace of the model's forward, not after this rank's own training calls
+        # (whose host-side work would otherwise delay every later owner).
+        deferred: list = []
+
         def hook(module: nn.Module, inputs, outputs):
             if sae_stream is None:
                 return hook_body(module, inputs, outputs, None)
@@ -271,7 +277,13 @@ class Trainer:
                 if dist.get_rank() != owner:
                     return
                 mask = mask.bool()
+                if sae_stream is not None:
+                    deferred.append((hookpoint, inputs, outputs, mask))
+                    return
 
+            return train_hookpoint(hookpoint, inputs, outputs, mask, aux_out, out_shape)
+
+        def train_hookpoint(hookpoint, inputs, outputs, mask, aux_out, out_shape):
             outputs = outputs.flatten(0, 1)
             inputs = inputs.flatten(0, 1) if self.cfg.sae.transcode else outputs
             mask = mask.flatten(0, 1)
@@ -367,6 +379,10 @@ class Trainer:
                 for handle in handles:
                     handle.remove()
             if sae_stream is not None:
+                with torch.cuda.stream(sae_stream):
+                    for job in deferred:  # this rank's hookpoints, in the model's order
+                        train_hookpoint(*job, None, None)
+                deferred.clear()
                 torch.cuda.current_stream(device).wait_stream(sae_stream)  # the coders' work joins here
 
             # metric reads (one sync for all hookpoints of this batch)
