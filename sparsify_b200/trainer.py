@@ -73,6 +73,10 @@ class Trainer:
         self.distribute_modules()
 
         device = model.device
+        if dist.is_initialized() and dist.get_world_size() > 1 and torch.device(device).type == "cuda":
+            # collectives run beside the persistent tensor-core kernels: leave NCCL a few SMs
+            from . import ops
+            ops.set_reserved_sms(int(os.environ.get("SPARSIFY_RESERVED_SMS", "4")))
         input_widths = resolve_widths(model, cfg.hookpoints)
         unique_widths = set(input_widths.values())
         if cfg.distribute_modules and len(unique_widths) > 1:
