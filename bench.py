@@ -421,6 +421,11 @@ def run_ours(a):
     for b in range(2):
         consumed[b].record(main)
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The loss of every step is copied to pinned host memory and read by the host one step
+    # later (while the next step is already queued), as a training loop logs it.
+    loss_host = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ready = [torch.cuda.Event() for _ in range(2)]
+    losses = []
     f0.record()
     fetch(0)
     for t in range(a.steps):
@@ -429,9 +434,16 @@ def run_ours(a):
         main.wait_event(ready[t % 2])
         fvu = step(bufs[t % 2], tgt(t))
         consumed[t % 2].record(main)
-        float(fvu.cpu())
+        loss_host[t % 2].copy_(fvu, non_blocking=True)
+        loss_ready[t % 2].record(main)
+        if t > 0:
+            loss_ready[(t - 1) % 2].synchronize()
+            losses.append(float(loss_host[(t - 1) % 2]))
+    loss_ready[(a.steps - 1) % 2].synchronize()
+    losses.append(float(loss_host[(a.steps - 1) % 2]))
     f1.record()
     sync()
+    assert len(losses) == a.steps and all(v == v for v in losses), "a step's loss did not reach the host"
     ms_e2e = torch.tensor([f0.elapsed_time(f1) / a.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
