@@ -524,9 +524,9 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols =
   const size_t groups = (size_t)(kl + 7) / 8;
   const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
   const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
-  const size_t budget = 227 * 1024;
-  if (fixed + 2 * kStageBytes > budget) return SC_ERR_UNSUPPORTED;
-  int stages = (int)((budget - fixed) / kStageBytes);
+  const size_t smem_limit = 227 * 1024;
+  if (fixed + 2 * kStageBytes > smem_limit) return SC_ERR_UNSUPPORTED;
+  int stages = (int)((smem_limit - fixed) / kStageBytes);
   if (stages > 6) stages = 6;
   pl->stages = stages;
   pl->off_lists_val = (size_t)stages * kStageBytes;
