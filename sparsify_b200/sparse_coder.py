@@ -242,7 +242,7 @@ class SparseCoder(nn.Module):
             sae_out, top_acts, top_indices, fvu, auxk_loss = FusedSaeStep.apply(
                 x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead,
                 self.W_skip)
-            return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_tensor(0.0))
+            return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_zeros(()))
         # Multi-TopK alone needs no dense pre-activations: the encoder kernel selects
         # the top 4k once and the top k is its leading part.
         wide_k = 4 * self.cfg.k if self.cfg.multi_topk and self.cfg.activation == "topk" else 0
@@ -282,7 +282,7 @@ class SparseCoder(nn.Module):
             auxk_loss = (e_hat - e.detach()).pow(2).sum()
             auxk_loss = scale * auxk_loss / total_variance
         else:
-            auxk_loss = sae_out.new_tensor(0.0)
+            auxk_loss = sae_out.new_zeros(())  # filled on the device: no host round trip
 
         l2_loss = e.pow(2).sum()
         fvu = l2_loss / total_variance
@@ -295,7 +295,7 @@ class SparseCoder(nn.Module):
             sae_out = self.decode(top_acts, top_indices)
             multi_topk_fvu = (sae_out - y).pow(2).sum() / total_variance
         else:
-            multi_topk_fvu = sae_out.new_tensor(0.0)
+            multi_topk_fvu = sae_out.new_zeros(())
 
         return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, multi_topk_fvu)
 
