@@ -359,7 +359,8 @@ class Trainer:
             if reducer is not None:
                 reducer.enabled = substep == 0
 
-            N = int(tokens_mask.sum().item())
+            # without excluded tokens every token counts: no read-back of the mask's sum
+            N = int(tokens_mask.sum().item()) if self.cfg.exclude_tokens else tokens_mask.numel()
             num_tokens_in_step += N
 
             # clean next-token distribution for the KL objective (trainer.py:478-483)
