@@ -677,6 +677,11 @@ def run_kernel(a):
         ms = timed(lambda: ops.embedding_bag_fwd(idx, vals, W, None))
         nbytes = N * k * D * 2 + N * k * 12 + N * D * 4
         results.append(dict(kernel="embedding_bag_fwd", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+    if which in ("decode", "all"):
+        yb = gout.bfloat16()
+        ms = timed(lambda: ops.decode_residual(idx, vals, W, None, yb, want_e16=True))
+        nbytes = N * k * D * 2 + N * k * 12 + N * D * (2 + 4 + 2)
+        results.append(dict(kernel="decode_residual", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
     if which in ("bwd_acts", "all"):
         ms = timed(lambda: ops.embedding_bag_bwd_acts(idx, gout, W))
         nbytes = N * k * D * 2 + N * D * 4 + N * k * 12
