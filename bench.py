@@ -397,6 +397,9 @@ def run_ours(a):
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
     enc_ms = statistics.mean(s.elapsed_time(e) for s, e in ops.timers.get("encode_topk", [])) \
         if ops.timers.get("encode_topk") else None
+    upd = ops.timers.get("rows_adam", [])
+    # the optimiser kernel runs as `launches_per_step` launches: sum them per step
+    upd_ms = sum(s_.elapsed_time(e_) for s_, e_ in upd) / a.steps if upd else None
     ops.timers = None
     launches = counter.n
 
@@ -476,6 +479,12 @@ def run_ours(a):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roof,
+            "update_kernel": None if upd_ms is None else {
+                "kernel": "rows_adam_kernel", "ms_per_step": upd_ms, "bound": "hbm",
+                # parameters, moments and bf16 copies of both matrices (26 B per element), plus the
+                # gathered residual and input rows of this rank's share of the exchanged tokens
+                "achieved": (2 * M * D * 26 / world + 2 * world * N * k * D * 2 / world) / (upd_ms * 1e-3) / 1e9,
+                "peak": peaks["hbm"], "unit": "GB/s"},
             "step_roofline": {"ms": step_roof_ms, "frac": step_roof_ms / ms,
                               "def": "max(encoder FLOPs / tensor peak, gather+scatter bytes / HBM peak)"},
         }

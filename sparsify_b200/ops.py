@@ -307,10 +307,13 @@ def rows_adam_(row_ptr: Tensor, entries: Tensor, k: int, coefA: Tensor, vecA: Te
     ha = _lib.AdamHparams(hpA["lr"], hpA["beta1"], hpA["beta2"], hpA["eps"], hpA["step"])
     hb = _lib.AdamHparams(hpB["lr"], hpB["beta1"], hpB["beta2"], hpB["eps"], hpB["step"])
     with torch.cuda.device(pA.device):
+        end = _timed("rows_adam", pA.device)
         call("sc_rows_adam", ptr(row_ptr), ptr(entries), int(k), ptr(coefA), ptr(vecA), dtype_code(vecA),
              ptr(coefB), ptr(vecB), dtype_code(vecB), int(M), int(D), ptr(pA), ptr(mA), ptr(vA), ptr(shadowA),
              int(bool(projectA)), int(bool(normalizeA)), float(norm_eps), ctypes.byref(ha), ptr(pB), ptr(mB),
              ptr(vB), ptr(shadowB), ctypes.byref(hb), ptr(extraA), ptr(extra_rank), int(parts), int(max_ctas), _stream(pA))
+        if end is not None:
+            end.record(torch.cuda.current_stream(pA.device))
 
 
 def total_variance(y: Tensor) -> Tensor:
