@@ -29,6 +29,15 @@ from torch import Tensor
 from . import ops
 
 
+def _start_all_gather(t: Tensor, world: int):
+    """Asynchronous all-gather of `t` along dim 0: (source, gathered buffer, work handle)."""
+    import torch.distributed as dist
+    t = t.contiguous()
+    out = t.new_empty((world * t.shape[0],) + tuple(t.shape[1:]))
+    work = dist.all_gather_into_tensor(out.view(-1), t.view(-1), async_op=True)
+    return t, out, work
+
+
 class FusedSaeStep(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, y: Tensor | None, W_enc: Tensor, b_enc: Tensor, W_dec: Tensor,
@@ -41,6 +50,15 @@ class FusedSaeStep(torch.autograd.Function):
         k = cfg.k
         x = x.detach()
         xe = ops.prep_input(x, None if cfg.transcode else b_dec.detach(), comp)
+        # Sharded data-parallel update: the rows every rank will need from every other rank
+        # (inputs now, residuals after the decode) start travelling as soon as they exist, so
+        # that the exchange runs under the encoder GEMM instead of in front of the update.
+        early = None
+        shard = getattr(sae, "_shard", None)
+        if (shard is not None and sae.defer_weight_update and ctx.needs_input_grad[2] and ctx.needs_input_grad[4]
+                and not getattr(sae, "ragged_tokens", False) and sae.precision == "bf16"):
+            early = {"vecB": _start_all_gather(xe, shard[1])}
+        sae._early = early
         w_enc_src = sae.shadow("encoder.weight") if lowp else W_enc.detach()
         if cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
             acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), k)
@@ -78,6 +96,8 @@ class FusedSaeStep(torch.autograd.Function):
                 ctx.skip = x_b
             sse, e = ops.sq_err(target.to(torch.float32), out, want_diff=True)
             e16 = ops.prep_input(e, None, torch.bfloat16) if sae.precision == "bf16" else None
+        if early is not None and e16 is not None:
+            early["vecA"] = _start_all_gather(e16, shard[1])
         fvu = sse / tv
 
         # ---- AuxK (sparsify/sparse_coder.py:231-249) in compact dense form: the dead

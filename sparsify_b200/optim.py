@@ -229,8 +229,21 @@ class FusedAdam(torch.optim.Optimizer):
             dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1))
             return out
 
+        # the row arrays may already be on their way (started by the forward pass)
+        early = getattr(sae, "_early", None) or {}
+        sae._early = None
+
+        def take(name, t):
+            if name in early:
+                src, out, work = early[name]
+                work.wait()
+                if src is t or (src.data_ptr() == t.data_ptr() and src.shape == t.shape):
+                    return out
+            return gather(t)
+
+        vecB_all = take("vecB", vecB)   # same order on every rank: issued first, waited first
+        vecA_all = take("vecA", vecA)
         idx_all, coefA_all, coefB_all = gather(idx), gather(coefA), gather(coefB)
-        vecA_all, vecB_all = gather(vecA), gather(vecB)
         per = sae.encoder.weight.shape[0] // world
         # indices relative to this rank's slice; the CSR build skips the ones outside [0, per)
         local = idx_all.to(torch.int64) - rank * per
