@@ -180,12 +180,19 @@ class FusedAdam(torch.optim.Optimizer):
             # one launch per matrix: each then gathers from a single [N, D] bf16 array (134 MB at
             # d=4096, 16384 tokens), which L2 holds far better than both at once (-0.3 ms per step)
             ops.rows_adam_(*args, parts=2, **kw)
+            if shard is not None:
+                # everyone needs every row of the encoder copy for the next forward: its
+                # all-gather runs while the decoder half of the update is computed
+                mine = shadow_enc[0][rows].clone()
+                sae._enc_work = dist.all_gather_into_tensor(shadow_enc[0].view(-1), mine.view(-1), async_op=True)
+                sae._enc_work_src = mine
             ops.rows_adam_(*args, parts=1, **kw)
         if shard is not None:
-            # everyone needs every row for the next forward: the encoder copy right away, the
-            # decoder copy only at decode time, so its all-gather runs under the encoder GEMM
-            mine = shadow_enc[0][rows].clone()
-            dist.all_gather_into_tensor(shadow_enc[0].view(-1), mine.view(-1))
+            if getattr(sae, "_overlap_decoder", False):
+                mine = shadow_enc[0][rows].clone()
+                dist.all_gather_into_tensor(shadow_enc[0].view(-1), mine.view(-1))
+            # the decoder copy is needed only at decode time: its all-gather runs under the
+            # encoder GEMM of the next forward
             mine_dec = shadow_dec[0][rows].clone()
             sae.wait_decoder()
             sae._dec_work = dist.all_gather_into_tensor(shadow_dec[0].view(-1), mine_dec.view(-1), async_op=True)

@@ -87,6 +87,7 @@ class SparseCoder(nn.Module):
         self._dec_unit_norm: tuple | None = None  # (data_ptr, version) at which W_dec rows had unit norm
         self._dec_event = None  # completion of a decoder update running on a side stream
         self._dec_work = None  # asynchronous all-gather of the decoder's bf16 copy
+        self._enc_work = None  # the same for the encoder's copy
         self._shadows: dict[str, tuple[int, int, Tensor]] = {}
 
         self.encoder = nn.Linear(d_in, self.num_latents, device=device, dtype=dtype)
@@ -189,6 +190,8 @@ class SparseCoder(nn.Module):
         p = self.encoder.weight if name == "encoder.weight" else getattr(self, name)
         if p is None:
             return None
+        if name == "encoder.weight":
+            self.wait_encoder()
         if p.dtype == torch.bfloat16:
             return p.detach()
         hit = self._shadows.get(name)
@@ -322,6 +325,14 @@ class SparseCoder(nn.Module):
             # construction / checkpoint handling on the host before .to("cuda")
             norm = torch.norm(W, dim=1, keepdim=True)
             self.W_dec.data /= norm + eps
+
+    def wait_encoder(self) -> None:
+        """Makes the current stream wait for the all-gather of the encoder's bf16
+        copy that a sharded update left in flight."""
+        work, self._enc_work = getattr(self, "_enc_work", None), None
+        if work is not None:
+            work.wait()
+            self._enc_work_src = None
 
     def wait_decoder(self) -> None:
         """Makes the current stream wait for decoder work that FusedAdam left in
