@@ -333,7 +333,7 @@ def run_ours(a):
         gd = torch.Generator(device="cpu").manual_seed(7)
         fixed_dead = torch.zeros(M, dtype=torch.bool)
         fixed_dead[torch.randperm(M, generator=gd)[: int(a.dead_frac * M)]] = True
-        fixed_dead = fixed_dead.to(dev)
+        fixed_dead = sae.prepare_dead_mask(fixed_dead.to(dev))  # read back once, as the Trainer does per step
 
     def step(x, y=None):
         nonlocal tokens_seen

@@ -81,6 +81,13 @@ int sc_topk_rows(const float* pre, int64_t N, int64_t M, int k,
                  const uint8_t* col_mask, float* top_vals, int64_t* top_idx,
                  void* stream);
 
+/* The same selection written back densely: out_bf16[n,m] = bf16(pre[n,m]) for the
+ * row's k largest entries (among the columns with col_mask != 0 when given) and 0
+ * elsewhere. The AuxK reconstruction of sparsify/sparse_coder.py:240-247 then is
+ * one dense GEMM over the dead latents' columns. */
+int sc_topk_mask_rows(const float* pre, int64_t N, int64_t M, int k,
+                      const uint8_t* col_mask, void* out_bf16, void* stream);
+
 /* groupmax: max and argmax inside each of k contiguous groups of M/k columns.
  * sparsify/fused_encoder.py:34-43. */
 int sc_groupmax_rows(const float* pre, int64_t N, int64_t M, int k,

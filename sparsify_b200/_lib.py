@@ -38,6 +38,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_prep_input": (c_int, [P, c_int, P, I64, I64, P, c_int, P]),
     "sc_preacts_dense": (c_int, [P, c_int, P, c_int, P, I64, I64, I64, P, c_int, P]),
     "sc_topk_rows": (c_int, [P, I64, I64, c_int, P, P, P, P]),
+    "sc_topk_mask_rows": (c_int, [P, I64, I64, c_int, P, P, P]),
     "sc_groupmax_rows": (c_int, [P, I64, I64, c_int, P, P, P]),
     "sc_encode_topk_workspace_bytes": (c_size_t, [I64, I64, I64, c_int]),
     "sc_encode_topk": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, c_size_t, P, P]),

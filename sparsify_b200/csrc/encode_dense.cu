@@ -112,12 +112,15 @@ constexpr int kSelThreads = 512;
 __global__ void __launch_bounds__(kSelThreads)
 topk_rows_kernel(const float* __restrict__ pre, int64_t M, int k,
                  const uint8_t* __restrict__ col_mask, float* __restrict__ top_vals,
-                 int64_t* __restrict__ top_idx) {
+                 int64_t* __restrict__ top_idx, __nv_bfloat16* __restrict__ dense_out) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_out, s_eq;
   const float* row = pre + (int64_t)blockIdx.x * M;
-  float* ov = top_vals + (int64_t)blockIdx.x * k;
-  int64_t* oi = top_idx + (int64_t)blockIdx.x * k;
+  // dense_out != NULL: instead of (values, indices) the row is written back densely as bf16
+  // with everything outside its top k set to zero
+  float* ov = dense_out == nullptr ? top_vals + (int64_t)blockIdx.x * k : nullptr;
+  int64_t* oi = dense_out == nullptr ? top_idx + (int64_t)blockIdx.x * k : nullptr;
+  __nv_bfloat16* od = dense_out == nullptr ? nullptr : dense_out + (int64_t)blockIdx.x * M;
 
   uint32_t prefix = 0, prefix_mask = 0, need = (uint32_t)k;
   for (int shift = 24; shift >= 0; shift -= 8) {
@@ -153,7 +156,9 @@ topk_rows_kernel(const float* __restrict__ pre, int64_t M, int k,
     uint32_t key = (col_mask == nullptr || col_mask[c]) ? order_key(v) : 0u;
     bool take = key > prefix;
     if (!take && key == prefix) take = atomicAdd(&s_eq, 1u) < need;
-    if (take) {
+    if (od != nullptr) {
+      od[c] = __float2bfloat16_rn(take ? v : 0.f);
+    } else if (take) {
       uint32_t slot = atomicAdd(&s_out, 1u);
       if (slot < (uint32_t)k) { ov[slot] = v; oi[slot] = c; }
     }
@@ -256,8 +261,21 @@ extern "C" int sc_topk_rows(const float* pre, int64_t N, int64_t M, int k,
   SC_REQUIRE(pre && top_vals && top_idx, "sc_topk_rows: null pointer");
   SC_REQUIRE(N <= 0x7fffffffLL, "sc_topk_rows: N too large");
   topk_rows_kernel<<<(unsigned)N, kSelThreads, 0, sc::as_stream(stream)>>>(pre, M, k, col_mask,
-                                                                          top_vals, top_idx);
+                                                                          top_vals, top_idx, nullptr);
   SC_CHECK_LAUNCH("sc_topk_rows");
+  return SC_OK;
+}
+
+extern "C" int sc_topk_mask_rows(const float* pre, int64_t N, int64_t M, int k, const uint8_t* col_mask,
+                                 void* out_bf16, void* stream) {
+  SC_REQUIRE(N >= 0 && M > 0 && k > 0, "sc_topk_mask_rows: bad shape");
+  SC_REQUIRE(k <= M, "sc_topk_mask_rows: k=%d exceeds M=%lld", k, (long long)M);
+  if (N == 0) return SC_OK;
+  SC_REQUIRE(pre && out_bf16, "sc_topk_mask_rows: null pointer");
+  SC_REQUIRE(N <= 0x7fffffffLL, "sc_topk_mask_rows: N too large");
+  topk_rows_kernel<<<(unsigned)N, kSelThreads, 0, sc::as_stream(stream)>>>(
+      pre, M, k, col_mask, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16));
+  SC_CHECK_LAUNCH("sc_topk_mask_rows");
   return SC_OK;
 }
 

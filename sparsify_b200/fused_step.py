@@ -106,7 +106,7 @@ class FusedSaeStep(torch.autograd.Function):
         auxk = fvu.new_zeros(())
         ctx.aux = None
         if num_dead > 0:
-            dead_idx = dead_mask.nonzero().squeeze(1)
+            dead_idx = sae.dead_indices(dead_mask)  # no read-back when the mask was prepared
             nd = int(dead_idx.numel())
             pad = (-nd) % 8  # the GEMM wants a multiple of 8 in its contraction dimension
             k_aux = target.shape[-1] // 2
@@ -121,10 +121,10 @@ class FusedSaeStep(torch.autograd.Function):
                 be = torch.cat([be, be.new_zeros(pad)])
             xe_b = xe if xe.dtype == torch.bfloat16 else xe.to(torch.bfloat16)
             P = ops.gemm_nt(xe_b, We, bias=be, relu=True, out_dtype=torch.float32)  # [N, nd + pad]
-            if nd > k_aux:  # keep each row's k_aux largest, zero the rest
-                vals, sel = ops.topk_rows(P, k_aux)
-                P = torch.zeros_like(P).scatter_(1, sel, vals)
-            Pb = P.to(torch.bfloat16)
+            if nd > k_aux:  # keep each row's k_aux largest, zero the rest (one pass, bf16 out)
+                Pb = ops.topk_mask_rows(P, k_aux)
+            else:
+                Pb = P.to(torch.bfloat16)
             e_hat = ops.gemm_nt(Pb, ops.transpose_bf16(Wd), bias=b_dec.detach(), out_dtype=torch.float32)
             sse_aux, diff = ops.sq_err(e_hat, e, want_diff=True)  # diff = e_hat - e
             auxk = scale * sse_aux / tv

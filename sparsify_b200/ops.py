@@ -89,6 +89,18 @@ def topk_rows(pre: Tensor, k: int, col_mask: Tensor | None = None) -> tuple[Tens
     return vals, idx
 
 
+def topk_mask_rows(pre: Tensor, k: int, col_mask: Tensor | None = None) -> Tensor:
+    """bf16 copy of `pre` with everything outside each row's k largest entries zeroed."""
+    _check_cuda(pre, col_mask)
+    pre = pre.detach().to(torch.float32).contiguous()
+    N, M = pre.shape
+    out = torch.empty(N, M, dtype=torch.bfloat16, device=pre.device)
+    mask = col_mask.to(torch.uint8).contiguous() if col_mask is not None else None
+    with torch.cuda.device(pre.device):
+        call("sc_topk_mask_rows", ptr(pre), N, M, int(k), ptr(mask), ptr(out), _stream(pre))
+    return out
+
+
 def groupmax_rows(pre: Tensor, k: int) -> tuple[Tensor, Tensor]:
     _check_cuda(pre)
     pre = pre.detach().to(torch.float32).contiguous()

@@ -240,7 +240,7 @@ class SparseCoder(nn.Module):
     def forward(
         self, x: Tensor, y: Tensor | None = None, *, dead_mask: Tensor | None = None
     ) -> ForwardOutput:
-        num_dead = int(dead_mask.sum()) if dead_mask is not None else 0
+        num_dead = self._count_dead(dead_mask)
         if self.fused and fused_supported(self, x, num_dead):
             sae_out, top_acts, top_indices, fvu, auxk_loss = FusedSaeStep.apply(
                 x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead,
@@ -301,6 +301,34 @@ class SparseCoder(nn.Module):
             multi_topk_fvu = sae_out.new_zeros(())
 
         return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, multi_topk_fvu)
+
+    # ------------------------------------------------------------------ dead latents
+    def prepare_dead_mask(self, dead_mask: Tensor | None) -> Tensor | None:
+        """Reads the dead latents of `dead_mask` back once (their indices, hence their
+        number) and remembers them for the forward call that receives this very tensor.
+        A caller that knows the mask ahead of time - the Trainer, at the end of the
+        previous step, where it reads its metrics anyway - calls this there, and the
+        forward pass then runs without any device read-back."""
+        if dead_mask is None:
+            self._dead_cache = None
+            return None
+        dead_idx = dead_mask.nonzero().squeeze(1)
+        self._dead_cache = (dead_mask, int(dead_idx.numel()), dead_idx)
+        return dead_mask
+
+    def _count_dead(self, dead_mask: Tensor | None) -> int:
+        if dead_mask is None:
+            return 0
+        cache = getattr(self, "_dead_cache", None)
+        if cache is not None and cache[0] is dead_mask:
+            return cache[1]
+        return int(dead_mask.sum())
+
+    def dead_indices(self, dead_mask: Tensor) -> Tensor:
+        cache = getattr(self, "_dead_cache", None)
+        if cache is not None and cache[0] is dead_mask:
+            return cache[2]
+        return dead_mask.nonzero().squeeze(1)
 
     # ------------------------------------------------------------------ decoder norm
     @torch.no_grad()

@@ -162,6 +162,7 @@ class Trainer:
                           if cfg.loss_fn == "fvu" else float("inf"))  # trainer.py:180-184
         self.metrics: list[dict] = []
         self._tokens_seen = 0  # upper bound of every num_tokens_since_fired counter
+        self._dead_masks: dict[str, Tensor] = {}  # next step's dead masks, already read back
 
     # ------------------------------------------------------------------ state
     def load_state(self, path: str):
@@ -181,6 +182,7 @@ class Trainer:
                 elif k in rank_state["best_loss"]:
                     self.best_loss[k] = rank_state["best_loss"][k]
 
+        self._dead_masks.clear()
         print(f"\033[92mResuming training at step {self.global_step} from '{path}'\033[0m")
         for i, scheduler in enumerate(self.lr_schedulers):
             scheduler.load_state_dict(
@@ -322,7 +324,8 @@ class Trainer:
                 out = raw(
                     x=inputs,
                     y=outputs,
-                    dead_mask=(self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold
+                    dead_mask=((self._dead_masks[name] if name in self._dead_masks else
+                                self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold)
                                if may_be_dead else None),
                 )
                 did_fire[name][out.latent_indices.flatten()] = True
@@ -409,6 +412,22 @@ class Trainer:
                     for sae in self.saes.values():
                         sae.remove_gradient_parallel_to_decoder_directions()
 
+                # Dead-latent bookkeeping (trainer.py:529-538; independent of the optimiser step,
+                # done first): the metric reads above have just drained the device queue, so this
+                # is where next step's dead latents are read back (their indices, once) - the
+                # forward pass then needs no read-back of its own.
+                self._tokens_seen += num_tokens_in_step
+                with torch.no_grad():
+                    for name, counts in self.num_tokens_since_fired.items():
+                        counts += num_tokens_in_step
+                        counts[did_fire[name]] = 0
+                        if self.cfg.auxk_alpha > 0 and self._tokens_seen > self.cfg.dead_feature_threshold:
+                            self._dead_masks[name] = self.saes[name].prepare_dead_mask(
+                                counts > self.cfg.dead_feature_threshold)
+                    num_tokens_in_step = 0
+                    for mask in did_fire.values():
+                        mask.zero_()
+
                 for optimizer in self.optimizers:
                     optimizer.step()
                     optimizer.zero_grad()
@@ -418,15 +437,6 @@ class Trainer:
                 k = self.get_current_k()
                 for sae in self.saes.values():
                     sae.cfg.k = k
-
-                self._tokens_seen += num_tokens_in_step
-                with torch.no_grad():
-                    for name, counts in self.num_tokens_since_fired.items():
-                        counts += num_tokens_in_step
-                        counts[did_fire[name]] = 0
-                    num_tokens_in_step = 0
-                    for mask in did_fire.values():
-                        mask.zero_()
 
                 if (step + 1) % self.cfg.save_every == 0:
                     self.save()

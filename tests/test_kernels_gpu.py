@@ -410,3 +410,19 @@ def test_encode_groupmax_tc(cuda_lib, N, D, M, k):
     assert torch.equal(idx // gsz, torch.arange(k).expand(N, k))
     assert (pre.gather(1, idx) - rv).abs().max() < 1e-4
     assert (idx == ri).float().mean() > 0.999
+
+
+def test_topk_mask_rows(cuda_lib):
+    """Dense bf16 row with everything but the k largest entries zeroed, against torch.topk."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    pre = torch.randn(37, 1000, generator=g).clamp_min(0)  # post-ReLU: many ties at zero
+    k = 300
+    out = ops.topk_mask_rows(pre.cuda(), k).cpu()
+    vals, idx = pre.topk(k, dim=1)
+    want = torch.zeros_like(pre).scatter_(1, idx, vals).bfloat16()
+    assert torch.equal(out, want)
+    mask = torch.zeros(1000, dtype=torch.bool); mask[::3] = True
+    out = ops.topk_mask_rows(pre.cuda(), 50, col_mask=mask.cuda()).cpu()
+    vals, idx = torch.where(mask, pre, torch.full_like(pre, -1.0)).topk(50, dim=1)
+    assert torch.equal(out, torch.zeros_like(pre).scatter_(1, idx, vals).bfloat16())
