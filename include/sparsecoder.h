@@ -247,7 +247,7 @@ typedef struct sc_adam_hparams {
  *   A: optional projection (sparsify/sparse_coder.py:281-295), Adam, optional
  *      row normalisation W /= ||W|| + norm_eps (sparse_coder.py:273-279, which
  *      the reference applies before the next forward), bf16 shadow refresh.
- * The dense [M,D] gradients are never materialised. D % 4 == 0, D <= 4096.
+ * The dense [M,D] gradients are never materialised. D % 4 == 0, D <= 8192.
  * hpA / hpB are host pointers. shadow pointers may be NULL. extraA (fp32
  * [n,D]) with extra_rank (int32 [M]: row of extraA for latent m, or -1) adds
  * dense gradient rows to the decoder gradient - the AuxK term of

@@ -16,7 +16,8 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kNV = 4;  // float4 groups per thread: rows of up to 4096 floats
+// float4 groups per thread (template parameter NV): 4 for rows of up to 4096 floats (64
+// registers, four CTAs per SM), 8 for rows of up to 8192 (two CTAs per SM)
 
 struct Hp {
   float lr, beta1, beta2, eps, bc1, bc2_sqrt;
@@ -54,7 +55,7 @@ struct Args {
 };
 
 // sum over the CSR segment [lo, hi) of coef[e] * vec[e / k, cols of this thread]
-template <typename T>
+template <typename T, int kNV>
 __device__ __forceinline__ void gather_rows(const int32_t* __restrict__ entries, int32_t lo, int32_t hi, int k,
                                             const float* __restrict__ coef, const T* __restrict__ vec, int64_t D,
                                             float4 (&g)[kNV]) {
@@ -79,8 +80,8 @@ __device__ __forceinline__ void gather_rows(const int32_t* __restrict__ entries,
 
 // The two matrices are handled one after the other (encoder, then decoder) so that
 // only one gradient row is live at a time: 64 registers, four CTAs per SM.
-template <typename TA, typename TB>
-__global__ void __launch_bounds__(kThreads, 4)
+template <typename TA, typename TB, int kNV>
+__global__ void __launch_bounds__(kThreads, kNV == 4 ? 4 : 2)
 rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const Args a) {
   __shared__ float scratch[33];
   const int64_t D = a.D;
@@ -92,7 +93,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
     float4 g[kNV];
 
     if (doB) {  // ---- encoder row: Adam ----
-      gather_rows<TB>(a.entries, lo, hi, a.k, a.coefB, vecB, D, g);
+      gather_rows<TB, kNV>(a.entries, lo, hi, a.k, a.coefB, vecB, D, g);
 #pragma unroll
       for (int c = 0; c < kNV; ++c) {
         const int col = (c * kThreads + threadIdx.x) * 4;
@@ -114,7 +115,7 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
     if (!doA) continue;
 
     // ---- decoder row: project, Adam, normalise ----
-    gather_rows<TA>(a.entries, lo, hi, a.k, a.coefA, vecA, D, g);
+    gather_rows<TA, kNV>(a.entries, lo, hi, a.k, a.coefA, vecA, D, g);
     if (a.extraA != nullptr) {
       const int32_t r = a.extra_rank[m];
       if (r >= 0) {
@@ -196,9 +197,9 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
              "sc_rows_adam: null pointer");
   SC_REQUIRE(sc::valid_dtype(vecA_dtype) && sc::valid_dtype(vecB_dtype), "sc_rows_adam: bad dtype");
   SC_REQUIRE(hpA->step >= 1 && hpB->step >= 1, "sc_rows_adam: step counts from 1");
-  if (D % 4 != 0 || D > (int64_t)kThreads * 4 * kNV)
+  if (D % 4 != 0 || D > (int64_t)kThreads * 4 * 8)
     return sc::fail(SC_ERR_UNSUPPORTED, "sc_rows_adam: D=%lld must be a multiple of 4 and at most %d",
-                    (long long)D, kThreads * 4 * kNV);
+                    (long long)D, kThreads * 4 * 8);
   const void* ptrs[] = {vecA, vecB, pA, mA, vA, pB, mB, vB};
   for (const void* q : ptrs) SC_REQUIRE(sc::aligned(q, 16), "sc_rows_adam: pointers must be 16-byte aligned");
   Args a;
@@ -216,14 +217,18 @@ extern "C" int sc_rows_adam(const int32_t* row_ptr, const int32_t* entries, int 
   cudaStream_t st = sc::as_stream(stream);
   dim3 grid((unsigned)(max_ctas > 0 && max_ctas < M ? max_ctas : M)), block(kThreads);
   using bf16 = __nv_bfloat16;
-  if (vecA_dtype == SC_F32 && vecB_dtype == SC_F32)
-    rows_adam_kernel<float, float><<<grid, block, 0, st>>>((const float*)vecA, (const float*)vecB, a);
-  else if (vecA_dtype == SC_F32)
-    rows_adam_kernel<float, bf16><<<grid, block, 0, st>>>((const float*)vecA, (const bf16*)vecB, a);
-  else if (vecB_dtype == SC_F32)
-    rows_adam_kernel<bf16, float><<<grid, block, 0, st>>>((const bf16*)vecA, (const float*)vecB, a);
-  else
-    rows_adam_kernel<bf16, bf16><<<grid, block, 0, st>>>((const bf16*)vecA, (const bf16*)vecB, a);
+#define SC_LAUNCH_RA(TA, TB)                                                                          \
+  do {                                                                                                \
+    if (D <= (int64_t)kThreads * 16)                                                                  \
+      rows_adam_kernel<TA, TB, 4><<<grid, block, 0, st>>>((const TA*)vecA, (const TB*)vecB, a);       \
+    else                                                                                              \
+      rows_adam_kernel<TA, TB, 8><<<grid, block, 0, st>>>((const TA*)vecA, (const TB*)vecB, a);       \
+  } while (0)
+  if (vecA_dtype == SC_F32 && vecB_dtype == SC_F32) SC_LAUNCH_RA(float, float);
+  else if (vecA_dtype == SC_F32) SC_LAUNCH_RA(float, bf16);
+  else if (vecB_dtype == SC_F32) SC_LAUNCH_RA(bf16, float);
+  else SC_LAUNCH_RA(bf16, bf16);
+#undef SC_LAUNCH_RA
   SC_CHECK_LAUNCH("sc_rows_adam");
   return SC_OK;
 }

@@ -64,7 +64,7 @@ class FusedAdam(torch.optim.Optimizer):
         Returns whether it was enabled."""
         W = sae.encoder.weight
         ok = (sae.W_dec is not None and W.is_cuda and W.dtype == torch.float32 and W.shape[1] % 4 == 0
-              and W.shape[1] <= 4096)
+              and W.shape[1] <= 8192)
         if ok and data_parallel and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             # Data parallel: ranks exchange the sparse factors (indices, coefficients,
             # residual and input rows) instead of dense gradients and each rank updates
