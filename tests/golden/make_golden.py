@@ -369,7 +369,7 @@ def gen_trainer_e2e(sparsify):
             save(f"trainer_{loss_fn}", t, dict(steps=steps, B=B, T=T, D=D, M=M, k=k, lr=1e-2, warmup=1))
 
 
-def gen_trajectory200(sparsify):
+def gen_trajectory200(sparsify, warmup=10, name="trajectory200"):
     """200 optimiser steps of the reference Trainer at the CPU configuration
     (d_in=768, 24576 latents, k=32, 4096 tokens/step, fp32, Adam, AuxK enabled)
     on the seeded synthetic activations of sparsify_b200.synthetic; only the FVU
@@ -386,7 +386,7 @@ def gen_trajectory200(sparsify):
     fvus = []
     with tempfile.TemporaryDirectory() as tmp:
         cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="adam",
-                          lr_warmup_steps=10, auxk_alpha=1 / 32, hookpoints=["layers.0"], log_to_wandb=False,
+                          lr_warmup_steps=warmup, auxk_alpha=1 / 32, hookpoints=["layers.0"], log_to_wandb=False,
                           save_dir=tmp, run_name="golden", save_every=10**9)
         trainer = Trainer(cfg, dataset, model)
         sae = trainer.saes["layers.0"]
@@ -399,8 +399,8 @@ def gen_trajectory200(sparsify):
 
         sae.forward = recording_forward
         trainer.fit()
-    save("trajectory200", dict(fvu=torch.tensor(fvus)),
-         dict(steps=steps, B=B, T=T, D=D, M=M, k=k, atoms=65536, active=32, warmup=10, auxk_alpha=1 / 32))
+    save(name, dict(fvu=torch.tensor(fvus)),
+         dict(steps=steps, B=B, T=T, D=D, M=M, k=k, atoms=65536, active=32, warmup=warmup, auxk_alpha=1 / 32))
     print("fvu first/last:", fvus[0], fvus[-1])
 
 
@@ -426,3 +426,4 @@ if __name__ == "__main__":
     gen_muon(ref)
     if "--trajectory" in sys.argv:  # about three minutes of CPU time on 8 threads
         gen_trajectory200(ref)
+        gen_trajectory200(ref, warmup=1000, name="trajectory200_warmup1000")  # the reference's default

@@ -106,13 +106,15 @@ def test_muon_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
         assert rel_l2(p.detach(), t[f"final.{name}"]) < 1e-2, (name, rel_l2(p.detach(), t[f"final.{name}"]))
 
 
-def test_fvu_trajectory_200_steps(cuda_lib, tmp_path):
+@pytest.mark.parametrize("fixture,drop", [("trajectory200", 0.05), ("trajectory200_warmup1000", 0.01)])
+def test_fvu_trajectory_200_steps(cuda_lib, tmp_path, fixture, drop):
     """200 steps at d_in=768, 24576 latents, k=32, 4096 tokens per step, bf16 operands:
     the FVU of every step stays within 2 % of the reference Trainer's fp32 CPU run
-    (tests/golden/trajectory200.safetensors) on the same seeded inputs and the same
-    initial weights."""
+    (tests/golden/trajectory200*.safetensors: a 10-step warm-up, where the FVU moves
+    0.71 -> 0.63, and the reference's default of 1000 steps, 0.71 -> 0.70) on the same
+    seeded inputs and the same initial weights."""
     from sparsify_b200.synthetic import SyntheticActivations, batch_seed
-    t, meta = load_golden("trajectory200")
+    t, meta = load_golden(fixture)
     steps, B, T, D, M = meta["steps"], meta["B"], meta["T"], meta["D"], meta["M"]
     gen = SyntheticActivations(D, meta["atoms"], meta["active"], device="cpu")
     acts = torch.stack([gen.batch(B * T, batch_seed(s)).reshape(B, T, D) for s in range(steps)])
@@ -131,7 +133,7 @@ def test_fvu_trajectory_200_steps(cuda_lib, tmp_path):
     assert len(fvus) == steps
     worst = max(abs(a - b) / b for a, b in zip(fvus, want))
     assert worst < 0.02, (worst, fvus[::20], want[::20])
-    assert fvus[-1] < fvus[0] - 0.05  # it trained
+    assert fvus[-1] < fvus[0] - drop  # it trained
 
 
 def test_signum_trajectory_matches_reference_trainer(cuda_lib, tmp_path):
