@@ -118,3 +118,31 @@ def test_load_many_layers_and_pattern(tmp_path):
     assert SparseCoder.load_many(str(tmp_path), local=True, pattern="layers.1*") == {}
     with pytest.raises(NotImplementedError):
         SparseCoder.load_many("someone/some-repo")
+
+
+def test_schedulefree_signum_modes_and_state_on_host():
+    """train()/eval() convert between the gradient point y and the average x through z and
+    invert each other; stepping outside training mode is refused; the state dict carries z
+    and the schedule-free counters (host-side logic of sparsify/trainer.py:158-159,652-677)."""
+    from sparsify_b200.optim import ScheduleFreeSignum
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(5, 4))
+    opt = ScheduleFreeSignum([p], lr=1e-2, momentum=0.95)
+    with pytest.raises(RuntimeError, match="train"):
+        p.grad = torch.zeros_like(p)
+        opt.step()
+    opt.train()
+    y = p.detach().clone()
+    z = torch.randn(5, 4)
+    opt.state[p]["z"] = z.clone()
+    opt.eval()
+    x = p.detach().clone()
+    assert torch.allclose(x, torch.lerp(y, z, 1 - 1 / 0.95), atol=1e-6)
+    opt.train()
+    assert torch.allclose(p.detach(), y, atol=1e-5)
+    sd = opt.state_dict()
+    assert sd["param_groups"][0]["train_mode"] is True and sd["param_groups"][0]["k"] == 0
+    opt2 = ScheduleFreeSignum([torch.nn.Parameter(torch.zeros(5, 4))], lr=1.0)
+    opt2.load_state_dict(sd)
+    assert opt2.param_groups[0]["momentum"] == 0.95 and opt2.param_groups[0]["lr"] == 1e-2
+    assert torch.equal(next(iter(opt2.state.values()))["z"], z)
