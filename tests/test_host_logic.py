@@ -146,3 +146,19 @@ def test_schedulefree_signum_modes_and_state_on_host():
     opt2.load_state_dict(sd)
     assert opt2.param_groups[0]["momentum"] == 0.95 and opt2.param_groups[0]["lr"] == 1e-2
     assert torch.equal(next(iter(opt2.state.values()))["z"], z)
+
+
+def test_prepared_dead_mask_is_used_by_identity():
+    """A mask prepared ahead of time answers count and indices from the cache - for that
+    tensor object only; any other mask is counted afresh."""
+    sae = SparseCoder(16, SparseCoderConfig(num_latents=64, k=4), device="cpu")
+    mask = torch.zeros(64, dtype=torch.bool)
+    mask[[3, 10, 40]] = True
+    assert sae.prepare_dead_mask(mask) is mask
+    assert sae._count_dead(mask) == 3 and sae.dead_indices(mask).tolist() == [3, 10, 40]
+    other = mask.clone()
+    other[5] = True
+    assert sae._count_dead(other) == 4 and sae.dead_indices(other).tolist() == [3, 5, 10, 40]
+    assert sae._count_dead(None) == 0
+    sae.prepare_dead_mask(None)
+    assert sae._count_dead(mask) == 3
