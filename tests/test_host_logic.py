@@ -2,6 +2,7 @@
 module plan, learning-rate schedule, checkpoint layout of a CPU-resident coder."""
 
 import json
+import os
 
 import pytest
 import torch
@@ -162,3 +163,26 @@ def test_prepared_dead_mask_is_used_by_identity():
     assert sae._count_dead(None) == 0
     sae.prepare_dead_mask(None)
     assert sae._count_dead(mask) == 3
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` (the CPU arm: the oracle port on the host cores) prints one
+    JSON line with the metric, the workload and the cpu_baseline / e2e objects; a rank other
+    than 0 of a multi-process launch exits without work."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+           "--d", "64", "--latents", "512", "--k", "4", "--cpu-tokens", "64", "--atoms", "1024", "--active", "8"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "sae_train_tokens_per_s"
+    assert line["unit"] == "tokens/s" and line["higher_is_better"] is True and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
+    assert "workload" in line["config"]
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    out = subprocess.run(cmd + ["--gpus", "2"], capture_output=True, text=True, timeout=300, cwd=root, env=env)
+    assert out.returncode == 0 and out.stdout.strip() == ""
