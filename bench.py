@@ -280,6 +280,10 @@ def run_ours(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if a.gpus != world:
+        print(f"bench.py: --gpus {a.gpus} but the launcher started {world} process(es); "
+              f"launch with python -m torch.distributed.run --nproc-per-node {a.gpus} for {a.gpus} GPUs",
+              file=sys.stderr, flush=True)
     N, D, M, k = a.tokens, a.d, a.latents, a.k
     ops.set_reserved_sms(max(a.reserve_sms, 0) if world > 1 else 0)
     torch.manual_seed(0)  # identical replicas on every rank (sparsify/trainer.py:80-87)
