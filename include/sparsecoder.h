@@ -55,6 +55,15 @@ int sc_set_reserved_sms(int n);
 size_t sc_last_error(char* buf, size_t cap);
 const char* sc_status_string(int status);
 
+/* Self-test of the bounded device-side wait shared by the tensor-core kernels:
+ * a one-thread kernel waits for limit_ns (at most 100 ms) on a barrier that
+ * nothing arrives on, gives up, stores its wait code (199) in *status_word and
+ * returns. The context stays usable; a host that reads a non-zero status word
+ * after any entry point that takes one must treat the outputs of that call as
+ * invalid (SC_ERR_TIMEOUT). No counterpart in the reference (it has no device
+ * code of its own). */
+int sc_selftest_wait_timeout(int32_t* status_word, int64_t limit_ns, void* stream);
+
 /* ---- encoder forward ---------------------------------------------------
  * sparsify/fused_encoder.py:19-50 (FusedEncoder.forward):
  *   preacts = relu(x @ W^T + b); top-k (or groupmax) per row.
@@ -98,8 +107,10 @@ int sc_groupmax_rows(const float* pre, int64_t N, int64_t M, int k,
  * N x M matrix never reaches HBM; then a merge picks the final k per row.
  * Requirements: D % 8 == 0 (16-byte rows), k <= 128, M >= k.
  * ws must hold sc_encode_topk_workspace_bytes(N, D, M, k) bytes, 256-aligned.
- * status_word (device int32, may be NULL) receives a non-zero code if a
- * bounded wait inside the kernel gave up.
+ * status_word (device int32, may be NULL; the caller zeroes it) receives a
+ * non-zero code if a bounded wait inside the kernel gave up; a word that is
+ * already non-zero is left alone, so one word can collect over many calls and
+ * be read once where the host synchronises anyway.
  * sparsify/fused_encoder.py:29-33. */
 size_t sc_encode_topk_workspace_bytes(int64_t N, int64_t D, int64_t M, int k);
 int sc_encode_topk(const void* x_bf16, const void* W_bf16, const float* bias,

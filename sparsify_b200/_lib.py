@@ -15,6 +15,7 @@ import torch
 LIB_PATH = Path(__file__).resolve().parent / "libsparsecoder.so"
 
 SC_OK = 0
+SC_ERR_TIMEOUT = 5
 SC_F32, SC_BF16 = 0, 1
 STATUS_NAMES = {
     0: "SC_OK",
@@ -35,6 +36,7 @@ SIGNATURES: dict[str, tuple] = {
     "sc_set_reserved_sms": (c_int, [c_int]),
     "sc_last_error": (c_size_t, [c_char_p, c_size_t]),
     "sc_status_string": (c_char_p, [c_int]),
+    "sc_selftest_wait_timeout": (c_int, [P, I64, P]),
     "sc_prep_input": (c_int, [P, c_int, P, I64, I64, P, c_int, P]),
     "sc_preacts_dense": (c_int, [P, c_int, P, c_int, P, I64, I64, I64, P, c_int, P]),
     "sc_topk_rows": (c_int, [P, I64, I64, c_int, P, P, P, P]),

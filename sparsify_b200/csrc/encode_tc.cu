@@ -60,7 +60,9 @@ struct Params {
   int group_cols;
   float* gm_vals;
   int64_t* gm_idx;
-  int debug;  // diagnostics: bit 0 = epilogue only drains (no bias / top-k work)
+#ifdef SC_DIAG
+  int debug;  // diagnostics build only: bit 0 = epilogue only drains (no bias / top-k work)
+#endif
   uint32_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
 
@@ -176,10 +178,9 @@ __device__ __noinline__ RowState list_insert(float* lv, uint16_t* li, float* gv,
   return replace_min<16>(lv, li, gv, gp, k, groups, v, rel_col, tau, st);
 }
 
-__global__ void init_tau_kernel(float* tau, int64_t n, int32_t* status) {
+__global__ void init_tau_kernel(float* tau, int64_t n) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i < n) tau[i] = -1.f;
-  if (i == 0 && status != nullptr) *status = 0;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -249,21 +250,31 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       int buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      long long wait_tmem = 0, wait_full = 0;  // diagnostics (debug bit 2)
+#ifdef SC_DIAG
+      long long wait_tmem = 0, wait_full = 0;  // debug bit 2
       const long long t_begin = clock64();
+#endif
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
         int rb, strip, t0, t1;
         decode_unit(p, u, rb, strip, t0, t1);
         for (int t = t0; t < t1 && ok; ++t) {
+#ifdef SC_DIAG
           const long long w0 = clock64();
+#endif
           if (!mbar_wait(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+#ifdef SC_DIAG
           wait_tmem += clock64() - w0;
+#endif
           fence_after_sync();
           const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
           for (int kc = 0; kc < kc_count; ++kc) {
+#ifdef SC_DIAG
             const long long w1 = clock64();
+#endif
             if (!mbar_wait(&full[stage], phase, p.status, kWaitFull)) { ok = false; break; }
+#ifdef SC_DIAG
             wait_full += clock64() - w1;
+#endif
             fence_after_sync();
             const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
             const uint64_t adesc = make_smem_desc_sw128(sa);
@@ -283,12 +294,14 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           if (buf == 0) acc_phase ^= 1;
         }
       }
+#ifdef SC_DIAG
       if ((p.debug & 4) && p.status != nullptr && blockIdx.x == 0) {
         // kilo-cycles of SM 0's MMA thread: total, waiting for a free accumulator, waiting for operands
         p.status[3] = (int)((clock64() - t_begin) >> 10);
         p.status[4] = (int)(wait_tmem >> 10);
         p.status[5] = (int)(wait_full >> 10);
       }
+#endif
     }
   } else {
     // ---------------- epilogue: bias + ReLU + running top-k ----------------
@@ -311,7 +324,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       RowState st;
       st.thr = -1.f; st.minpos = 0; st.cnt = 0;
       float published = -1.f;  // last bound this thread pushed to p.tau
-      unsigned n_ins = 0, n_cols = 0;  // diagnostics (debug bit 1)
+#ifdef SC_DIAG
+      unsigned n_ins = 0, n_cols = 0;  // debug bit 1
+#endif
       // rows past N are padding: an infinite bound keeps them out of the lists
       float tau = (grow < p.N && p.group_cols == 0) ? __ldcg(p.tau + grow) : INFINITY;
       // Threshold the raw (pre-ReLU) value is compared with: max(thr, tau), or
@@ -340,8 +355,13 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         const int64_t tile_col0 = (int64_t)t * BN;
         const int ncols = (int)min((int64_t)BN, p.M - tile_col0);
         const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(q * 32) << 16);
+#ifdef SC_DIAG
+        const int n_chunks = (p.debug & 1) ? 0 : BN / 32;
+#else
+        constexpr int n_chunks = BN / 32;
+#endif
 #pragma unroll 1
-        for (int c = 0; c < ((p.debug & 1) ? 0 : BN / 32); ++c) {
+        for (int c = 0; c < n_chunks; ++c) {
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
@@ -387,7 +407,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           // runs as often as the busiest row has candidates, not once per marked column.
           const uint16_t rel0 = (uint16_t)(tile_col0 - strip_col0 + c * 32);
           while (__any_sync(0xffffffffu, m != 0)) {
+#ifdef SC_DIAG
             ++n_cols;
+#endif
             if (m != 0) {
               const int i = __ffs(m) - 1;
               m &= m - 1;
@@ -400,7 +422,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                 } else {
                   st = list_insert(lv, li, gv, gp, k, val, (uint16_t)(rel0 + i), tau, st);
                 }
+#ifdef SC_DIAG
                 ++n_ins;
+#endif
               }
             }
           }
@@ -424,10 +448,12 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         if (buf == 0) acc_phase ^= 1;
       }
       if (!ok) break;
+#ifdef SC_DIAG
       if ((p.debug & 2) && p.status != nullptr) {  // status[1] = insertions, status[2] = visited columns
         atomicAdd(p.status + 1, (int)n_ins);
         if (lane == 0) atomicAdd(p.status + 2, (int)n_cols);
       }
+#endif
       // write this strip's candidates and publish the row's lower bound
       if (grow < p.N && p.group_cols == 0) {
         float* cv = p.cand_vals + (grow * p.n_strips + strip) * k;
@@ -585,10 +611,14 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   Params p;
   p.bias = bias; p.cand_vals = cand_vals; p.cand_idx = cand_idx; p.tau = tau; p.status = status_word;
   p.N = N; p.D = D; p.M = M; p.k = k;
+  p.row_group = kRowGroupDefault;
+#ifdef SC_DIAG
+  // diagnostics build (-DSC_DIAG) only: the shipped library reads no environment
   const char* dbg = getenv("SC_ENCODE_DEBUG");
   p.debug = dbg ? atoi(dbg) : 0;
   const char* rg_env = getenv("SC_ENCODE_ROWGROUP");
-  p.row_group = rg_env && atoi(rg_env) > 0 ? atoi(rg_env) : kRowGroupDefault;
+  if (rg_env && atoi(rg_env) > 0) p.row_group = atoi(rg_env);
+#endif
   p.group_cols = 0; p.gm_vals = nullptr; p.gm_idx = nullptr;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
   p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
@@ -596,7 +626,7 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   p.off_bias = (uint32_t)pl.off_bias; p.off_bars = (uint32_t)pl.off_bars;
 
   cudaStream_t st = sc::as_stream(stream);
-  init_tau_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(tau, N, status_word);
+  init_tau_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(tau, N);
   SC_CHECK_LAUNCH("init_tau");
   SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
   int sms = 148;
@@ -639,7 +669,9 @@ extern "C" int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const 
   Params p;
   p.bias = bias; p.cand_vals = nullptr; p.cand_idx = nullptr; p.tau = nullptr; p.status = status_word;
   p.N = N; p.D = D; p.M = M; p.k = k;
+#ifdef SC_DIAG
   p.debug = 0;
+#endif
   p.row_group = kRowGroupDefault;
   p.group_cols = (int)g; p.gm_vals = top_vals; p.gm_idx = top_idx;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;

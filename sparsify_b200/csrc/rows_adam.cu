@@ -54,6 +54,12 @@ struct Args {
   Hp hpA, hpB;
 };
 
+// Asks L2 to fetch `bytes` (a multiple of 16, 16-byte aligned) starting at p; no
+// register or shared-memory destination, nothing to wait for.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // sum over the CSR segment [lo, hi) of coef[e] * vec[e / k, cols of this thread]
 template <typename T, int kNV>
 __device__ __forceinline__ void gather_rows(const int32_t* __restrict__ entries, int32_t lo, int32_t hi, int k,
@@ -88,8 +94,18 @@ rows_adam_kernel(const TA* __restrict__ vecA, const TB* __restrict__ vecB, const
   const bool doA = (a.parts & 1) != 0, doB = (a.parts & 2) != 0;
   // one CTA per latent, or (grid smaller than M) a persistent CTA striding over the latents
   for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
-    const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
     const int64_t off = m * D;
+#ifndef SC_NO_L2_PREFETCH
+    // The parameter and moment rows are needed only after the gather below, whose loads
+    // depend on one another (row_ptr -> entries -> rows): start them towards L2 now, so
+    // that the three 4*D-byte streams travel while the gather waits for its own data.
+    if (threadIdx.x < 6) {
+      const int t = threadIdx.x;
+      const float* row = t == 0 ? a.pB : t == 1 ? a.mB : t == 2 ? a.vB : t == 3 ? a.pA : t == 4 ? a.mA : a.vA;
+      if (t < 3 ? doB : doA) prefetch_l2(row + off, (uint32_t)(D * sizeof(float)));
+    }
+#endif
+    const int32_t lo = a.row_ptr[m], hi = a.row_ptr[m + 1];
     float4 g[kNV];
 
     if (doB) {  // ---- encoder row: Adam ----

@@ -69,14 +69,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // false; the caller must then leave its loop and fall through to the teardown.
 constexpr uint64_t kWaitLimitNs = 4000000000ull;
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status, int32_t code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status, int32_t code,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   for (int i = 0; i < 2048; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (global_timer_ns() - t0 > limit_ns) {
       if (status != nullptr) atomicCAS(status, 0, code);
       return false;
     }

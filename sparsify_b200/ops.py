@@ -27,6 +27,24 @@ def _timed(name: str, device):
     return e
 
 
+class span:
+    """Context manager: when `timers` is set, brackets the enclosed work on the current stream
+    of `device` with a CUDA-event pair filed under `name` (e.g. how long the compute stream
+    waits for an exchange that should have finished in the background)."""
+
+    def __init__(self, name: str, device):
+        self.name, self.device, self.end = name, device, None
+
+    def __enter__(self):
+        self.end = _timed(self.name, self.device)
+        return self
+
+    def __exit__(self, *exc):
+        if self.end is not None:
+            self.end.record(torch.cuda.current_stream(self.device))
+        return False
+
+
 def _stream(t: Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -34,6 +52,46 @@ def _stream(t: Tensor):
 def _ws(nbytes: int, device) -> Tensor:
     # torch's caching allocator returns 512-byte aligned blocks
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# One status word per device, shared by every kernel that has bounded waits (the
+# tensor-core encoder and GEMM). A wait that gives up stores its code there and
+# the word keeps the first code until check_status() reads and clears it.
+_status_words: dict[int, Tensor] = {}
+
+
+def status_word(device) -> Tensor:
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(index)
+    if word is None:
+        word = _status_words[index] = torch.zeros(8, dtype=torch.int32, device=torch.device("cuda", index))
+    return word
+
+
+def check_status(device=None) -> None:
+    """Raises SparseCoderLibError(SC_ERR_TIMEOUT) if a bounded device-side wait of a
+    tensor-core kernel gave up since the last check (its outputs are then invalid).
+    Reads one word back, i.e. synchronises: call it where the host waits for the
+    device anyway (the Trainer does so once per step, with its metric reads)."""
+    words = [status_word(device)] if device is not None else list(_status_words.values())
+    for word in words:
+        code = int(word[0].item())
+        if code != 0:
+            word.zero_()
+            raise _lib.SparseCoderLibError(
+                "device wait", _lib.SC_ERR_TIMEOUT,
+                f"a bounded wait inside a tensor-core kernel on {word.device} gave up (wait code {code}); "
+                "the results of the calls since the last check are invalid")
+
+
+def selftest_wait_timeout(device, limit_ms: float = 2.0) -> None:
+    """Launches the library's wait self-test: a kernel whose only wait can never be
+    satisfied and runs out after limit_ms. check_status() must raise afterwards."""
+    word = status_word(device)
+    with torch.cuda.device(word.device):
+        call("sc_selftest_wait_timeout", ptr(word), int(limit_ms * 1e6),
+             torch.cuda.current_stream(word.device).cuda_stream)
 
 
 def _check_cuda(*ts: Tensor | None):
@@ -135,7 +193,7 @@ def encode_topk_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> tupl
     idx = torch.empty(N, k, dtype=torch.int64, device=dev)
     nbytes = _lib.lib().sc_encode_topk_workspace_bytes(N, D, M, int(k))
     ws = _ws(nbytes, dev)
-    status = torch.zeros(8, dtype=torch.int32, device=dev)  # [0] wait-timeout code, [1:] diagnostics
+    status = status_word(dev)  # [0] wait-timeout code (sticky), [1:] diagnostics builds only
     bias32 = _f32(bias)
     with torch.cuda.device(dev):
         end = _timed("encode_topk", dev)
@@ -165,7 +223,7 @@ def encode_groupmax_tc(x_bf16: Tensor, W_bf16: Tensor, bias: Tensor, k: int) -> 
     dev = x_bf16.device
     vals = torch.empty(N, k, dtype=torch.float32, device=dev)
     idx = torch.empty(N, k, dtype=torch.int64, device=dev)
-    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    status = status_word(dev)
     bias32 = _f32(bias)
     with torch.cuda.device(dev):
         call("sc_encode_groupmax", ptr(x_bf16), ptr(W_bf16), ptr(bias32), N, D, M, int(k),
@@ -489,7 +547,7 @@ def gemm_nt(A: Tensor, B: Tensor, *, alpha: float = 1.0, beta: float = 0.0, Cin:
     if out_t is not None:
         assert out_t.shape == (N, M) and out_t.is_contiguous() and out_t.dtype == out.dtype
     bias32 = _f32(bias)
-    status = torch.zeros(8, dtype=torch.int32, device=A.device)
+    status = status_word(A.device)
     with torch.cuda.device(A.device):
         call("sc_gemm_bf16_nt", ptr(A), ptr(B), M, N, K, float(alpha), float(beta), ptr(Cin),
              dtype_code(Cin) if Cin is not None else 0, ptr(bias32), int(bool(relu)), ptr(out),

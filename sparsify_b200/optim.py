@@ -248,13 +248,17 @@ class FusedAdam(torch.optim.Optimizer):
                     return out
             return gather(t)
 
-        vecB_all = take("vecB", vecB)   # same order on every rank: issued first, waited first
-        vecA_all = take("vecA", vecA)
-        idx_all, coefA_all, coefB_all = gather(idx), gather(coefA), gather(coefB)
+        dev = idx.device
+        with ops.span("x_wait_rows", dev):
+            vecB_all = take("vecB", vecB)   # same order on every rank: issued first, waited first
+            vecA_all = take("vecA", vecA)
+        with ops.span("x_gather_factors", dev):
+            idx_all, coefA_all, coefB_all = gather(idx), gather(coefA), gather(coefB)
         per = sae.encoder.weight.shape[0] // world
-        # indices relative to this rank's slice; the CSR build skips the ones outside [0, per)
-        local = idx_all.to(torch.int64) - rank * per
-        row_ptr, entries = ops.csr_build(local, per)
+        with ops.span("x_csr_slice", dev):
+            # indices relative to this rank's slice; the CSR build skips the ones outside [0, per)
+            local = idx_all.to(torch.int64) - rank * per
+            row_ptr, entries = ops.csr_build(local, per)
         return dict(row_ptr=row_ptr, entries=entries, k=k, coefA=coefA_all, vecA=vecA_all, coefB=coefB_all,
                     vecB=vecB_all, extra=pend.get("extra"))
 

@@ -359,7 +359,8 @@ class SparseCoder(nn.Module):
         copy that a sharded update left in flight."""
         work, self._enc_work = getattr(self, "_enc_work", None), None
         if work is not None:
-            work.wait()
+            with ops.span("x_wait_encoder_copy", self.device):
+                work.wait()
             self._enc_work_src = None
 
     def wait_decoder(self) -> None:
@@ -372,7 +373,8 @@ class SparseCoder(nn.Module):
             torch.cuda.current_stream(self.device).wait_event(event)
         work, self._dec_work = self._dec_work, None
         if work is not None:
-            work.wait()  # asynchronous all-gather of the decoder's bf16 copy (sharded update)
+            with ops.span("x_wait_decoder_copy", self.device):
+                work.wait()  # asynchronous all-gather of the decoder's bf16 copy (sharded update)
 
     def materialize_pending(self) -> None:
         """Turns a deferred sparse weight gradient into dense .grad tensors

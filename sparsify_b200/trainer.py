@@ -52,6 +52,25 @@ def linear_schedule_with_warmup(optimizer, num_warmup_steps: int, num_training_s
     return torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda)
 
 
+def sparse_update_allowed(cfg: TrainConfig, world_size: int) -> bool:
+    """Whether the optimiser may consume the weight gradients in sparse form (and, on several
+    data-parallel ranks, shard the update over them).
+
+    Needs: nothing else wants the dense gradients (no accumulation, the plain FVU objective).
+    On several data-parallel ranks the sharded update also assumes that every rank holds the
+    same set of dead latents, because their AuxK gradient rows are summed with a collective
+    whose shape is that set. The dead-latent counters advance by each rank's own unmasked
+    token count (sparsify/trainer.py:471-472,529-538), which `exclude_tokens` makes differ
+    between ranks: with AuxK enabled the sets can then diverge, so that combination keeps the
+    dense gradients, whose all-reduce has a fixed shape (as DistributedDataParallel's has)."""
+    if cfg.grad_acc_steps * cfg.micro_acc_steps != 1 or cfg.loss_fn != "fvu":
+        return False
+    data_parallel = world_size > 1 and not cfg.distribute_modules
+    if data_parallel and cfg.exclude_tokens and cfg.auxk_alpha > 0:
+        return False
+    return True
+
+
 class Trainer:
     def __init__(self, cfg: TrainConfig, dataset, model: nn.Module):
         self.model = model
@@ -106,7 +125,7 @@ class Trainer:
                 lrs = [f"{lr:.2e}" for lr in sorted(set(pg["lr"] for pg in pgs))]
                 adam = FusedAdam(pgs)
                 # (end-to-end losses reach the weights through sae_out: dense gradients)
-                no_acc = cfg.grad_acc_steps * cfg.micro_acc_steps == 1 and cfg.loss_fn == "fvu"
+                no_acc = sparse_update_allowed(cfg, dist.get_world_size() if dist.is_initialized() else 1)
                 for sae in self.saes.values():
                     sae.attach_optimizer(adam)
                     sae.ragged_tokens = bool(cfg.exclude_tokens)
@@ -402,6 +421,11 @@ class Trainer:
                     avg_multi_topk_fvu[name] += float(self.maybe_all_reduce(multi) / denom)
             pending_metrics.clear()
             avg_losses = avg_e2e if e2e else dict(avg_fvu)
+            if torch.device(device).type == "cuda":
+                # the reads above waited for the device: the cheapest place to learn that a
+                # bounded wait inside a tensor-core kernel gave up (its results are garbage)
+                from . import ops
+                ops.check_status(device)
 
             if substep == 0:
                 if reducer is not None:

@@ -5,10 +5,10 @@ with seeded inputs. Run once where the reference tree is available:
     SPARSIFY_REF=/path/to/sparsify python tests/golden/make_golden.py
 
 The reference's non-arithmetic dependencies that are not installed here
-(natsort, simple_parsing, accelerate) are replaced by small stub modules that
-take no part in the arithmetic that is frozen; schedulefree's wrapper class,
-which only the optimizer="signum" fixture uses, is replaced by the oracle's
-restatement of its published algorithm. The fixtures
+(natsort, simple_parsing, accelerate) are replaced by small stand-in modules
+(oracle/ref_loader.py) that take no part in the arithmetic that is frozen;
+schedulefree's wrapper class, which only the optimizer="signum" fixture uses, is
+replaced by the oracle's restatement of its published algorithm. The fixtures
 are what the oracle (oracle/sae_oracle.py) is pinned against.
 """
 
@@ -29,58 +29,17 @@ HERE = Path(__file__).resolve().parent
 
 
 def import_reference():
-    root = os.environ.get("SPARSIFY_REF", "")
-    if not root or not Path(root, "sparsify", "fused_encoder.py").exists():
-        raise SystemExit("set SPARSIFY_REF to a checkout of EleutherAI/sparsify v1.3.0")
-    os.environ["SPARSIFY_DISABLE_TRITON"] = "1"
-    import transformers  # noqa: F401  (must precede the accelerate stub)
-
-    def natsorted(seq, key=None):
-        def split(s):
-            return [int(t) if t.isdigit() else t for t in re.split(r"(\d+)", str(s))]
-        return sorted(seq, key=(lambda v: split(key(v))) if key else split)
-
-    natsort = types.ModuleType("natsort")
-    natsort.natsorted = natsorted
-
-    class Serializable:
-        def to_dict(self):
-            return dataclasses.asdict(self)
-
-        @classmethod
-        def from_dict(cls, d, drop_extra_fields=False):
-            names = {f.name for f in dataclasses.fields(cls)}
-            return cls(**{k: v for k, v in d.items() if k in names})
-
-        def save_json(self, path):
-            with open(path, "w") as f:
-                json.dump(self.to_dict(), f)
-
-    sp = types.ModuleType("simple_parsing")
-    sp.Serializable = Serializable
-    sp.list_field = lambda *d: dataclasses.field(default_factory=lambda: list(d))
-    sp.field = dataclasses.field
-    sp.parse = lambda *a, **k: None
-
-    acc = types.ModuleType("accelerate")
-    acc_utils = types.ModuleType("accelerate.utils")
-    acc_utils.send_to_device = lambda obj, device: obj
-    acc.utils = acc_utils
-
-    # schedulefree is not installed: its wrapper is replaced by the oracle's restatement of the
-    # published algorithm (only the optimizer="signum" fixture depends on it; that fixture pins
-    # SignSGD, the learning-rate rule and the Trainer's glue, not the wrapper itself)
+    """The unmodified reference, imported through oracle/ref_loader.py (which documents the
+    stand-ins for its four absent non-arithmetic dependencies). schedulefree's wrapper, which
+    only the optimizer="signum" fixture uses, is the oracle's restatement of the published
+    algorithm: that fixture pins SignSGD, the learning-rate rule and the Trainer's glue, not
+    the wrapper itself."""
     sys.path.insert(0, str(HERE.parent.parent))
+    from oracle import ref_loader
     from oracle.sae_oracle import ScheduleFreeWrapperPort
-    sf = types.ModuleType("schedulefree")
-    sf.ScheduleFreeWrapper = ScheduleFreeWrapperPort
-
-    for name, mod in [("natsort", natsort), ("simple_parsing", sp), ("accelerate", acc),
-                      ("accelerate.utils", acc_utils), ("schedulefree", sf)]:
-        sys.modules.setdefault(name, mod)
-    sys.path.insert(0, root)
-    import sparsify  # noqa: F401
-    return sparsify
+    if ref_loader.find_reference() is None:
+        raise SystemExit("set SPARSIFY_REF to a checkout of EleutherAI/sparsify v1.3.0 (or run oracle/make_ref.py)")
+    return ref_loader.import_reference(schedulefree_wrapper=ScheduleFreeWrapperPort)
 
 
 def save(name: str, tensors: dict, meta: dict | None = None):

@@ -166,23 +166,44 @@ def test_prepared_dead_mask_is_used_by_identity():
 
 
 def test_bench_reference_arm_prints_the_contract_line():
-    """`bench.py --impl reference` (the CPU arm: the oracle port on the host cores) prints one
-    JSON line with the metric, the workload and the cpu_baseline / e2e objects; a rank other
-    than 0 of a multi-process launch exits without work."""
+    """`bench.py --impl reference` (the CPU arm: the vendored reference's own Trainer.fit() on
+    the host cores, or the oracle port where the reference is absent) prints one JSON line
+    with the metric, the workload and the cpu_baseline / e2e objects, on every host thread even
+    under a launcher that exports OMP_NUM_THREADS=1; a rank other than 0 of a multi-process
+    launch exits without work."""
     import subprocess
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parent.parent
     cmd = [sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
-           "--d", "64", "--latents", "512", "--k", "4", "--cpu-tokens", "64", "--atoms", "1024", "--active", "8"]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
+           "--d", "64", "--latents", "512", "--k", "4", "--cpu-tokens", "64", "--atoms", "1024", "--active", "8",
+           "--config0-steps", "0"]
+    env1 = dict(os.environ, OMP_NUM_THREADS="1")  # what torch.distributed.run exports to its workers
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root, env=env1)
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["metric"] == "sae_train_tokens_per_s"
     assert line["unit"] == "tokens/s" and line["higher_is_better"] is True and line["value"] > 0
-    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    from oracle import ref_loader
+    assert line["cpu_baseline"]["kind"] == ("reference" if ref_loader.find_reference() is not None else "port")
+    assert line["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
     assert "workload" in line["config"]
     env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
     out = subprocess.run(cmd + ["--gpus", "2"], capture_output=True, text=True, timeout=300, cwd=root, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_sparse_update_is_refused_where_dead_sets_can_diverge():
+    """Data parallel + excluded tokens + AuxK: each rank's dead-latent counters advance by its own
+    unmasked token count, so the dead sets (the shape of a collective in the sharded update) may
+    differ between ranks; that combination must keep the dense, fixed-shape gradient exchange."""
+    from sparsify_b200.trainer import sparse_update_allowed
+    mk = lambda **kw: TrainConfig(SparseCoderConfig(num_latents=64, k=4), **kw)
+    assert sparse_update_allowed(mk(), 1) and sparse_update_allowed(mk(), 8)
+    assert sparse_update_allowed(mk(exclude_tokens=[0], auxk_alpha=1 / 32), 1)
+    assert sparse_update_allowed(mk(exclude_tokens=[0], auxk_alpha=0.0), 8)
+    assert not sparse_update_allowed(mk(exclude_tokens=[0], auxk_alpha=1 / 32), 8)
+    assert sparse_update_allowed(mk(exclude_tokens=[0], auxk_alpha=1 / 32, distribute_modules=True), 8)
+    assert not sparse_update_allowed(mk(grad_acc_steps=2), 1)
+    assert not sparse_update_allowed(mk(loss_fn="ce"), 1)

@@ -110,8 +110,10 @@ def test_forward_backward_bf16_vs_oracle(cuda_lib):
     ref = O.sae_forward_backward(params, x, cfg=O.OracleCfg(k=k), round_operands=rnd)
     acts, idx = sort_topk(out.latent_acts.detach().cpu(), out.latent_indices.cpu())
     racts, ridx = sort_topk(ref.latent_acts, ref.latent_indices)
-    agree = (idx == ridx).float().mean()
-    assert agree > 0.999, float(agree)
+    # index sets identical except where the k-th and (k+1)-th pre-activations are within 1e-3 (relative)
+    from tests.test_kernels_gpu import check_topk_sets
+    pre = O.preacts(rnd(x - params["b_dec"]).double(), rnd(params["W_enc"]).double(), params["b_enc"].double()).float()
+    check_topk_sets(out.latent_acts.detach(), out.latent_indices, pre, k)
     assert rel_l2(acts, racts) < 1e-3
     assert rel_l2(out.sae_out.detach(), ref.sae_out) < 1e-3
     assert abs(float(out.fvu) - float(ref.fvu)) < 1e-3 * float(ref.fvu)
