@@ -51,6 +51,11 @@ int sc_version(void);
  * (0 <= n <= 64), e.g. for the kernels of a communication library that should
  * run concurrently. Process-wide; set it before sizing workspaces. */
 int sc_set_reserved_sms(int n);
+/* The tensor-core encoder (sc_encode_topk, sc_encode_groupmax) runs by default as
+ * pairs of CTAs on the two SMs of a TPC (tcgen05 cta_group::2: one 256-row tile
+ * per pair, each CTA loading its own operands); on = 0 selects the one-CTA form.
+ * Process-wide; set it before sizing workspaces. Results are identical. */
+int sc_set_cta_pairs(int on);
 /* Copies the last error message (NUL-terminated) into buf; returns its length. */
 size_t sc_last_error(char* buf, size_t cap);
 const char* sc_status_string(int status);

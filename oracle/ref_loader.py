@@ -152,7 +152,7 @@ def time_reference_trainer(acts: torch.Tensor, *, num_latents: int, k: int, warm
     backward, decoder normalisation and projection, torch.optim.Adam, schedule, dead-latent
     bookkeeping) on the host over acts [steps, B, T, D] (fp32) and returns the seconds of
     every step after the first `warmup_steps`, measured between consecutive step starts and
-    the end of fit() (the final checkpoint is written outside the last interval)."""
+    the end of the last step (the checkpoint fit() would write afterwards is skipped)."""
     sparsify = import_reference()
     from sparsify import SparseCoderConfig, TrainConfig, Trainer
     if threads:
@@ -166,8 +166,9 @@ def time_reference_trainer(acts: torch.Tensor, *, num_latents: int, k: int, warm
                           run_name="timed", save_every=10 ** 9)
         trainer = Trainer(cfg, dataset, model)
         done = []
-        orig_save = trainer.save
-        trainer.save = lambda: (done.append(time.perf_counter()), orig_save())[1]
+        # fit() ends by writing a checkpoint (weights and optimiser state: gigabytes at full width);
+        # that write is not part of a step, so this instance records the time instead of saving
+        trainer.save = lambda: done.append(time.perf_counter())
         trainer.fit()
     stamps = model.stamps + done[:1]
     per_step = [b - a for a, b in zip(stamps[:-1], stamps[1:])]

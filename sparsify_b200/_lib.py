@@ -34,6 +34,7 @@ I64 = c_int64
 SIGNATURES: dict[str, tuple] = {
     "sc_version": (c_int, []),
     "sc_set_reserved_sms": (c_int, [c_int]),
+    "sc_set_cta_pairs": (c_int, [c_int]),
     "sc_last_error": (c_size_t, [c_char_p, c_size_t]),
     "sc_status_string": (c_char_p, [c_int]),
     "sc_selftest_wait_timeout": (c_int, [P, I64, P]),

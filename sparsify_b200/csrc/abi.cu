@@ -14,10 +14,12 @@ char g_err[512] = "";
 
 namespace {
 std::atomic<int> g_reserved_sms{0};
+std::atomic<int> g_cta_pairs{1};
 }  // namespace
 
 namespace sc {
 int reserved_sms() { return g_reserved_sms.load(std::memory_order_relaxed); }
+bool cta_pairs() { return g_cta_pairs.load(std::memory_order_relaxed) != 0; }
 
 int fail(int status, const char* fmt, ...) {
   std::lock_guard<std::mutex> lock(g_err_mutex);
@@ -34,6 +36,11 @@ extern "C" int sc_version(void) { return 100; }
 extern "C" int sc_set_reserved_sms(int n) {
   SC_REQUIRE(n >= 0 && n <= 64, "sc_set_reserved_sms: %d outside [0, 64]", n);
   g_reserved_sms.store(n, std::memory_order_relaxed);
+  return SC_OK;
+}
+
+extern "C" int sc_set_cta_pairs(int on) {
+  g_cta_pairs.store(on != 0, std::memory_order_relaxed);
   return SC_OK;
 }
 

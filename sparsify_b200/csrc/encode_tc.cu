@@ -11,6 +11,12 @@
 // matrix never reaches HBM. Each (row, strip) emits k candidates; a second
 // kernel merges the strips of a row into the final k.
 //
+// By default two CTAs on the SMs of one TPC work as a pair (tcgen05 cta_group::2)
+// on a 256-token row block: each loads its own 128 rows of x and its own half of
+// the W tile with its own TMA loads, the even CTA issues 256x256x16 MMAs for
+// both, and each drains its own 128 accumulator rows. An SM then reads 8 KB of
+// shared memory per MMA instead of 12 KB, which is what bounds the one-CTA form.
+//
 // A per-row lower bound on the k-th largest value (`tau`) is published after
 // every finished strip and read at the start of later strips of the same rows:
 // values not above it cannot be among the row's top k, which removes most list
@@ -28,12 +34,15 @@ constexpr int BN = 256;   // latents per tile (TMEM columns per accumulator)
 constexpr int BK = 64;    // bf16 per 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr uint32_t kStageBytes = (BM + BN) * BK * 2;  // 48 KiB
+// bytes one CTA stages per k-chunk: its 128 rows of x plus its share of the W tile (all 256
+// rows alone, 128 as one of a pair)
+constexpr uint32_t stage_bytes(int cg) { return (uint32_t)(BM + BN / cg) * BK * 2; }  // 48 / 32 KiB
 constexpr int kMaxK = 128;
-constexpr int kRowGroupDefault = 32;  // row blocks whose units run together (L2 footprint of x)
+constexpr int kRowGroupRows = 4096;  // rows whose units run together (L2 footprint of x: 32 MB at d=4096)
 
 struct Plan {
-  int n_rb;       // row blocks
+  int cg;         // CTAs per work unit: 1, or 2 (a pair sharing 256-row blocks)
+  int n_rb;       // row blocks (of 128 * cg rows)
   int n_ct;       // column tiles
   int n_strips;   // strips per row block
   int stages;     // smem ring depth
@@ -53,7 +62,7 @@ struct Params {
   int32_t* status;
   int64_t N, D, M;
   int k, n_rb, n_ct, n_strips, stages, units;
-  int row_group;  // row blocks per scheduling group
+  int row_group;  // row blocks (of 128 rows per CTA of the unit) per scheduling group
   // groupmax mode (group_cols > 0): the M columns form k groups of group_cols consecutive
   // latents and every row keeps the largest post-ReLU value of each group; results go
   // straight to gm_vals / gm_idx ([N, k]), strips hold whole groups, no lists, no merge.
@@ -183,11 +192,17 @@ __global__ void init_tau_kernel(float* tau, int64_t n) {
   if (i < n) tau[i] = -1.f;
 }
 
+// CG = CTAs per work unit. CG == 2: launched as clusters of two CTAs (a pair); rank 0 of the
+// cluster is the leader that issues the MMAs and owns the `full` and `tempty` barriers that
+// both CTAs signal; `empty` and `tfull` exist in both CTAs and the leader's commits reach both.
+template <int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                       const Params p) {
+  constexpr uint32_t kStageBytes = stage_bytes(CG);
   extern __shared__ unsigned char smem_dyn[];
-  // 1024-byte alignment for the swizzled tiles
+  // 1024-byte alignment for the swizzled tiles (the same offset in both CTAs of a pair: the
+  // dynamic shared memory of a kernel starts at the same address in every CTA)
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   float* l_val = reinterpret_cast<float*>(smem + p.off_lists_val);         // [128][k]
@@ -202,30 +217,35 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kc_count = (int)((p.D + BK - 1) / BK);
+  const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;   // position inside the pair
+  const bool leader = cta_rank == 0;
+  const int unit0 = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_stride = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     prefetch_tensor_map(&tmap_x);
     prefetch_tensor_map(&tmap_w);
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull[b], 1); mbar_init(&tempty[b], 4 * CG); }
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if constexpr (CG == 2) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   }
   fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync();  // the peer's barriers and tensor memory are ready too
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer (one per CTA; each loads only its own operands) ----------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      for (int u = unit0; u < p.units && ok; u += unit_stride) {
         int rb, strip, t0, t1;
         decode_unit(p, u, rb, strip, t0, t1);
         for (int t = t0; t < t1 && ok; ++t) {
@@ -233,18 +253,34 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kWaitEmpty)) { ok = false; break; }
             unsigned char* sa = smem + (size_t)stage * kStageBytes;
             unsigned char* sb = sa + BM * BK * 2;
-            mbar_arrive_expect_tx(&full[stage], kStageBytes);
-            tma_load_2d(sa, &tmap_x, kc * BK, rb * BM, &full[stage]);
-            tma_load_2d(sb, &tmap_w, kc * BK, t * BN, &full[stage]);
+            if constexpr (CG == 2) {
+              // the bytes of both CTAs are counted on the leader's barrier, which its MMA thread waits on
+              if (leader) mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes);
+              const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+              tma_load_2d_pair(sa, &tmap_x, kc * BK, (rb * 2 + (int)cta_rank) * BM, bar);
+              tma_load_2d_pair(sb, &tmap_w, kc * BK, t * BN + (int)cta_rank * (BN / 2), bar);
+            } else {
+              mbar_arrive_expect_tx(&full[stage], kStageBytes);
+              tma_load_2d(sa, &tmap_x, kc * BK, rb * BM, &full[stage]);
+              tma_load_2d(sb, &tmap_w, kc * BK, t * BN, &full[stage]);
+            }
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
           }
         }
       }
+      if constexpr (CG == 2) {
+        // Stay until the leader's last commits have reached this CTA's `empty` barriers: a CTA of
+        // a pair must not leave while its peer can still signal its shared memory.
+        for (int i = 0; i < p.stages && ok; ++i) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kWaitEmpty)) ok = false;
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+    // ---------------- MMA issuer (the leader's, for both CTAs of a pair) ----------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * CG, BN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -254,14 +290,18 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       long long wait_tmem = 0, wait_full = 0;  // debug bit 2
       const long long t_begin = clock64();
 #endif
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      for (int u = unit0; u < p.units && ok; u += unit_stride) {
         int rb, strip, t0, t1;
         decode_unit(p, u, rb, strip, t0, t1);
         for (int t = t0; t < t1 && ok; ++t) {
 #ifdef SC_DIAG
           const long long w0 = clock64();
 #endif
-          if (!mbar_wait(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+          if constexpr (CG == 2) {
+            if (!mbar_wait_cluster(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+          } else {
+            if (!mbar_wait(&tempty[buf], acc_phase ^ 1, p.status, kWaitTmemEmpty)) { ok = false; break; }
+          }
 #ifdef SC_DIAG
           wait_tmem += clock64() - w0;
 #endif
@@ -282,14 +322,22 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
               // 32 bytes per K step inside the 128-byte swizzle row
-              mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                       (kc | kk) != 0 ? 1u : 0u);
+              if constexpr (CG == 2)
+                mma_bf16_pair(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                              (kc | kk) != 0 ? 1u : 0u);
+              else
+                mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                         (kc | kk) != 0 ? 1u : 0u);
             }
-            mma_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if constexpr (CG == 2) mma_commit_pair(&empty[stage], 3);
+            else mma_commit(&empty[stage]);
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
-          mma_commit(&tfull[buf]);  // accumulator complete
+          // accumulator complete (each CTA of a pair drains its own 128 rows)
+          if constexpr (CG == 2) mma_commit_pair(&tfull[buf], 3);
+          else mma_commit(&tfull[buf]);
           buf ^= 1;
           if (buf == 0) acc_phase ^= 1;
         }
@@ -316,10 +364,13 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     int buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+    // the leader's `tempty` barrier as the peer CTA addresses it
+    const uint32_t tempty_leader0 = CG == 2 ? map_to_cta(smem_u32(&tempty[0]), 0) : 0u;
+    const uint32_t tempty_leader1 = CG == 2 ? map_to_cta(smem_u32(&tempty[1]), 0) : 0u;
+    for (int u = unit0; u < p.units && ok; u += unit_stride) {
       int rb, strip, t0, t1;
       decode_unit(p, u, rb, strip, t0, t1);
-      const int64_t grow = (int64_t)rb * BM + row;
+      const int64_t grow = ((int64_t)rb * CG + cta_rank) * BM + row;
       const int64_t strip_col0 = (int64_t)t0 * BN;
       RowState st;
       st.thr = -1.f; st.minpos = 0; st.cnt = 0;
@@ -443,7 +494,10 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         // accumulator drained
         fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
+        if (lane == 0) {
+          if (CG == 2 && !leader) mbar_arrive_cluster(buf ? tempty_leader1 : tempty_leader0);
+          else mbar_arrive(&tempty[buf]);
+        }
         buf ^= 1;
         if (buf == 0) acc_phase ^= 1;
       }
@@ -470,11 +524,15 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   }
 
 
-  // teardown
+  // teardown: nobody's tensor or shared memory is touched by the peer any more
   fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync();
   fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == 1) {
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
+  }
 }
 
 // ---- merge: final k of a row from its n_strips*k candidates --------------------
@@ -521,15 +579,17 @@ topk_merge_kernel(const float* __restrict__ cand_vals, const int32_t* __restrict
 }
 
 int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols = 0) {
-  pl->n_rb = (int)((N + BM - 1) / BM);
+  const int cg = sc::cta_pairs() ? 2 : 1;
+  pl->cg = cg;
+  pl->n_rb = (int)((N + BM * cg - 1) / (BM * cg));
   pl->n_ct = (int)((M + BN - 1) / BN);
   // groupmax with groups of whole tiles: a strip must hold whole groups, i.e. the strip count
   // divides the group count k
   const bool whole_groups = group_cols >= BN;
   // Strips per row block: the fewest (longest strips, fewest list insertions)
-  // that keep the persistent grid of 148 CTAs busy; strips hold at most 255
-  // tiles so that a strip-relative column fits 16 bits.
-  const int sms = 148 - sc::reserved_sms();
+  // that keep the persistent grid (one CTA, or one CTA pair, per work unit) busy; strips
+  // hold at most 255 tiles so that a strip-relative column fits 16 bits.
+  const int sms = (148 - sc::reserved_sms()) / cg;
   int min_strips = (pl->n_ct + 254) / 255;
   int best = -1;
   double best_eff = -1.0;
@@ -551,17 +611,49 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols =
   const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
   const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
   const size_t smem_limit = 227 * 1024;
-  if (fixed + 2 * kStageBytes > smem_limit) return SC_ERR_UNSUPPORTED;
-  int stages = (int)((smem_limit - fixed) / kStageBytes);
-  if (stages > 6) stages = 6;
+  const size_t stage = stage_bytes(cg);
+  if (fixed + 2 * stage > smem_limit) return SC_ERR_UNSUPPORTED;
+  int stages = (int)((smem_limit - fixed) / stage);
+  if (stages > 8) stages = 8;
   pl->stages = stages;
-  pl->off_lists_val = (size_t)stages * kStageBytes;
+  pl->off_lists_val = (size_t)stages * stage;
   pl->off_lists_idx = pl->off_lists_val + lists_val;
   pl->off_gmin = pl->off_lists_idx + lists_idx;
   pl->off_gpos = pl->off_gmin + gmin;
   pl->off_bias = pl->off_gpos + gpos;
   pl->off_bars = pl->off_bias + 4 * BN * sizeof(float);
   pl->smem = pl->off_bars + 256 + 1024;
+  return SC_OK;
+}
+
+// Launches the persistent kernel: one CTA per SM, as clusters of two for the pair form.
+int launch_encoder(const Plan& pl, const CUtensorMap& tmx, const CUtensorMap& tmw, const Params& p,
+                   cudaStream_t st, const char* what) {
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  sms -= sc::reserved_sms();
+  if (pl.cg == 1) {
+    SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+    const int grid = pl.units < sms ? pl.units : sms;
+    encode_topk_tc_kernel<1><<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
+  } else {
+    SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+    const int pairs = pl.units < sms / 2 ? pl.units : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SC_CUDA(cudaLaunchKernelEx(&cfg, encode_topk_tc_kernel<2>, tmx, tmw, p));
+  }
+  SC_CHECK_LAUNCH(what);
   return SC_OK;
 }
 
@@ -605,13 +697,13 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   CUtensorMap tmx, tmw;
   int rc = make_tensor_map_bf16(&tmx, x_bf16, (uint64_t)N, (uint64_t)D, BM);
   if (rc != SC_OK) return rc;
-  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN);
+  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN / pl.cg);
   if (rc != SC_OK) return rc;
 
   Params p;
   p.bias = bias; p.cand_vals = cand_vals; p.cand_idx = cand_idx; p.tau = tau; p.status = status_word;
   p.N = N; p.D = D; p.M = M; p.k = k;
-  p.row_group = kRowGroupDefault;
+  p.row_group = kRowGroupRows / (BM * pl.cg);
 #ifdef SC_DIAG
   // diagnostics build (-DSC_DIAG) only: the shipped library reads no environment
   const char* dbg = getenv("SC_ENCODE_DEBUG");
@@ -628,14 +720,8 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   cudaStream_t st = sc::as_stream(stream);
   init_tau_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(tau, N);
   SC_CHECK_LAUNCH("init_tau");
-  SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-  int sms = 148;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  sms -= sc::reserved_sms();
-  const int grid = pl.units < sms ? pl.units : sms;
-  encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
-  SC_CHECK_LAUNCH("encode_topk_tc");
+  rc = launch_encoder(pl, tmx, tmw, p, st, "encode_topk_tc");
+  if (rc != SC_OK) return rc;
   const int ncand = pl.n_strips * k;
   topk_merge_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(cand_vals, cand_idx, N, ncand, k, top_vals, top_idx);
   SC_CHECK_LAUNCH("topk_merge");
@@ -664,7 +750,7 @@ extern "C" int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const 
   CUtensorMap tmx, tmw;
   int rc = make_tensor_map_bf16(&tmx, x_bf16, (uint64_t)N, (uint64_t)D, BM);
   if (rc != SC_OK) return rc;
-  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN);
+  rc = make_tensor_map_bf16(&tmw, W_bf16, (uint64_t)M, (uint64_t)D, BN / pl.cg);
   if (rc != SC_OK) return rc;
   Params p;
   p.bias = bias; p.cand_vals = nullptr; p.cand_idx = nullptr; p.tau = nullptr; p.status = status_word;
@@ -672,19 +758,11 @@ extern "C" int sc_encode_groupmax(const void* x_bf16, const void* W_bf16, const 
 #ifdef SC_DIAG
   p.debug = 0;
 #endif
-  p.row_group = kRowGroupDefault;
+  p.row_group = kRowGroupRows / (BM * pl.cg);
   p.group_cols = (int)g; p.gm_vals = top_vals; p.gm_idx = top_idx;
   p.n_rb = pl.n_rb; p.n_ct = pl.n_ct; p.n_strips = pl.n_strips; p.stages = pl.stages; p.units = pl.units;
   p.off_lists_val = (uint32_t)pl.off_lists_val; p.off_lists_idx = (uint32_t)pl.off_lists_idx;
   p.off_gmin = (uint32_t)pl.off_gmin; p.off_gpos = (uint32_t)pl.off_gpos;
   p.off_bias = (uint32_t)pl.off_bias; p.off_bars = (uint32_t)pl.off_bars;
-  cudaStream_t st = sc::as_stream(stream);
-  SC_CUDA(cudaFuncSetAttribute(encode_topk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-  int sms = 148, dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  sms -= sc::reserved_sms();
-  const int grid = pl.units < sms ? pl.units : sms;
-  encode_topk_tc_kernel<<<grid, kThreads, pl.smem, st>>>(tmx, tmw, p);
-  SC_CHECK_LAUNCH("encode_groupmax_tc");
-  return SC_OK;
+  return launch_encoder(pl, tmx, tmw, p, sc::as_stream(stream), "encode_groupmax_tc");
 }

@@ -175,5 +175,110 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA pairs (cta_group::2) -------------------------------------------------
+// Two CTAs of a cluster, on the two SMs of one TPC, compute one 256-row tile
+// together: each stages its own 128 rows of A and its own half of the B tile in
+// its own shared memory with its own TMA loads (no multicast of any kind), the
+// even CTA ("leader") issues the MMAs for both, and each CTA finds its 128 rows
+// of the accumulator in its own tensor memory. Per MMA an SM reads two thirds
+// of the shared-memory bytes that the one-CTA form reads.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address of this CTA's shared-memory location `smem_addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrives on an mbarrier of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// try_wait with cluster-scope acquire, for barriers that threads of the peer CTA arrive on.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int32_t* status, int32_t code,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (global_timer_ns() - t0 > limit_ns) {
+      if (status != nullptr) atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
+// The pair form of tma_load_2d: the data lands in the executing CTA's shared memory, the
+// bytes are counted on `bar_cluster_addr`, an mbarrier of either CTA of the pair (the
+// leader's: map_to_cta(addr, 0)). A plain one-destination load: nothing is multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, int32_t c0, int32_t c1,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+
+// Tensor-memory allocation for a pair: the same warp of BOTH CTAs executes each of these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B^T over the pair (M = 256: 128 rows per CTA; each CTA
+// holds half of B's rows); issued by one thread of the leader CTA. The descriptors are
+// shared-memory offsets that hold in both CTAs.
+__device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Once every MMA issued so far by this thread has completed, arrives on the mbarrier at
+// `bar`'s offset in each CTA of the cluster whose bit is set in cta_mask (0b11: both of a pair).
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+
 }  // namespace tc
 }  // namespace sc

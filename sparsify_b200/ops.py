@@ -176,6 +176,11 @@ def set_reserved_sms(n: int) -> None:
     call("sc_set_reserved_sms", int(n))
 
 
+def set_cta_pairs(on: bool) -> None:
+    """Tensor-core encoder as CTA pairs (default) or single CTAs; see sc_set_cta_pairs."""
+    call("sc_set_cta_pairs", int(bool(on)))
+
+
 def tc_encode_supported(D: int, M: int, k: int) -> bool:
     return D % 8 == 0 and 0 < k <= 128 and k <= M
 

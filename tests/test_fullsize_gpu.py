@@ -39,11 +39,16 @@ def sample_rows(n_rows: int, count: int, seed: int) -> torch.Tensor:
             if base + off < n_rows:
                 rows.add(base + off)
     g = torch.Generator().manual_seed(seed)
-    for r in torch.randperm(n_rows, generator=g).tolist():
+    # random rows, drawn alternately from the lower and the upper half so that a problem that
+    # uses only the first half of the tokens still sees half of the samples
+    half = n_rows // 2
+    lower, upper = torch.randperm(half, generator=g).tolist(), (torch.randperm(n_rows - half, generator=g) + half).tolist()
+    for lo_r, up_r in zip(lower, upper):
         if len(rows) >= count:
             break
-        rows.add(r)
-    return torch.tensor(sorted(rows)[:count] if len(rows) > count else sorted(rows))
+        rows.add(lo_r)
+        rows.add(up_r)
+    return torch.tensor(sorted(rows))
 
 
 @pytest.fixture(scope="module")
@@ -83,7 +88,7 @@ def test_encoder_fullsize_sampled_rows(full_problem, N, M, k):
     ops.check_status(vals.device)  # no bounded wait gave up
     keep = p["rows"] < N
     rows = p["rows"][keep]
-    assert len(rows) >= 128
+    assert len(rows) >= 100
     check_topk_sets(vals[rows.cuda()], idx[rows.cuda()], p["pre"][keep][:, :M], k)
     # every row, cheaply: k distinct in-range indices, values descending and non-negative
     assert bool(((idx >= 0) & (idx < M)).all())
@@ -172,7 +177,7 @@ def test_fused_step_fullsize_vs_oracle(cuda_lib):
     tok_ids = sorted(out_ref)
     ref_rows = torch.stack([out_ref[t] for t in tok_ids])
     assert rel_l2(out.sae_out.detach()[torch.tensor(tok_ids).cuda()], ref_rows) < ACT_TOL
-    assert abs(float(out.fvu) - fvu_ref) <= 1e-3 * fvu_ref
+    assert abs(float(out.fvu.detach()) - fvu_ref) <= 1e-3 * fvu_ref
 
     # gradients, read back from Adam's first moment after step 1: exp_avg = (1 - beta1) g
     st_enc, st_dec = opt.state[sae.encoder.weight], opt.state[sae.W_dec]
@@ -186,20 +191,26 @@ def test_fused_step_fullsize_vs_oracle(cuda_lib):
     assert rel_l2(opt.state[sae.encoder.bias]["exp_avg"].cpu() / (1 - b1), gb_enc) < GRAD_TOL
     assert rel_l2(opt.state[sae.b_dec]["exp_avg"].cpu() / (1 - b1), gb_dec) < GRAD_TOL
 
-    # parameters after Adam (and the decoder's re-normalisation): compare the change itself
+    # Parameters after Adam (and the decoder's re-normalisation). At step 1 Adam moves every
+    # element by lr * g / (|g| + eps): a sign-like function of g, so the update is checked as
+    # arithmetic - the oracle's Adam applied to the gradient the GPU used (read back from its
+    # first moment, itself checked against the oracle above) - and the change must then agree
+    # to fp32 rounding.
     def adam_rows(p_old, grad):
         p, m, v = p_old.clone(), torch.zeros_like(p_old), torch.zeros_like(p_old)
         O.adam_step_(p, grad, m, v, step=1, lr=lr, beta1=b1, beta2=b2)
         return p
-    We_new = adam_rows(old["W_enc"][sampled], gWe_s)
-    Wd_new = adam_rows(old["W_dec"][sampled], gWd_proj)
+    We_new = adam_rows(old["W_enc"][sampled], gWe_gpu)
+    Wd_new = adam_rows(old["W_dec"][sampled], gWd_gpu)
     O.normalize_decoder_(Wd_new)                                # applied at the end of the step here
     d_enc = sae.encoder.weight.detach()[sc].cpu() - old["W_enc"][sampled]
     d_dec = sae.W_dec.detach()[sc].cpu() - old["W_dec"][sampled]
-    assert rel_l2(d_enc, We_new - old["W_enc"][sampled]) < GRAD_TOL
-    assert rel_l2(d_dec, Wd_new - old["W_dec"][sampled]) < 2 * GRAD_TOL
-    assert rel_l2(sae.encoder.bias.detach().cpu() - old["b_enc"], adam_rows(old["b_enc"], gb_enc) - old["b_enc"]) < GRAD_TOL
-    assert rel_l2(sae.b_dec.detach().cpu() - old["b_dec"], adam_rows(old["b_dec"], gb_dec) - old["b_dec"]) < GRAD_TOL
+    assert rel_l2(d_enc, We_new - old["W_enc"][sampled]) < 1e-3
+    assert rel_l2(d_dec, Wd_new - old["W_dec"][sampled]) < 1e-3
+    assert rel_l2(sae.W_dec.detach()[sc].cpu().norm(dim=1), torch.ones(len(sampled))) < 1e-6
+    for name, p in (("b_enc", sae.encoder.bias), ("b_dec", sae.b_dec)):
+        g_gpu = opt.state[p]["exp_avg"].cpu() / (1 - b1)
+        assert rel_l2(p.detach().cpu() - old[name], adam_rows(old[name], g_gpu) - old[name]) < 1e-3, name
     # the bf16 copies the next forward reads are the rounded new parameters
     assert torch.equal(sae.shadow("encoder.weight")[sc].cpu(), sae.encoder.weight.detach()[sc].cpu().to(torch.bfloat16))
     assert torch.equal(sae.shadow("W_dec")[sc].cpu(), sae.W_dec.detach()[sc].cpu().to(torch.bfloat16))

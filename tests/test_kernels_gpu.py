@@ -176,6 +176,34 @@ def test_encoder_tc_vs_oracle(cuda_lib, N, D, M, k):
     check_topk_sets(vals, idx, pre, k)
 
 
+@pytest.mark.parametrize("N,D,M,k", [
+    (200, 256, 1024, 32),
+    (384, 1024, 4352, 32),
+    (1024, 4096, 16384, 32),
+    (300, 128, 2048, 128),
+])
+def test_encoder_tc_single_cta_form(cuda_lib, N, D, M, k):
+    """The encoder runs as CTA pairs by default; the one-CTA form must give the same answer."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(40)
+    x = bf16_round(torch.randn(N, D, generator=g)).cuda().bfloat16()
+    W = bf16_round(torch.randn(M, D, generator=g) / D ** 0.5).cuda().bfloat16()
+    b = (0.1 * torch.randn(M, generator=g)).cuda()
+    vals2, idx2 = ops.encode_topk_tc(x, W, b, k)
+    ops.set_cta_pairs(False)
+    try:
+        vals1, idx1 = ops.encode_topk_tc(x, W, b, k)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_cta_pairs(True)
+    ops.check_status(x.device)
+    pre = O.preacts(x.cpu().double(), W.cpu().double(), b.cpu().double()).float()
+    check_topk_sets(vals1, idx1, pre, k)
+    check_topk_sets(vals2, idx2, pre, k)
+    # same accumulation order per output element in both forms: the values agree exactly
+    assert torch.equal(vals1, vals2) and torch.equal(idx1, idx2)
+
+
 def test_encoder_tc_few_positive(cuda_lib):
     """Rows with fewer than k positive pre-activations still return k distinct
     valid indices (zeros fill the tail), as torch.topk over post-ReLU values does."""
