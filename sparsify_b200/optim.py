@@ -29,14 +29,33 @@ def _touched(p: Tensor) -> None:
 
 
 class FusedAdam(torch.optim.Optimizer):
+    # torch.optim.Adam's remaining hyper-parameters at the values this optimiser implements.
+    # They are stored in every parameter group so that a state dict written here has the keys
+    # torch.optim.Adam.load_state_dict installs (and its step() then reads) in the reference
+    # Trainer, and one written by torch.optim.Adam is checked against them when loaded here.
+    _TORCH_ADAM_FIXED = dict(weight_decay=0, amsgrad=False, maximize=False, foreach=None, capturable=False,
+                             differentiable=False, fused=None, decoupled_weight_decay=False)
+
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8):
         if lr < 0:
             raise ValueError(f"Invalid learning rate: {lr}")
-        defaults = dict(lr=lr, betas=betas, eps=eps)
+        defaults = dict(lr=lr, betas=betas, eps=eps, **self._TORCH_ADAM_FIXED)
         super().__init__(params, defaults)
         self._project: set[int] = set()
         self._shadow: dict[int, tuple] = {}
         self._sparse: list = []  # coders whose weight gradients arrive in sparse form
+
+    def load_state_dict(self, state_dict) -> None:
+        """Accepts state dicts written by this class and by torch.optim.Adam (the reference
+        Trainer's optimizer_0.pt, sparsify/trainer.py:219-223); refuses Adam variants this
+        optimiser does not implement instead of silently ignoring them."""
+        for group in state_dict["param_groups"]:
+            if group.get("weight_decay", 0) != 0 or group.get("amsgrad", False) or group.get("maximize", False):
+                raise ValueError("FusedAdam implements plain Adam only (weight_decay=0, amsgrad=False, maximize=False)")
+        super().load_state_dict(state_dict)
+        for group in self.param_groups:  # the execution-strategy flags of torch's Adam mean nothing here
+            for key, val in self._TORCH_ADAM_FIXED.items():
+                group[key] = val if key in ("foreach", "capturable", "differentiable", "fused") else group.get(key, val)
 
     def project_rows(self, p: Tensor) -> None:
         """Marks `p` (a [M, D] decoder) for gradient projection at every step."""

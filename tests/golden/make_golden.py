@@ -372,8 +372,58 @@ def gen_muon(sparsify):
         save(f"newtonschulz_{name}", dict(G=G, X=X.float()))
 
 
+def gen_checkpoints(sparsify):
+    """Checkpoint trees written by the reference itself, for the loaders of this package:
+    `SparseCoder.save_to_disk` of a small SAE and of a transcoder with a skip connection
+    (sparsify/sparse_coder.py:167-179), and the tree `Trainer.save()` leaves after three
+    optimiser steps (sparsify/trainer.py:648-699). Stored under tests/golden/ckpt_ref/."""
+    import shutil
+    from sparsify import SparseCoder, SparseCoderConfig, TrainConfig, Trainer
+    root = HERE / "ckpt_ref"
+    if root.exists():
+        shutil.rmtree(root)
+    for name, cfg in (("sae", SparseCoderConfig(num_latents=48, k=4)),
+                      ("transcoder", SparseCoderConfig(num_latents=40, k=3, transcode=True, skip_connection=True))):
+        torch.manual_seed(31)
+        sae = SparseCoder(12, cfg)
+        with torch.no_grad():
+            for q in sae.parameters():
+                q.add_(0.1 * torch.randn_like(q))
+        sae.save_to_disk(root / name)
+    steps, B, T, D, M, k = 3, 2, 8, 12, 48, 4
+    g = torch.Generator().manual_seed(32)
+    acts = torch.randn(steps, B, T, D, generator=g)
+    model = FakeModel(acts)
+    dataset = [{"input_ids": torch.zeros(T, dtype=torch.long)} for _ in range(steps * B)]
+    cfg = TrainConfig(SparseCoderConfig(num_latents=M, k=k), batch_size=B, optimizer="adam", lr_warmup_steps=2,
+                      auxk_alpha=1 / 32, dead_feature_threshold=20, hookpoints=["layers.0"], log_to_wandb=False,
+                      save_dir=str(root), run_name="trainer", save_every=10 ** 9)
+    trainer = Trainer(cfg, dataset, model)
+    trainer.fit()  # ends with Trainer.save()
+    print("wrote", sorted(str(f.relative_to(root)) for f in root.rglob("*") if f.is_file()))
+
+
+def check_reference_loads_ours(sparsify):
+    """The other direction: a tree written by THIS package (SparseCoder.save_to_disk and
+    Trainer.save, on the host) read by the reference's own loaders
+    (sparsify/sparse_coder.py:134-165, sparsify/trainer.py:186-227). Records the outcome in
+    tests/golden/ckpt_interchange.json; tests/test_checkpoint_interchange.py repeats the check
+    live wherever the reference is at hand."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from tests.test_checkpoint_interchange import reference_reads_our_tree
+    with tempfile.TemporaryDirectory() as tmp:
+        report = reference_reads_our_tree(sparsify, Path(tmp))
+    with open(HERE / "ckpt_interchange.json", "w") as f:
+        json.dump(report, f, indent=1)
+    print("ckpt_interchange.json:", report)
+
+
 if __name__ == "__main__":
     ref = import_reference()
+    if "--checkpoints" in sys.argv:  # only the checkpoint interchange fixtures
+        gen_checkpoints(ref)
+        check_reference_loads_ours(ref)
+        sys.exit(0)
     torch.set_num_threads(1)  # one summation order
     gen_encoder(ref)
     gen_decoder(ref)
