@@ -51,9 +51,10 @@ int sc_version(void);
  * (0 <= n <= 64), e.g. for the kernels of a communication library that should
  * run concurrently. Process-wide; set it before sizing workspaces. */
 int sc_set_reserved_sms(int n);
-/* The tensor-core encoder (sc_encode_topk, sc_encode_groupmax) runs by default as
+/* on != 0 makes the tensor-core encoder (sc_encode_topk, sc_encode_groupmax) run as
  * pairs of CTAs on the two SMs of a TPC (tcgen05 cta_group::2: one 256-row tile
- * per pair, each CTA loading its own operands); on = 0 selects the one-CTA form.
+ * per pair, each CTA loading its own operands with its own loads); the default is
+ * one CTA per tile, which measured faster under the B200's power cap.
  * Process-wide; set it before sizing workspaces. Results are identical. */
 int sc_set_cta_pairs(int on);
 /* Copies the last error message (NUL-terminated) into buf; returns its length. */
@@ -163,7 +164,7 @@ int sc_decode_residual(const int64_t* idx, const float* acts, const void* W,
                        void* ws, size_t ws_bytes, void* stream);
 
 /* Latent-major CSR of the [N,k] index matrix: row_ptr[M+1], entries[N*k]
- * (flat position n*k+j, ascending inside each latent).
+ * (flat position n*k+j, ascending inside each latent, whatever its length).
  * ws: sc_csr_workspace_bytes(M) bytes.
  * sparsify/xformers.py:56-85,146-163 (count, cumsum, reverse mapping). */
 size_t sc_csr_workspace_bytes(int64_t M);
@@ -184,7 +185,9 @@ int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M,
  * resolves the array's device address (cudaGetSymbolAddress) and should
  * therefore come before any stream capture on that device. All calls share the
  * one array: calls that may overlap on the GPU (different streams, or the same
- * device from several threads) race and must be serialised by the caller. */
+ * device from several threads) race and must be serialised by the caller.
+ * The array is the one of the device that is current at the call, so `stream`
+ * must belong to that device. */
 int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_t M,
                          int32_t* row_ptr, int32_t* entries, void* stream);
 

@@ -14,7 +14,7 @@ char g_err[512] = "";
 
 namespace {
 std::atomic<int> g_reserved_sms{0};
-std::atomic<int> g_cta_pairs{1};
+std::atomic<int> g_cta_pairs{0};
 }  // namespace
 
 namespace sc {

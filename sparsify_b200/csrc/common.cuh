@@ -17,7 +17,7 @@ int fail(int status, const char* fmt, ...);
 // communication library's kernels that have to run beside them.
 int reserved_sms();
 
-// Whether the tensor-core encoder runs as CTA pairs (sc_set_cta_pairs; default on).
+// Whether the tensor-core encoder runs as CTA pairs (sc_set_cta_pairs; default off).
 bool cta_pairs();
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }

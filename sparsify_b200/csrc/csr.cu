@@ -2,8 +2,9 @@
 //
 // count (atomic histogram) -> exclusive scan -> slot fill (atomic cursors) ->
 // per-latent sort of the claimed slots, so that the entries of each latent
-// come out in ascending flat position n*k+j whatever order the atomics ran in.
-// Latents with more than kSortMax entries keep the arrival order.
+// come out in ascending flat position n*k+j whatever order the atomics ran in:
+// a warp per latent for segments of up to kSortMax entries, and a second small
+// launch that sorts the (rare) longer segments in place, one CTA per segment.
 #include <mutex>
 
 #include "common.cuh"
@@ -137,15 +138,25 @@ __global__ void csr_fill_kernel(const int64_t* __restrict__ idx, int64_t total, 
 
 // One warp per latent; segments of 2..32 entries sort in registers, segments up
 // to kSortMax in a per-warp shared-memory buffer (bitonic network).
+// Longer segments are queued: *long_count = how many, long_ids[0 .. long_cap) their latents
+// (the histogram and cursor arrays, dead by then, serve as the queue).
 constexpr int kSortWarps = 4;
 __global__ void __launch_bounds__(kSortWarps * 32)
-csr_sort_kernel(const int32_t* __restrict__ row_ptr, int64_t M, int32_t* __restrict__ entries) {
+csr_sort_kernel(const int32_t* __restrict__ row_ptr, int64_t M, int32_t* __restrict__ entries,
+                int32_t* __restrict__ long_count, int32_t* __restrict__ long_ids, int32_t long_cap) {
   __shared__ int32_t s_buf[kSortWarps][kSortMax];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t m = (int64_t)blockIdx.x * kSortWarps + warp;
   if (m >= M) return;
   const int32_t lo = row_ptr[m], len = row_ptr[m + 1] - lo;
-  if (len <= 1 || len > kSortMax) return;
+  if (len > kSortMax) {
+    if (lane == 0) {
+      const int32_t slot = atomicAdd(long_count, 1);
+      if (slot < long_cap) long_ids[slot] = (int32_t)m;
+    }
+    return;
+  }
+  if (len <= 1) return;
   if (len <= 32) {
     int32_t v = lane < len ? entries[lo + lane] : 0x7fffffff;
     for (int size = 2; size <= 32; size <<= 1) {
@@ -180,6 +191,70 @@ csr_sort_kernel(const int32_t* __restrict__ row_ptr, int64_t M, int32_t* __restr
   for (int i = lane; i < len; i += 32) entries[lo + i] = buf[i];
 }
 
+// Sorts the queued long segments in place in global memory, one CTA per segment: a bitonic
+// network in its all-ascending form (the first step of every merge pairs i with i ^ (size-1),
+// the others i with i ^ stride), which sorts any length as if the tail were padded with
+// +infinity - a pair whose upper index lies beyond the segment is simply left alone.
+__global__ void __launch_bounds__(1024)
+csr_sort_long_kernel(const int32_t* __restrict__ row_ptr, int32_t* __restrict__ entries,
+                     const int32_t* __restrict__ long_count, const int32_t* __restrict__ long_ids,
+                     int32_t long_cap) {
+  const int32_t n_long = min(*long_count, long_cap);
+  for (int32_t w = blockIdx.x; w < n_long; w += gridDim.x) {
+    const int32_t m = long_ids[w];
+    const int32_t lo = row_ptr[m], len = row_ptr[m + 1] - lo;
+    int32_t* seg = entries + lo;
+    int64_t n2 = 1;
+    while (n2 < len) n2 <<= 1;
+    for (int64_t size = 2; size <= n2; size <<= 1) {
+      for (int64_t stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int64_t i = threadIdx.x; i < n2 / 2; i += blockDim.x) {
+          const int64_t a = 2 * i - (i & (stride - 1));                     // bit `stride` clear
+          const int64_t b = (stride == (size >> 1)) ? (a ^ (size - 1)) : (a + stride);
+          if (b < len) {
+            const int32_t x = seg[a], y = seg[b];
+            if (x > y) { seg[a] = y; seg[b] = x; }
+          }
+        }
+        __syncthreads();
+      }
+    }
+  }
+}
+
+// count -> scan -> fill -> sort with the three scratch arrays given (counts, cursor: M ints
+// each; tile_sums: ceil(M / kScanTile) ints).
+int build_csr(const int64_t* idx, int64_t N, int k, int64_t M, int32_t* row_ptr, int32_t* entries,
+              int32_t* counts, int32_t* cursor, int32_t* tile_sums, cudaStream_t st) {
+  const int64_t total = N * k;
+  // scratch keeps whatever an earlier call left: the histogram must start at zero
+  SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
+  if (total == 0) return launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
+  SC_CHECK_LAUNCH("csr_count");
+  int rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
+  if (rc != SC_OK) return rc;
+  csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
+  SC_CHECK_LAUNCH("csr_fill");
+  // histogram and cursors are dead now: counts[0] counts the long segments, cursor[0..M) lists them
+  int32_t* long_count = counts;
+  int32_t* long_ids = cursor;
+  const int32_t long_cap = (int32_t)M;
+  SC_CUDA(cudaMemsetAsync(long_count, 0, sizeof(int32_t), st));
+  csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(
+      row_ptr, M, entries, long_count, long_ids, long_cap);
+  SC_CHECK_LAUNCH("csr_sort");
+  if (total > kSortMax) {  // otherwise no segment can be long
+    const int64_t most = total / kSortMax;
+    csr_sort_long_kernel<<<(unsigned)(most < 64 ? most : 64), 1024, 0, st>>>(row_ptr, entries, long_count, long_ids,
+                                                                            long_cap);
+    SC_CHECK_LAUNCH("csr_sort_long");
+  }
+  return SC_OK;
+}
+
 }  // namespace
 
 extern "C" size_t sc_csr_workspace_bytes(int64_t M) {
@@ -205,26 +280,8 @@ extern "C" int sc_csr_build(const int64_t* idx, int64_t N, int k, int64_t M, int
   int32_t* counts = static_cast<int32_t*>(ws);
   int32_t* cursor = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + one);
   int32_t* tile_sums = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + 2 * one);
-  const int64_t total = N * k;
-  SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
-  if (total > 0) {
-    SC_REQUIRE(idx && entries, "sc_csr_build: null pointer");
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
-    SC_CHECK_LAUNCH("csr_count");
-    int rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
-    if (rc != SC_OK) return rc;
-    csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
-    SC_CHECK_LAUNCH("csr_fill");
-    csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(
-        row_ptr, M, entries);
-    SC_CHECK_LAUNCH("csr_sort");
-  } else {
-    int rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
-    if (rc != SC_OK) return rc;
-  }
-  return SC_OK;
+  SC_REQUIRE(N * (int64_t)k == 0 || (idx && entries), "sc_csr_build: null pointer");
+  return build_csr(idx, N, k, M, row_ptr, entries, counts, cursor, tile_sums, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -276,24 +333,7 @@ extern "C" int sc_csr_build_noalloc(const int64_t* idx, int64_t N, int k, int64_
   int32_t* counts = static_cast<int32_t*>(scratch);
   int32_t* cursor = counts + kNoAllocMaxLatents;
   int32_t* tile_sums = cursor + kNoAllocMaxLatents;
-  const int64_t total = N * k;
-  // the array keeps whatever the previous call left: the histogram must start at zero
-  SC_CUDA(cudaMemsetAsync(counts, 0, (size_t)M * sizeof(int32_t), st));
-  if (total > 0) {
-    SC_REQUIRE(idx && entries, "sc_csr_build_noalloc: null pointer");
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    csr_count_kernel<<<blocks, 256, 0, st>>>(idx, total, M, counts);
-    SC_CHECK_LAUNCH("csr_count");
-    rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
-    if (rc != SC_OK) return rc;
-    csr_fill_kernel<<<blocks, 256, 0, st>>>(idx, total, M, cursor, entries);
-    SC_CHECK_LAUNCH("csr_fill");
-    csr_sort_kernel<<<(unsigned)((M + kSortWarps - 1) / kSortWarps), kSortWarps * 32, 0, st>>>(row_ptr, M, entries);
-    SC_CHECK_LAUNCH("csr_sort");
-  } else {
-    rc = launch_scan(counts, M, row_ptr, cursor, tile_sums, st);
-    if (rc != SC_OK) return rc;
-  }
-  return SC_OK;
+  // every call shares the one array; build_csr clears what has to start at zero
+  SC_REQUIRE(N * (int64_t)k == 0 || (idx && entries), "sc_csr_build_noalloc: null pointer");
+  return build_csr(idx, N, k, M, row_ptr, entries, counts, cursor, tile_sums, st);
 }

@@ -180,8 +180,8 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // together: each stages its own 128 rows of A and its own half of the B tile in
 // its own shared memory with its own TMA loads (no multicast of any kind), the
 // even CTA ("leader") issues the MMAs for both, and each CTA finds its 128 rows
-// of the accumulator in its own tensor memory. Per MMA an SM reads two thirds
-// of the shared-memory bytes that the one-CTA form reads.
+// of the accumulator in its own tensor memory. Per k-chunk an SM stages two thirds
+// of the bytes that the one-CTA form stages.
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

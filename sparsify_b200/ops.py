@@ -177,7 +177,8 @@ def set_reserved_sms(n: int) -> None:
 
 
 def set_cta_pairs(on: bool) -> None:
-    """Tensor-core encoder as CTA pairs (default) or single CTAs; see sc_set_cta_pairs."""
+    """Tensor-core encoder as CTA pairs (tcgen05 cta_group::2) or, the default, single CTAs; see
+    sc_set_cta_pairs."""
     call("sc_set_cta_pairs", int(bool(on)))
 
 

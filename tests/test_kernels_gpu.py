@@ -104,10 +104,23 @@ def test_csr_exact(cuda_lib):
     for m in range(M):
         lo, hi = int(ref_ptr[m]), int(ref_ptr[m + 1])
         seg = entries[lo:hi]
-        if hi - lo <= 2048:
-            assert torch.equal(seg, ref_order[lo:hi]), m  # ascending flat positions
-        else:
-            assert torch.equal(seg.sort().values, ref_order[lo:hi]), m
+        assert torch.equal(seg, ref_order[lo:hi]), m  # ascending flat positions, long segments too
+
+
+def test_csr_long_segments_exact(cuda_lib):
+    """Latents hit by more tokens than the in-warp sort holds (2048): lengths just above the limit,
+    a non-power-of-two length and one latent that every token selects."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    N, k, M = 70000, 4, 64
+    idx = torch.randint(8, M, (N, k), generator=g)
+    idx[:, 0] = 3                       # N entries
+    idx[:2049, 1] = 5                   # one above the limit
+    idx[10000:15001, 2] = 6             # 5001 entries
+    row_ptr, entries = ops.csr_build(idx.cuda(), M)
+    ref_ptr, ref_order = O.csr_by_latent(idx, M)
+    assert torch.equal(row_ptr.cpu().long(), ref_ptr)
+    assert torch.equal(entries.cpu().long(), ref_order)
 
 
 def test_csr_empty_and_ragged(cuda_lib):
@@ -182,20 +195,20 @@ def test_encoder_tc_vs_oracle(cuda_lib, N, D, M, k):
     (1024, 4096, 16384, 32),
     (300, 128, 2048, 128),
 ])
-def test_encoder_tc_single_cta_form(cuda_lib, N, D, M, k):
-    """The encoder runs as CTA pairs by default; the one-CTA form must give the same answer."""
+def test_encoder_tc_cta_pair_form(cuda_lib, N, D, M, k):
+    """The encoder's CTA-pair form (tcgen05 cta_group::2) must give the answer of the default form."""
     from sparsify_b200 import ops
     g = torch.Generator().manual_seed(40)
     x = bf16_round(torch.randn(N, D, generator=g)).cuda().bfloat16()
     W = bf16_round(torch.randn(M, D, generator=g) / D ** 0.5).cuda().bfloat16()
     b = (0.1 * torch.randn(M, generator=g)).cuda()
-    vals2, idx2 = ops.encode_topk_tc(x, W, b, k)
-    ops.set_cta_pairs(False)
+    vals1, idx1 = ops.encode_topk_tc(x, W, b, k)
+    ops.set_cta_pairs(True)
     try:
-        vals1, idx1 = ops.encode_topk_tc(x, W, b, k)
+        vals2, idx2 = ops.encode_topk_tc(x, W, b, k)
         torch.cuda.synchronize()
     finally:
-        ops.set_cta_pairs(True)
+        ops.set_cta_pairs(False)
     ops.check_status(x.device)
     pre = O.preacts(x.cpu().double(), W.cpu().double(), b.cpu().double()).float()
     check_topk_sets(vals1, idx1, pre, k)

@@ -50,6 +50,30 @@ def test_noalloc_matches_regular_twice_in_a_row(cuda_lib):
         assert torch.equal(got_entries, want_entries)
 
 
+def test_noalloc_at_its_largest_size_and_with_no_tokens(cuda_lib):
+    """M = 262144 uses the built-in scratch to its last slot (256 scan tiles); N = 0 takes the
+    branch that only writes an all-zero row_ptr. A latent selected by every token exercises the
+    sort of long segments, whose queue lives in the same scratch."""
+    g = torch.Generator().manual_seed(124)
+    M, N, k = 262144, 3000, 4
+    idx = torch.randint(16, M, (N, k), generator=g)
+    idx[:, 0] = M - 1
+    idx[:, 1] = 7
+    idx = idx.cuda()
+    want_ptr, want_entries = _regular(cuda_lib, idx, M)
+    got_ptr, got_entries = _noalloc(cuda_lib, idx, M)
+    torch.cuda.synchronize()
+    assert torch.equal(got_ptr, want_ptr) and torch.equal(got_entries, want_entries)
+    assert int(got_ptr[-1]) == N * k
+    seg = got_entries[int(got_ptr[7]):int(got_ptr[8])].cpu()
+    assert torch.equal(seg, torch.arange(N, dtype=torch.int32) * k + 1)  # ascending flat positions
+    empty = torch.zeros(0, 4, dtype=torch.int64, device="cuda")
+    want_ptr, _ = _regular(cuda_lib, empty, 513)
+    got_ptr, _ = _noalloc(cuda_lib, empty, 513)
+    torch.cuda.synchronize()
+    assert torch.equal(got_ptr, want_ptr) and int(got_ptr.abs().sum()) == 0
+
+
 def test_noalloc_rejects_sizes_beyond_its_scratch(cuda_lib):
     from sparsify_b200 import _lib
     rc = cuda_lib.sc_csr_build_noalloc(None, 0, 4, 262144 + 1, 1, None, None)
