@@ -199,6 +199,16 @@ class FusedSaeStep(torch.autograd.Function):
                 vecA = ops.prep_input(gout, None, torch.bfloat16)
             sae._pending = dict(row_ptr=row_ptr, entries=entries, k=k, idx=idx, coefA=acts * scale,
                                 vecA=vecA, coefB=gacts, vecB=xe, extra=extra)
+            early = getattr(sae, "_early", None)
+            if early is not None:
+                # sharded update: the small factors (indices and the two coefficient arrays, already
+                # divided by the world size) follow the row arrays as soon as they exist, so that the
+                # optimiser step finds them gathered
+                world = sae._shard[1]
+                pend = sae._pending
+                early["idx"] = _start_all_gather(idx.to(torch.int32), world)
+                early["coefA"] = _start_all_gather((pend["coefA"].to(torch.float32) / world).reshape(idx.shape), world)
+                early["coefB"] = _start_all_gather((gacts.to(torch.float32) / world).reshape(idx.shape), world)
             g_W_dec = g_W_enc = None
             g_b_enc = ops.csr_segment_sum(row_ptr, entries, gacts, M)
         else:

@@ -138,8 +138,11 @@ class FusedAdam(torch.optim.Optimizer):
             return
         sae._pending = None
         shard = getattr(sae, "_shard", None)
+        late_vecA = None
         if shard is not None:
-            pend = self._exchange_factors(sae, pend, shard)
+            # (the gathered residual rows may still be travelling: the encoder half of the update
+            # does not need them, so they are waited for only in front of the decoder half)
+            pend, late_vecA = self._exchange_factors(sae, pend, shard)
         hps, states = [], []
         for p in (W_dec, W_enc):
             group, state = self._group_of(p), self._state_for(p)
@@ -205,6 +208,8 @@ class FusedAdam(torch.optim.Optimizer):
                 mine = shadow_enc[0][rows].clone()
                 sae._enc_work = dist.all_gather_into_tensor(shadow_enc[0].view(-1), mine.view(-1), async_op=True)
                 sae._enc_work_src = mine
+            if late_vecA is not None:
+                args = args[:4] + (late_vecA(),) + args[5:]  # the residual rows of every rank, now needed
             ops.rows_adam_(*args, parts=1, **kw)
         if shard is not None:
             if getattr(sae, "_overlap_decoder", False):
@@ -255,31 +260,39 @@ class FusedAdam(torch.optim.Optimizer):
             dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1))
             return out
 
-        # the row arrays may already be on their way (started by the forward pass)
+        # the arrays may already be on their way (started by the forward and backward passes)
         early = getattr(sae, "_early", None) or {}
         sae._early = None
+        dev = idx.device
 
         def take(name, t):
             if name in early:
                 src, out, work = early[name]
                 work.wait()
-                if src is t or (src.data_ptr() == t.data_ptr() and src.shape == t.shape):
+                if src.shape == t.shape and src.dtype == t.dtype:
                     return out
             return gather(t)
 
-        dev = idx.device
         with ops.span("x_wait_rows", dev):
             vecB_all = take("vecB", vecB)   # same order on every rank: issued first, waited first
-            vecA_all = take("vecA", vecA)
+        late = None
+        if "vecA" in early and early["vecA"][0].shape == vecA.shape:
+            def late():  # waited for in front of the decoder half of the update
+                with ops.span("x_wait_residual_rows", dev):
+                    early["vecA"][2].wait()
+                return early["vecA"][1]
+            vecA_all = vecA  # placeholder with a valid address: the encoder half never reads it
+        else:
+            vecA_all = gather(vecA)
         with ops.span("x_gather_factors", dev):
-            idx_all, coefA_all, coefB_all = gather(idx), gather(coefA), gather(coefB)
+            idx_all, coefA_all, coefB_all = take("idx", idx), take("coefA", coefA), take("coefB", coefB)
         per = sae.encoder.weight.shape[0] // world
         with ops.span("x_csr_slice", dev):
             # indices relative to this rank's slice; the CSR build skips the ones outside [0, per)
             local = idx_all.to(torch.int64) - rank * per
             row_ptr, entries = ops.csr_build(local, per)
         return dict(row_ptr=row_ptr, entries=entries, k=k, coefA=coefA_all, vecA=vecA_all, coefB=coefB_all,
-                    vecB=vecB_all, extra=pend.get("extra"))
+                    vecB=vecB_all, extra=pend.get("extra")), late
 
     @torch.no_grad()
     def step(self, closure=None):
