@@ -36,7 +36,10 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="ours: this library; reference: the reference's own CPU path on the host cores; "
+                         "reference-gpu: the reference's own CUDA path (bf16 autocast, its Triton decoder) on one "
+                         "GPU of this box, printed as context next to this library's figure")
     ap.add_argument("--tokens", type=int, default=16384, help="tokens per rank per step")
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--latents", type=int, default=131072)
@@ -49,6 +52,8 @@ def parse_args():
     ap.add_argument("--config0-steps", type=int, default=10,
                     help="timed steps of the CPU arm's second figure, the reference's CPU-sized configuration "
                          "(d_in=768, 24576 latents, k=32, 4096 tokens per step); 0 skips it")
+    ap.add_argument("--no-gpu-reference", action="store_true",
+                    help="skip the same-box figure of the reference's own CUDA path (a child process, N=1 only)")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the secondary workloads (AuxK active, transcoder k=64 with skip, and on several "
                          "ranks the hookpoint-sharded Muon workload) that follow the headline measurement")
@@ -305,6 +310,60 @@ def run_reference(a):
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(a):
+    """The reference's own GPU path on cuda:0 of this box: sparsify's Trainer.fit() with its
+    bf16 autocast forward, dense pre-activations + torch.topk, its Triton embedding-bag
+    decoder and torch.optim.Adam, on the workload's full shape. Context for the headline,
+    not a contract arm; runs in a process of its own (see gpu_reference_sample)."""
+    import contextlib
+
+    from oracle import ref_loader
+    from sparsify_b200.synthetic import SyntheticActivations, batch_seed
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    steps, warmup = max(1, min(a.steps, 10)), max(1, min(a.warmup, 3))
+    gen = SyntheticActivations(a.d, min(a.atoms, 65536), a.active, device=dev)
+    acts = torch.stack([gen.batch(a.tokens, batch_seed(t), torch.bfloat16).reshape(1, a.tokens, a.d)
+                        for t in range(warmup + steps)])
+    del gen
+    torch.cuda.empty_cache()
+    with contextlib.redirect_stdout(sys.stderr):
+        res = ref_loader.time_reference_trainer(acts, num_latents=a.latents, k=a.k, warmup_steps=warmup, triton=True)
+    sec = statistics.median(res["seconds"])
+    import sparsify.utils as ref_utils
+    print(json.dumps({"impl": "reference-gpu", "metric": METRIC, "value": a.tokens / sec, "unit": UNIT, "n_gpus": 1,
+                      "steps": len(res["seconds"]), "warmup": warmup, "ms_per_step": sec * 1e3,
+                      "decoder": ref_utils.decoder_impl.__name__,
+                      "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+                      "sample": f"sparsify {res['version']} Trainer.fit() on one B200: fp32 parameters, bf16 autocast "
+                                f"forward, {ref_utils.decoder_impl.__name__}, torch.optim.Adam; {a.tokens} tokens/step at "
+                                f"d_in={a.d}, latents={a.latents}, k={a.k}; median of {len(res['seconds'])} steps after "
+                                f"{warmup}, wall clock between device synchronisations"}), flush=True)
+
+
+def gpu_reference_sample(a) -> dict:
+    """Runs `bench.py --impl reference-gpu` as a child process (its own CUDA context and memory;
+    a failure of the reference's GPU code cannot take the benchmark down) and returns its
+    line, or {"unavailable": reason}."""
+    from oracle import ref_loader
+    if ref_loader.find_reference() is None:
+        return {"unavailable": "the vendored reference (oracle/_ref) is not present"}
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference-gpu", "--steps", "5", "--warmup", "3",
+           "--tokens", str(a.tokens), "--d", str(a.d), "--latents", str(a.latents), "--k", str(a.k),
+           "--atoms", str(a.atoms), "--active", str(a.active)]
+    env = {k_: v for k_, v in os.environ.items() if k_ not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMP_NUM_THREADS")}
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=420, cwd=ROOT, env=env)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference's GPU path did not finish within 420 s"}
+    lines = [l for l in out.stdout.strip().splitlines() if l.startswith("{")]
+    if out.returncode != 0 or not lines:
+        tail = (out.stderr.strip().splitlines() or ["no output"])[-1]
+        return {"unavailable": f"the reference's GPU path failed here (exit {out.returncode}): {tail[:300]}"}
+    d = json.loads(lines[-1])
+    return {k_: d[k_] for k_ in ("value", "unit", "ms_per_step", "steps", "decoder", "peak_memory_gb", "sample")}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -747,6 +806,9 @@ def run_ours(a):
             base = cpu_arm(a, 2, 1, config0_steps=a.config0_steps)
             line["cpu_baseline"] = {k_: base[k_] for k_ in ("value", "unit", "cores", "kind", "sample", "config0")
                                     if k_ in base}
+        if world == 1 and not a.no_gpu_reference and not (a.transcode or a.multi_topk or a.dead_frac > 0):
+            torch.cuda.empty_cache()  # this process holds nothing large any more
+            line["gpu_reference"] = gpu_reference_sample(a)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -1075,7 +1137,7 @@ def run_kernel(a):
 
 if __name__ == "__main__":
     args = parse_args()
-    if args.impl != "reference" and args.cta_pairs:
+    if args.impl == "ours" and args.cta_pairs:
         from sparsify_b200 import ops as _ops_cfg
         _ops_cfg.set_cta_pairs(True)
     if args.kernel:
@@ -1084,5 +1146,7 @@ if __name__ == "__main__":
         run_modules(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_ours(args)

@@ -71,14 +71,19 @@ class _NoScheduleFree:
     """Placeholder so that `isinstance(opt, ScheduleFreeWrapper)` is False."""
 
 
-def import_reference(schedulefree_wrapper=None):
-    """Imports the reference package (CPU: Triton disabled, as the reference does when
-    SPARSIFY_DISABLE_TRITON=1, sparsify/utils.py:94-103) and returns the module."""
+def import_reference(schedulefree_wrapper=None, triton: bool = False):
+    """Imports the reference package and returns the module. triton=False (the CPU arm and the
+    fixtures): Triton disabled, as the reference does when SPARSIFY_DISABLE_TRITON=1
+    (sparsify/utils.py:94-103); triton=True leaves the reference's own dispatch alone, which
+    on a GPU box compiles and uses its Triton decoder kernels (sparsify/xformers.py)."""
     root = find_reference()
     if root is None:
         raise RuntimeError("the reference is not available: run `python oracle/make_ref.py` where a checkout of "
                            "EleutherAI/sparsify v1.3.0 exists, or point SPARSIFY_REF at one")
-    os.environ["SPARSIFY_DISABLE_TRITON"] = "1"
+    if triton:
+        os.environ.pop("SPARSIFY_DISABLE_TRITON", None)
+    else:
+        os.environ["SPARSIFY_DISABLE_TRITON"] = "1"
     import transformers  # noqa: F401  (must be imported before the accelerate stand-in exists)
 
     natsort = types.ModuleType("natsort")
@@ -122,7 +127,7 @@ class StoredActivations(torch.nn.Module):
         super().__init__()
         self.config = types.SimpleNamespace(num_hidden_layers=1)
         self.layers = torch.nn.ModuleList([_Layer(self)])
-        self.acts = acts  # [steps, B, T, D]
+        self.acts = acts  # [steps, B, T, D], on the device the coders are to live on
         self.cursor = -1  # the Trainer's width probe consumes one call
         self.dummy_inputs = {"input_ids": torch.zeros(1, acts.shape[2], dtype=torch.long)}
         self.stamps: list[float] = []
@@ -133,7 +138,7 @@ class StoredActivations(torch.nn.Module):
 
     @property
     def device(self):
-        return torch.device("cpu")
+        return self.acts.device
 
     def next_activation(self):
         i = max(self.cursor, 0)
@@ -142,18 +147,23 @@ class StoredActivations(torch.nn.Module):
 
     def forward(self, input_ids=None, **kw):
         if self.cursor >= 0:
+            if self.acts.is_cuda:
+                torch.cuda.synchronize(self.acts.device)  # the previous step has finished on the device
             self.stamps.append(time.perf_counter())
         return self.layers[0](input_ids)
 
 
 def time_reference_trainer(acts: torch.Tensor, *, num_latents: int, k: int, warmup_steps: int,
-                           auxk_alpha: float = 1 / 32, threads: int | None = None) -> dict:
+                           auxk_alpha: float = 1 / 32, threads: int | None = None, triton: bool = False) -> dict:
     """Runs the reference's own `Trainer.fit()` (sparsify/trainer.py:237-596: hook, forward,
     backward, decoder normalisation and projection, torch.optim.Adam, schedule, dead-latent
-    bookkeeping) on the host over acts [steps, B, T, D] (fp32) and returns the seconds of
-    every step after the first `warmup_steps`, measured between consecutive step starts and
-    the end of the last step (the checkpoint fit() would write afterwards is skipped)."""
-    sparsify = import_reference()
+    bookkeeping) over acts [steps, B, T, D] - on the host (fp32 tensors on the CPU) or, for a
+    same-box GPU figure, on the device the activations live on (the reference then runs its
+    bf16 autocast forward and, with triton=True, its Triton decoder) - and returns the seconds
+    of every step after the first `warmup_steps`, measured between consecutive step starts
+    (after a device synchronisation for CUDA activations) and the end of the last step (the
+    checkpoint fit() would write afterwards is skipped)."""
+    sparsify = import_reference(triton=triton)
     from sparsify import SparseCoderConfig, TrainConfig, Trainer
     if threads:
         torch.set_num_threads(threads)
@@ -168,7 +178,11 @@ def time_reference_trainer(acts: torch.Tensor, *, num_latents: int, k: int, warm
         done = []
         # fit() ends by writing a checkpoint (weights and optimiser state: gigabytes at full width);
         # that write is not part of a step, so this instance records the time instead of saving
-        trainer.save = lambda: done.append(time.perf_counter())
+        def finished():
+            if acts.is_cuda:
+                torch.cuda.synchronize(acts.device)
+            done.append(time.perf_counter())
+        trainer.save = finished
         trainer.fit()
     stamps = model.stamps + done[:1]
     per_step = [b - a for a, b in zip(stamps[:-1], stamps[1:])]
