@@ -4,8 +4,8 @@ FVU, with a hand-scheduled backward.
 It computes what SparseCoder.forward composes from `fused_encoder`,
 `decoder_impl` and elementwise torch ops (sparsify/sparse_coder.py:205-271 with
 sparsify/fused_encoder.py:52-87 and sparsify/xformers.py:139-185 behind it), for
-the common case - no Multi-TopK, inputs that need no gradient; AuxK and the
-skip connection in the bf16 / mixed precisions - in fewer passes over memory:
+the common case - inputs that need no gradient; AuxK, the skip connection and
+Multi-TopK in the bf16 / mixed precisions - in fewer passes over memory:
 
 * `x - b_dec` and the bf16 cast are one kernel;
 * the residual e = y - out and its squared sum are one kernel; the gradient of
@@ -18,7 +18,11 @@ skip connection in the bf16 / mixed precisions - in fewer passes over memory:
   and applied by one kernel that also projects, normalises and refreshes the
   bf16 copies, so the dense [M, D] gradients never exist;
 * the encoder's input gradient is never gathered: its column sum, which is all
-  that b_dec needs, equals W_enc^T grad_b_enc.
+  that b_dec needs, equals W_enc^T grad_b_enc;
+* Multi-TopK (sparsify/sparse_coder.py:256-262) selects the top 4k once in the encoder
+  kernel (the top k is its leading part), decodes the k and the 4k set, and hands both
+  losses' weight gradients over as one sparse problem over a virtual batch of 2N tokens
+  (see `_multi_topk_factors`).
 """
 
 from __future__ import annotations
@@ -55,12 +59,16 @@ class FusedSaeStep(torch.autograd.Function):
         # that the exchange runs under the encoder GEMM instead of in front of the update.
         early = None
         shard = getattr(sae, "_shard", None)
+        multi = bool(cfg.multi_topk)
         if (shard is not None and sae.defer_weight_update and ctx.needs_input_grad[2] and ctx.needs_input_grad[4]
-                and not getattr(sae, "ragged_tokens", False) and sae.precision == "bf16"):
+                and not getattr(sae, "ragged_tokens", False) and sae.precision == "bf16" and not multi):
             early = {"vecB": _start_all_gather(xe, shard[1])}
         sae._early = early
         w_enc_src = sae.shadow("encoder.weight") if lowp else W_enc.detach()
-        if cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
+        if multi:
+            # the top 4k in descending order; its first k columns are the top k
+            acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), 4 * k)
+        elif cfg.activation == "topk" and lowp and ops.tc_encode_supported(D, M, k):
             acts, idx = ops.encode_topk_tc(xe, w_enc_src, b_enc.detach(), k)
         elif cfg.activation == "groupmax" and lowp and ops.tc_groupmax_supported(D, M, k):
             acts, idx = ops.encode_groupmax_tc(xe, w_enc_src, b_enc.detach(), k)
@@ -82,7 +90,21 @@ class FusedSaeStep(torch.autograd.Function):
         # exchanged in that form); AuxK and the other precisions need it in fp32.
         e16_only = sae.precision == "bf16" and num_dead == 0
         ctx.skip = None
-        if W_skip is None and D % 4 == 0:
+        ctx.multi = None
+        multi_fvu = None
+        if multi:
+            # FVU on the leading k, Multi-TopK FVU on all 4k; the returned reconstruction, activations
+            # and indices are the 4k ones, as in the reference
+            lp = sae.precision == "bf16"
+            idx_k, acts_k = idx[:, :k].contiguous(), acts[:, :k].contiguous()
+            _, ek32, ek16, sse_k = ops.decode_residual(idx_k, acts_k, w_dec_src, b_dec.detach(), target,
+                                                       want_out=False, want_e32=not lp, want_e16=lp)
+            out, e, e16, sse = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target,
+                                                   want_e32=not lp, want_e16=lp)
+            multi_fvu = sse / tv
+            sse = sse_k
+            ctx.multi = (ek16 if lp else ek32,)
+        elif W_skip is None and D % 4 == 0:
             # decode, residual and its squared sum in one pass
             out, e, e16, sse = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target,
                                                    want_e32=not e16_only, want_e16=sae.precision == "bf16")
@@ -138,13 +160,17 @@ class FusedSaeStep(torch.autograd.Function):
         ctx.sae = sae
         ctx.set_materialize_grads(False)
         ctx.mark_non_differentiable(idx)
-        return out, acts, idx, fvu, auxk
+        if multi_fvu is None:
+            multi_fvu = fvu.new_zeros(())
+        return out, acts, idx, fvu, auxk, multi_fvu
 
     @staticmethod
-    def backward(ctx, g_out, g_acts, g_idx, g_fvu, g_auxk):
+    def backward(ctx, g_out, g_acts, g_idx, g_fvu, g_auxk, g_multi=None):
         xe, idx, acts, e, tv = ctx.saved_tensors
         M, D, k = ctx.shape
         dev = e.device
+        if ctx.multi is not None:
+            return FusedSaeStep._backward_multi_topk(ctx, g_out, g_acts, g_fvu, g_multi)
         # d fvu / d out = -2 e / tv
         s = (-2.0 * g_fvu / tv).to(torch.float32) if g_fvu is not None else torch.zeros((), device=dev)
         if g_out is not None:
@@ -226,6 +252,66 @@ class FusedSaeStep(torch.autograd.Function):
         return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None, None, None, g_W_skip
 
 
+    @staticmethod
+    def _backward_multi_topk(ctx, g_out, g_acts, g_fvu, g_multi):
+        """loss = g_fvu * FVU(top k) + g_multi * FVU(top 4k). In the reference the 4k activations are
+        taken from `pre_acts`, whose gradient FusedEncoder.backward drops
+        (sparsify/fused_encoder.py:52-87): the Multi-TopK term reaches W_dec and b_dec only, the
+        encoder learns from the top-k term alone. With r4 = s4 * e4 (+ a gradient arriving through
+        the returned reconstruction) and rk = sk * ek (s = -2 g / total variance):
+          grad acts[n, j]  = rk[n] . W_dec[idx[n, j]]                     for j < k only
+          grad W_dec[m]    = sum over (n, j) with idx = m of acts[n, j] (r4[n] + [j < k] rk[n])
+          grad W_enc[m]    = sum of grad acts[n, j] x'[n],   grad b_enc[m] = sum of grad acts[n, j]
+        The two vectors per token (r4 for the entries j >= k, u = r4 + rk for j < k) make this one
+        sparse problem over 2N virtual tokens with 3k entries each: token n holds the entries
+        j >= k with vector e4 (scale folded into the coefficients), token N + n the entries j < k
+        (padded with invalid indices, which the CSR build skips) with vector u."""
+        xe, idx, acts, e4, tv = ctx.saved_tensors
+        (ek,) = ctx.multi
+        M, D, k = ctx.shape
+        dev = e4.device
+        N = idx.shape[0]
+        zero = torch.zeros((), device=dev)
+        s4 = (-2.0 * g_multi / tv).to(torch.float32) if g_multi is not None else zero
+        sk = (-2.0 * g_fvu / tv).to(torch.float32) if g_fvu is not None else zero
+        lp = e4.dtype == torch.bfloat16
+        if g_out is not None:  # general case: materialise the 4k residual with its incoming gradient
+            r4 = torch.addcmul(g_out.to(torch.float32), e4.to(torch.float32), s4)
+            r4 = r4.to(torch.bfloat16) if lp else r4
+            vec4, scale4 = r4, torch.ones((), device=dev)
+        else:
+            vec4, scale4 = e4, s4
+        idx_k = idx[:, :k].contiguous()
+        gacts_k = ops.embedding_bag_bwd_acts(idx_k, ek, ctx.w_dec_src) * sk   # [N, k]
+        u = (vec4.to(torch.float32) * scale4).add_(ek.to(torch.float32) * sk)
+        u = u.to(torch.bfloat16) if lp else u
+        pad_i = idx.new_full((N, 2 * k), -1)
+        pad_f = acts.new_zeros((N, 2 * k))
+        idx_v = torch.cat([idx[:, k:], torch.cat([idx_k, pad_i], dim=1)])
+        coefA_v = torch.cat([acts[:, k:] * scale4, torch.cat([acts[:, :k], pad_f], dim=1)])
+        coefB_v = torch.cat([acts.new_zeros((N, 3 * k)), torch.cat([gacts_k, pad_f], dim=1)])
+        vecA_v = torch.cat([vec4, u])
+        vecB_v = torch.cat([xe, xe])
+        kv = 3 * k
+        row_ptr, entries = ops.csr_build(idx_v, M)
+        sae = ctx.sae
+        if sae._pending is not None:
+            sae.materialize_pending()
+        if sae.defer_weight_update and ctx.needs_input_grad[2] and ctx.needs_input_grad[4]:
+            sae._pending = dict(row_ptr=row_ptr, entries=entries, k=kv, idx=idx_v, coefA=coefA_v, vecA=vecA_v,
+                                coefB=coefB_v, vecB=vecB_v, extra=None)
+            g_W_dec = g_W_enc = None
+            g_b_enc = ops.csr_segment_sum(row_ptr, entries, coefB_v, M)
+        else:
+            res = ops.rows_accumulate(row_ptr, entries, kv, M, D, coefA_v, vecA_v, coefB=coefB_v, vecB=vecB_v,
+                                      biasB=True)
+            g_W_dec, g_W_enc, g_b_enc = res["gradA"], res["gradB"], res["gbiasB"]
+        g_b_dec = ops.weighted_colsum(vec4) * scale4 + ops.weighted_colsum(ek) * sk
+        if not ctx.transcode:
+            g_b_dec = g_b_dec - ops.weighted_colsum(ctx.w_enc_src, g_b_enc)
+        return None, None, g_W_enc, g_b_enc, g_W_dec, g_b_dec, None, None, None, None
+
+
 def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
     """The fused function covers the common training case; everything else runs
     the composed path in SparseCoder.forward."""
@@ -233,7 +319,9 @@ def fused_supported(sae, x: Tensor, num_dead: int) -> bool:
         x.is_cuda
         and sae.W_dec is not None
         and (sae.W_skip is None or (sae._lowp() and x.shape[-1] % 8 == 0))
-        and not sae.cfg.multi_topk
+        and (not sae.cfg.multi_topk
+             or (sae.cfg.activation == "topk" and sae._lowp() and num_dead == 0 and sae.W_skip is None
+                 and ops.tc_encode_supported(x.shape[-1], sae.num_latents, 4 * sae.cfg.k)))
         and (num_dead == 0 or (sae._lowp() and x.shape[-1] % 8 == 0))
         and not x.requires_grad
         and x.shape[-1] % 4 == 0

@@ -242,10 +242,10 @@ class SparseCoder(nn.Module):
     ) -> ForwardOutput:
         num_dead = self._count_dead(dead_mask)
         if self.fused and fused_supported(self, x, num_dead):
-            sae_out, top_acts, top_indices, fvu, auxk_loss = FusedSaeStep.apply(
+            sae_out, top_acts, top_indices, fvu, auxk_loss, multi_topk_fvu = FusedSaeStep.apply(
                 x, y, self.encoder.weight, self.encoder.bias, self.W_dec, self.b_dec, self, dead_mask, num_dead,
                 self.W_skip)
-            return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, fvu.new_zeros(()))
+            return ForwardOutput(sae_out, top_acts, top_indices, fvu, auxk_loss, multi_topk_fvu)
         # Multi-TopK alone needs no dense pre-activations: the encoder kernel selects
         # the top 4k once and the top k is its leading part.
         wide_k = 4 * self.cfg.k if self.cfg.multi_topk and self.cfg.activation == "topk" else 0

@@ -350,6 +350,41 @@ def test_multi_topk_bf16_vs_oracle(cuda_lib):
         assert rel_l2(gt, ref.grads[pname]) < 1e-2, (pname, rel_l2(gt, ref.grads[pname]))
 
 
+@pytest.mark.parametrize("precision", ["mixed", "bf16"])
+def test_multi_topk_sparse_update_matches_dense_path(cuda_lib, precision):
+    """Multi-TopK in the fused step: its two losses' weight gradients handed to sc_rows_adam as one
+    sparse problem (a virtual batch of 2N tokens) against the same step with dense gradients."""
+    from sparsify_b200 import SparseCoder, SparseCoderConfig
+    from sparsify_b200.optim import FusedAdam
+    N, D, M, k = 512, 256, 4096, 16
+    g = torch.Generator().manual_seed(31)
+    xs = [torch.randn(N, D, generator=g).cuda() for _ in range(3)]
+    models = []
+    for sparse in (False, True):
+        torch.manual_seed(0)
+        sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=k, multi_topk=True), device="cuda", dtype=torch.float32)
+        sae.precision = precision
+        opt = FusedAdam(sae.parameters(), lr=1e-3)
+        sae.attach_optimizer(opt)
+        if sparse:
+            assert opt.enable_sparse_update(sae)
+        for x in xs:
+            sae.set_decoder_norm_to_unit_norm()
+            out = sae(x)
+            assert out.latent_indices.shape == (N, 4 * k) and float(out.multi_topk_fvu) > 0
+            (out.fvu + out.multi_topk_fvu / 8).backward()
+            if sparse:
+                assert sae.W_dec.grad is None and sae._pending is not None
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        sae.set_decoder_norm_to_unit_norm()
+        models.append(sae)
+    a, b = models
+    tol = 1e-5 if precision == "mixed" else 2e-4
+    for (n1, p1), (_, p2) in zip(a.named_parameters(), b.named_parameters()):
+        assert rel_l2(p2.detach(), p1.detach()) < tol, (n1, rel_l2(p2.detach(), p1.detach()))
+
+
 def test_training_steps_are_reproducible_bit_for_bit(cuda_lib):
     """Three fused training steps run twice from the same state give identical bits: the
     reference's scatter (atomics, xformers.py:132-136, fused_encoder.py:77-82) does not,
