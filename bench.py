@@ -735,7 +735,8 @@ def run_ours(a):
     secondary = {}
     if not a.no_secondary and not (a.transcode or a.multi_topk or a.dead_frac > 0):
         peaks = measured_peaks()
-        variants = [("auxk_active", dict(dead_frac=0.05)), ("transcoder_k64_skip", dict(transcode=True, k=64))]
+        variants = [("auxk_active", dict(dead_frac=0.05)), ("transcoder_k64_skip", dict(transcode=True, k=64)),
+                    ("multi_topk", dict(multi_topk=True))]
         for name, over in variants:
             b = copy.copy(a)
             for key, val in over.items():
