@@ -74,9 +74,10 @@ def parse_args():
     ap.add_argument("--reserve-sms", type=int, default=4,
                     help="SMs the persistent kernels leave free for NCCL's kernels when several ranks run "
                          "(measured at 8 GPUs: 23.6 ms per step with 4, 24.0 ms with 0); ignored on one GPU")
-    ap.add_argument("--cta-pairs", type=int, default=0,
-                    help="1: the tensor-core encoder runs as CTA pairs (tcgen05 cta_group::2); 0 (default): one CTA "
-                         "per work unit (measured faster under the power cap: 14.2 against 15.5 ms per launch)")
+    ap.add_argument("--cta-pairs", type=int, default=-1,
+                    help="1: the tensor-core encoder runs as CTA pairs (tcgen05 cta_group::2); 0: one CTA per work "
+                         "unit; -1 (default): the library chooses per shape (one CTA at k=32, where it measured "
+                         "14.2 against 15.5 ms per launch; pairs for wide top-k lists)")
     ap.add_argument("--modules", type=int, default=0,
                     help="secondary workload: this many hookpoints per rank, each with its own sparse coder "
                          "trained by Muon on activations gathered from every rank (distribute_modules); "
@@ -1138,9 +1139,9 @@ def run_kernel(a):
 
 if __name__ == "__main__":
     args = parse_args()
-    if args.impl == "ours" and args.cta_pairs:
+    if args.impl == "ours" and args.cta_pairs >= 0:
         from sparsify_b200 import ops as _ops_cfg
-        _ops_cfg.set_cta_pairs(True)
+        _ops_cfg.set_cta_pairs(bool(args.cta_pairs))
     if args.kernel:
         run_kernel(args)
     elif args.modules:

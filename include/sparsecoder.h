@@ -51,10 +51,12 @@ int sc_version(void);
  * (0 <= n <= 64), e.g. for the kernels of a communication library that should
  * run concurrently. Process-wide; set it before sizing workspaces. */
 int sc_set_reserved_sms(int n);
-/* on != 0 makes the tensor-core encoder (sc_encode_topk, sc_encode_groupmax) run as
- * pairs of CTAs on the two SMs of a TPC (tcgen05 cta_group::2: one 256-row tile
- * per pair, each CTA loading its own operands with its own loads); the default is
- * one CTA per tile, which measured faster under the B200's power cap.
+/* Form of the tensor-core encoder (sc_encode_topk, sc_encode_groupmax): one CTA per
+ * 128-row tile, or pairs of CTAs on the two SMs of a TPC sharing a 256-row tile
+ * (tcgen05 cta_group::2, each CTA loading its own operands with its own loads).
+ * on < 0 (default): chosen per shape - pairs when the top-k lists leave the one-CTA
+ * form fewer than four operand stages (k above about 40), else one CTA, which
+ * measured faster under the B200's power cap; on = 0 / 1 forces one form.
  * Process-wide; set it before sizing workspaces. Results are identical. */
 int sc_set_cta_pairs(int on);
 /* Copies the last error message (NUL-terminated) into buf; returns its length. */

@@ -14,12 +14,12 @@ char g_err[512] = "";
 
 namespace {
 std::atomic<int> g_reserved_sms{0};
-std::atomic<int> g_cta_pairs{0};
+std::atomic<int> g_cta_pairs{-1};  // -1: chosen per shape, 0: never, 1: always
 }  // namespace
 
 namespace sc {
 int reserved_sms() { return g_reserved_sms.load(std::memory_order_relaxed); }
-bool cta_pairs() { return g_cta_pairs.load(std::memory_order_relaxed) != 0; }
+int cta_pairs_mode() { return g_cta_pairs.load(std::memory_order_relaxed); }
 
 int fail(int status, const char* fmt, ...) {
   std::lock_guard<std::mutex> lock(g_err_mutex);
@@ -40,7 +40,7 @@ extern "C" int sc_set_reserved_sms(int n) {
 }
 
 extern "C" int sc_set_cta_pairs(int on) {
-  g_cta_pairs.store(on != 0, std::memory_order_relaxed);
+  g_cta_pairs.store(on < 0 ? -1 : (on != 0 ? 1 : 0), std::memory_order_relaxed);
   return SC_OK;
 }
 

@@ -17,8 +17,9 @@ int fail(int status, const char* fmt, ...);
 // communication library's kernels that have to run beside them.
 int reserved_sms();
 
-// Whether the tensor-core encoder runs as CTA pairs (sc_set_cta_pairs; default off).
-bool cta_pairs();
+// Form of the tensor-core encoder (sc_set_cta_pairs): -1 chosen per shape (default), 0 one CTA
+// per tile, 1 CTA pairs.
+int cta_pairs_mode();
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 

@@ -19,7 +19,9 @@
 // d=4096, 131072 latents, 16384 tokens, back to back under the 1000 W power cap: the
 // pair form needs 4 % fewer SM cycles but more energy per launch (15.3 J against
 // 14.0 J), the clock settles lower (1147 against 1312 MHz) and the launch takes 15.5 ms
-// against 14.2 ms - so the one-CTA form is the default. Results are identical.
+// against 14.2 ms - so the one-CTA form is the default for k = 32. Wide lists (k = 64,
+// k = 128 for Multi-TopK) leave the one-CTA form fewer than four 48 KB stages; there the
+// pair form is chosen, see make_plan. Results are identical.
 //
 // A per-row lower bound on the k-th largest value (`tau`) is published after
 // every finished strip and read at the start of later strips of the same rows:
@@ -583,7 +585,21 @@ topk_merge_kernel(const float* __restrict__ cand_vals, const int32_t* __restrict
 }
 
 int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols = 0) {
-  const int cg = sc::cta_pairs() ? 2 : 1;
+  const int kl = group_cols > 0 ? 1 : k;  // groupmax keeps no lists
+  const size_t lists_val = (size_t)BM * kl * sizeof(float);
+  const size_t lists_idx = (size_t)BM * kl * sizeof(uint16_t);
+  const size_t groups = (size_t)(kl + 7) / 8;
+  const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
+  const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
+  const size_t smem_limit = 227 * 1024;
+  // Form: forced by sc_set_cta_pairs, else chosen by what the lists leave for the operand ring.
+  // With four 48 KB stages (k up to ~40) the one-CTA form is the faster one under the power
+  // cap; wider lists leave it three stages (k = 64) or two (k = 128), and the pair form, whose
+  // stages are 32 KB, then wins: 14.0 against 15.2 ms at k = 64, 16.3 against 21.6 ms at k = 128
+  // (d = 4096, 131072 latents, 16384 tokens).
+  const int mode = sc::cta_pairs_mode();
+  const int single_stages = fixed + stage_bytes(1) <= smem_limit ? (int)((smem_limit - fixed) / stage_bytes(1)) : 0;
+  const int cg = mode == 1 ? 2 : mode == 0 ? 1 : (single_stages < 4 ? 2 : 1);
   pl->cg = cg;
   pl->n_rb = (int)((N + BM * cg - 1) / (BM * cg));
   pl->n_ct = (int)((M + BN - 1) / BN);
@@ -608,13 +624,6 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols =
   }
   pl->n_strips = best < 1 ? 1 : best;
   pl->units = pl->n_rb * pl->n_strips;
-  const int kl = group_cols > 0 ? 1 : k;  // groupmax keeps no lists
-  const size_t lists_val = (size_t)BM * kl * sizeof(float);
-  const size_t lists_idx = (size_t)BM * kl * sizeof(uint16_t);
-  const size_t groups = (size_t)(kl + 7) / 8;
-  const size_t gmin = groups * BM * sizeof(float), gpos = groups * BM * sizeof(uint16_t);
-  const size_t fixed = lists_val + lists_idx + gmin + gpos + 4 * BN * sizeof(float) + 256 /*barriers*/ + 1024 /*align*/;
-  const size_t smem_limit = 227 * 1024;
   const size_t stage = stage_bytes(cg);
   if (fixed + 2 * stage > smem_limit) return SC_ERR_UNSUPPORTED;
   int stages = (int)((smem_limit - fixed) / stage);

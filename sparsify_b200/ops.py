@@ -176,10 +176,10 @@ def set_reserved_sms(n: int) -> None:
     call("sc_set_reserved_sms", int(n))
 
 
-def set_cta_pairs(on: bool) -> None:
-    """Tensor-core encoder as CTA pairs (tcgen05 cta_group::2) or, the default, single CTAs; see
-    sc_set_cta_pairs."""
-    call("sc_set_cta_pairs", int(bool(on)))
+def set_cta_pairs(on: bool | None) -> None:
+    """Form of the tensor-core encoder: True = CTA pairs (tcgen05 cta_group::2), False = one CTA per
+    tile, None = chosen per shape (the default); see sc_set_cta_pairs."""
+    call("sc_set_cta_pairs", -1 if on is None else int(bool(on)))
 
 
 def tc_encode_supported(D: int, M: int, k: int) -> bool:

@@ -202,13 +202,14 @@ def test_encoder_tc_cta_pair_form(cuda_lib, N, D, M, k):
     x = bf16_round(torch.randn(N, D, generator=g)).cuda().bfloat16()
     W = bf16_round(torch.randn(M, D, generator=g) / D ** 0.5).cuda().bfloat16()
     b = (0.1 * torch.randn(M, generator=g)).cuda()
-    vals1, idx1 = ops.encode_topk_tc(x, W, b, k)
-    ops.set_cta_pairs(True)
     try:
+        ops.set_cta_pairs(False)
+        vals1, idx1 = ops.encode_topk_tc(x, W, b, k)
+        ops.set_cta_pairs(True)
         vals2, idx2 = ops.encode_topk_tc(x, W, b, k)
         torch.cuda.synchronize()
     finally:
-        ops.set_cta_pairs(False)
+        ops.set_cta_pairs(None)  # back to the per-shape choice
     ops.check_status(x.device)
     pre = O.preacts(x.cpu().double(), W.cpu().double(), b.cpu().double()).float()
     check_topk_sets(vals1, idx1, pre, k)
