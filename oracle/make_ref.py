@@ -3,7 +3,7 @@
     python oracle/make_ref.py [/path/to/sparsify-checkout]
 
 Copies the `sparsify/` package directory of a checkout of EleutherAI/sparsify
-v1.3.0 (default: $SPARSIFY_REF, else /root/reference) into `oracle/_ref/sparsify/`,
+v1.3.0 (the argument, else $SPARSIFY_REF) into `oracle/_ref/sparsify/`,
 unmodified. `oracle/_ref/` is git-ignored - the reference's sources never enter this
 repository's history - but it sits inside the working tree, so it is present
 wherever the tree is copied to after this script ran (like the compiled kernel
@@ -22,11 +22,11 @@ DEST = HERE / "_ref"
 
 
 def make_ref(src: str | os.PathLike | None = None, quiet: bool = False) -> Path | None:
-    candidates = [src, os.environ.get("SPARSIFY_REF"), "/root/reference"]
+    candidates = [src, os.environ.get("SPARSIFY_REF")]
     root = next((Path(c) for c in candidates if c and Path(c, "sparsify", "fused_encoder.py").exists()), None)
     if root is None:
         if not quiet:
-            print("make_ref: no reference checkout found (argument, $SPARSIFY_REF, /root/reference)", file=sys.stderr)
+            print("make_ref: no reference checkout found (argument or $SPARSIFY_REF)", file=sys.stderr)
         return DEST if (DEST / "sparsify" / "fused_encoder.py").exists() else None
     target = DEST / "sparsify"
     DEST.mkdir(exist_ok=True)
