@@ -84,7 +84,7 @@ def parse_args():
                          "--tokens is then the tokens per hookpoint per step over all ranks")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone on random inputs of the given sizes instead of the step: "
-                         "encode | decode | bwd_acts | csr | rows | rows_adam | adam | normalize | all | ns | gemm")
+                         "encode | decode | bwd_acts | csr | rows | topk_mask | rows_adam | adam | normalize | all | ns | gemm")
     return ap.parse_args()
 
 
@@ -1106,6 +1106,14 @@ def run_kernel(a):
         nbytes = 2 * M * D * 4 + N * D * 4 + N * D * 2 + N * k * 12
         results.append(dict(kernel="rows_accumulate", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
         del out
+    if which in ("topk_mask", "all"):
+        # the AuxK selection: the 2048 largest of 6560 post-ReLU pre-activations per token, written back densely
+        nd, k_aux = 6560, 2048
+        P = torch.relu(torch.randn(N, nd, device=dev, generator=g))
+        ms = timed(lambda: ops.topk_mask_rows(P, k_aux))
+        nbytes = N * nd * 6
+        results.append(dict(kernel="topk_mask_rows", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+        del P
     if which in ("rows_adam", "all"):
         # the fused sparse update of both matrices, as the training step launches it (one launch per matrix)
         row_ptr, entries = ops.csr_build(idx, M)

@@ -108,11 +108,17 @@ __device__ __forceinline__ uint32_t order_key(float v) {
 }
 
 constexpr int kSelThreads = 512;
+constexpr int64_t kSelCacheMax = 40960;  // rows of up to this many columns keep their keys in shared memory
 
+// One CTA per row, four 8-bit digit passes over the row's keys, then one pass that emits.
+// Post-ReLU rows are full of equal values (zeros), so every shared-memory atomic is aggregated
+// per warp first (threads with the same digit elect one to add their count), and rows that
+// fit keep their keys in shared memory, so that global memory is read once.
 __global__ void __launch_bounds__(kSelThreads)
 topk_rows_kernel(const float* __restrict__ pre, int64_t M, int k,
                  const uint8_t* __restrict__ col_mask, float* __restrict__ top_vals,
-                 int64_t* __restrict__ top_idx, __nv_bfloat16* __restrict__ dense_out) {
+                 int64_t* __restrict__ top_idx, __nv_bfloat16* __restrict__ dense_out, int cache_keys) {
+  extern __shared__ uint32_t s_keys[];  // [M] when cache_keys
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_need, s_out, s_eq;
   const float* row = pre + (int64_t)blockIdx.x * M;
@@ -121,25 +127,58 @@ topk_rows_kernel(const float* __restrict__ pre, int64_t M, int k,
   float* ov = dense_out == nullptr ? top_vals + (int64_t)blockIdx.x * k : nullptr;
   int64_t* oi = dense_out == nullptr ? top_idx + (int64_t)blockIdx.x * k : nullptr;
   __nv_bfloat16* od = dense_out == nullptr ? nullptr : dense_out + (int64_t)blockIdx.x * M;
+  const int lane = threadIdx.x & 31;
+  const unsigned lanes_below = (1u << lane) - 1u;
+
+  auto key_at = [&](int64_t c, bool first) -> uint32_t {
+    if (cache_keys && !first) return s_keys[c];
+    const uint32_t key = (col_mask == nullptr || col_mask[c]) ? order_key(row[c]) : 0u;
+    if (cache_keys) s_keys[c] = key;
+    return key;
+  };
 
   uint32_t prefix = 0, prefix_mask = 0, need = (uint32_t)k;
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (int64_t c = threadIdx.x; c < M; c += blockDim.x) {
-      uint32_t key = (col_mask == nullptr || col_mask[c]) ? order_key(row[c]) : 0u;
-      if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+    for (int64_t base = 0; base < M; base += blockDim.x) {  // whole warps stay together
+      const int64_t c = base + threadIdx.x;
+      bool active = false;
+      uint32_t digit = 0;
+      if (c < M) {
+        const uint32_t key = key_at(c, shift == 24);
+        active = (key & prefix_mask) == prefix;
+        digit = (key >> shift) & 0xffu;
+      }
+      const unsigned act = __ballot_sync(0xffffffffu, active);
+      if (active) {
+        const unsigned peers = __match_any_sync(act, digit);
+        if (lane == __ffs(peers) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
+      }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t cum = 0;
-      int d = 255;
-      for (; d > 0; --d) {
-        if (cum + hist[d] >= need) break;
-        cum += hist[d];
+    if (threadIdx.x < 32) {
+      // Which digit holds the need-th largest key: lane l owns bins 8l .. 8l+7; a suffix scan over the
+      // lanes finds the one lane whose bins straddle `need`, which then walks its eight bins.
+      uint32_t h[8], mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { h[j] = hist[lane * 8 + j]; mine += h[j]; }
+      uint32_t at_or_above = mine;  // becomes the count in this lane's bins and all higher ones
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_down_sync(0xffffffffu, at_or_above, o);
+        if (lane + o < 32) at_or_above += t;
       }
-      s_prefix = prefix | ((uint32_t)d << shift);
-      s_need = need - cum;  // still to take among keys sharing the longer prefix
+      uint32_t cum = at_or_above - mine;  // keys in higher bins than this lane's
+      if (cum < need && need <= at_or_above) {
+        int d = 7;
+        for (; d > 0; --d) {
+          if (cum + h[d] >= need) break;
+          cum += h[d];
+        }
+        s_prefix = prefix | ((uint32_t)(lane * 8 + d) << shift);
+        s_need = need - cum;  // still to take among keys sharing the longer prefix
+      }
     }
     __syncthreads();
     prefix = s_prefix;
@@ -151,18 +190,48 @@ topk_rows_kernel(const float* __restrict__ pre, int64_t M, int k,
   // equal to it belong to the result.
   if (threadIdx.x == 0) { s_out = 0; s_eq = 0; }
   __syncthreads();
-  for (int64_t c = threadIdx.x; c < M; c += blockDim.x) {
-    float v = row[c];
-    uint32_t key = (col_mask == nullptr || col_mask[c]) ? order_key(v) : 0u;
-    bool take = key > prefix;
-    if (!take && key == prefix) take = atomicAdd(&s_eq, 1u) < need;
+  for (int64_t base = 0; base < M; base += blockDim.x) {
+    const int64_t c = base + threadIdx.x;
+    const bool valid = c < M;
+    float v = 0.f;
+    uint32_t key = 0u;
+    if (valid) {
+      v = row[c];
+      key = cache_keys ? s_keys[c] : ((col_mask == nullptr || col_mask[c]) ? order_key(v) : 0u);
+    }
+    bool take = valid && key > prefix;
+    // ties with the k-th value: one shared counter, advanced once per warp
+    const bool eq = valid && key == prefix;
+    const unsigned eq_mask = __ballot_sync(0xffffffffu, eq);
+    if (eq_mask != 0u) {
+      uint32_t first = 0;
+      if (lane == __ffs(eq_mask) - 1) first = atomicAdd(&s_eq, (uint32_t)__popc(eq_mask));
+      first = __shfl_sync(0xffffffffu, first, __ffs(eq_mask) - 1);
+      if (eq) take = first + (uint32_t)__popc(eq_mask & lanes_below) < need;
+    }
     if (od != nullptr) {
-      od[c] = __float2bfloat16_rn(take ? v : 0.f);
-    } else if (take) {
-      uint32_t slot = atomicAdd(&s_out, 1u);
-      if (slot < (uint32_t)k) { ov[slot] = v; oi[slot] = c; }
+      if (valid) od[c] = __float2bfloat16_rn(take ? v : 0.f);
+    } else {
+      const unsigned take_mask = __ballot_sync(0xffffffffu, take);
+      if (take_mask != 0u) {
+        uint32_t first = 0;
+        if (lane == __ffs(take_mask) - 1) first = atomicAdd(&s_out, (uint32_t)__popc(take_mask));
+        first = __shfl_sync(0xffffffffu, first, __ffs(take_mask) - 1);
+        const uint32_t slot = first + (uint32_t)__popc(take_mask & lanes_below);
+        if (take && slot < (uint32_t)k) { ov[slot] = v; oi[slot] = c; }
+      }
     }
   }
+}
+
+int launch_topk_rows(const float* pre, int64_t N, int64_t M, int k, const uint8_t* col_mask, float* top_vals,
+                     int64_t* top_idx, __nv_bfloat16* dense_out, cudaStream_t st) {
+  const int cache = M <= kSelCacheMax ? 1 : 0;
+  const size_t smem = cache ? (size_t)M * sizeof(uint32_t) : 0;
+  if (smem > 48 * 1024)
+    SC_CUDA(cudaFuncSetAttribute(topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_rows_kernel<<<(unsigned)N, kSelThreads, smem, st>>>(pre, M, k, col_mask, top_vals, top_idx, dense_out, cache);
+  return SC_OK;
 }
 
 // ---- groupmax ---------------------------------------------------------------
@@ -260,8 +329,8 @@ extern "C" int sc_topk_rows(const float* pre, int64_t N, int64_t M, int k,
   if (N == 0) return SC_OK;
   SC_REQUIRE(pre && top_vals && top_idx, "sc_topk_rows: null pointer");
   SC_REQUIRE(N <= 0x7fffffffLL, "sc_topk_rows: N too large");
-  topk_rows_kernel<<<(unsigned)N, kSelThreads, 0, sc::as_stream(stream)>>>(pre, M, k, col_mask,
-                                                                          top_vals, top_idx, nullptr);
+  int rc = launch_topk_rows(pre, N, M, k, col_mask, top_vals, top_idx, nullptr, sc::as_stream(stream));
+  if (rc != SC_OK) return rc;
   SC_CHECK_LAUNCH("sc_topk_rows");
   return SC_OK;
 }
@@ -273,8 +342,9 @@ extern "C" int sc_topk_mask_rows(const float* pre, int64_t N, int64_t M, int k, 
   if (N == 0) return SC_OK;
   SC_REQUIRE(pre && out_bf16, "sc_topk_mask_rows: null pointer");
   SC_REQUIRE(N <= 0x7fffffffLL, "sc_topk_mask_rows: N too large");
-  topk_rows_kernel<<<(unsigned)N, kSelThreads, 0, sc::as_stream(stream)>>>(
-      pre, M, k, col_mask, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16));
+  int rc = launch_topk_rows(pre, N, M, k, col_mask, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16),
+                            sc::as_stream(stream));
+  if (rc != SC_OK) return rc;
   SC_CHECK_LAUNCH("sc_topk_mask_rows");
   return SC_OK;
 }
