@@ -251,12 +251,21 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+#ifdef SC_DIAG
+      long long wait_empty = 0;  // debug bit 2
+#endif
       for (int u = unit0; u < p.units && ok; u += unit_stride) {
         int rb, strip, t0, t1;
         decode_unit(p, u, rb, strip, t0, t1);
         for (int t = t0; t < t1 && ok; ++t) {
           for (int kc = 0; kc < kc_count; ++kc) {
+#ifdef SC_DIAG
+            const long long w2 = clock64();
+#endif
             if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kWaitEmpty)) { ok = false; break; }
+#ifdef SC_DIAG
+            wait_empty += clock64() - w2;
+#endif
             unsigned char* sa = smem + (size_t)stage * kStageBytes;
             unsigned char* sb = sa + BM * BK * 2;
             if constexpr (CG == 2) {
@@ -274,6 +283,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           }
         }
       }
+#ifdef SC_DIAG
+      if ((p.debug & 4) && p.status != nullptr && blockIdx.x == 0) p.status[6] = (int)(wait_empty >> 10);
+#endif
       if constexpr (CG == 2) {
         // Stay until the leader's last commits have reached this CTA's `empty` barriers: a CTA of
         // a pair must not leave while its peer can still signal its shared memory.
@@ -293,7 +305,7 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       uint32_t acc_phase = 0;
       bool ok = true;
 #ifdef SC_DIAG
-      long long wait_tmem = 0, wait_full = 0;  // debug bit 2
+      long long wait_tmem = 0, wait_full = 0, issue_time = 0;  // debug bit 2
       const long long t_begin = clock64();
 #endif
       for (int u = unit0; u < p.units && ok; u += unit_stride) {
@@ -325,6 +337,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
             const uint64_t adesc = make_smem_desc_sw128(sa);
             const uint64_t bdesc = make_smem_desc_sw128(sa + BM * BK * 2);
+#ifdef SC_DIAG
+            const long long w3 = clock64();
+#endif
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
               // 32 bytes per K step inside the 128-byte swizzle row
@@ -338,6 +353,9 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             // frees the stage (in both CTAs of a pair) once these MMAs have read it
             if constexpr (CG == 2) mma_commit_pair(&empty[stage], 3);
             else mma_commit(&empty[stage]);
+#ifdef SC_DIAG
+            issue_time += clock64() - w3;
+#endif
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
@@ -354,6 +372,7 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         p.status[3] = (int)((clock64() - t_begin) >> 10);
         p.status[4] = (int)(wait_tmem >> 10);
         p.status[5] = (int)(wait_full >> 10);
+        p.status[7] = (int)(issue_time >> 10);  // inside the MMA and commit instructions
       }
 #endif
     }
@@ -628,6 +647,9 @@ int make_plan(int64_t N, int64_t D, int64_t M, int k, Plan* pl, int group_cols =
   if (fixed + 2 * stage > smem_limit) return SC_ERR_UNSUPPORTED;
   int stages = (int)((smem_limit - fixed) / stage);
   if (stages > 8) stages = 8;
+#ifdef SC_MAX_STAGES
+  if (stages > SC_MAX_STAGES) stages = SC_MAX_STAGES;  // diagnostics builds: sensitivity to the ring depth
+#endif
   pl->stages = stages;
   pl->off_lists_val = (size_t)stages * stage;
   pl->off_lists_idx = pl->off_lists_val + lists_val;
