@@ -22,11 +22,12 @@ def _data(rank, step):
     return torch.randn(N, D, generator=g)
 
 
-def _build(device):
+def _build(device, multi_topk=False):
     from sparsify_b200 import SparseCoder, SparseCoderConfig
     from sparsify_b200.optim import FusedAdam
     torch.manual_seed(0)
-    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=K), device=device, dtype=torch.float32)
+    sae = SparseCoder(D, SparseCoderConfig(num_latents=M, k=K, multi_topk=multi_topk), device=device,
+                      dtype=torch.float32)
     opt = FusedAdam(sae.parameters(), lr=1e-3)
     sae.attach_optimizer(opt)
     return sae, opt
@@ -39,17 +40,23 @@ def _dead_mask():
     return m
 
 
-def _worker(rank, world, port, out, auxk):
+def _loss(o):
+    return o.fvu + o.auxk_loss / 32 + o.multi_topk_fvu / 8
+
+
+def _worker(rank, world, port, out, mode):
+    auxk, multi = mode == "auxk", mode == "multi_topk"
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        sae, opt = _build(f"cuda:{rank}")
+        sae, opt = _build(f"cuda:{rank}", multi)
         assert opt.enable_sparse_update(sae) and sae._shard == (rank, world)
         for step in range(STEPS):
             sae.set_decoder_norm_to_unit_norm()
             out_ = sae(_data(rank, step).cuda(), dead_mask=_dead_mask().cuda() if auxk else None)
-            (out_.fvu + out_.auxk_loss / 32).backward()
+            _loss(out_).backward()
+            assert sae.W_dec.grad is None and sae._pending is not None  # the sparse, sharded route
             for p in sae.parameters():
                 if p.grad is not None:
                     dist.all_reduce(p.grad)
@@ -64,22 +71,23 @@ def _worker(rank, world, port, out, auxk):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("auxk", [False, True])
-def test_sharded_sparse_update_matches_single_process(cuda_lib, auxk):
+@pytest.mark.parametrize("mode", ["plain", "auxk", "multi_topk"])
+def test_sharded_sparse_update_matches_single_process(cuda_lib, mode):
+    auxk, multi = mode == "auxk", mode == "multi_topk"
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, port, out, auxk), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, out, mode), nprocs=2, join=True)
 
     # single process: both ranks' batches per step, losses averaged (DDP's mean of gradients)
-    sae, opt = _build("cuda:0")
+    sae, opt = _build("cuda:0", multi)
     for step in range(STEPS):
         sae.set_decoder_norm_to_unit_norm()
         dead = _dead_mask().cuda() if auxk else None
         outs = [sae(_data(r, step).cuda(), dead_mask=dead) for r in range(2)]
-        loss = sum(o.fvu + o.auxk_loss / 32 for o in outs) / 2
+        loss = sum(_loss(o) for o in outs) / 2
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
