@@ -76,7 +76,7 @@ struct Params {
   float* gm_vals;
   int64_t* gm_idx;
 #ifdef SC_DIAG
-  int debug;  // diagnostics build only: bit 0 = epilogue only drains (no bias / top-k work)
+  int debug;  // diagnostics build only: bit 0 = epilogue only drains (no bias / top-k work), bit 3 = reads the accumulator only, bit 4 = stops after the threshold mask
 #endif
   uint32_t off_lists_val, off_lists_idx, off_gmin, off_gpos, off_bias, off_bars;
 };
@@ -441,6 +441,15 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
+#ifdef SC_DIAG
+          if (p.debug & 8) {  // accumulator read only
+            unsigned acc = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc ^= r[i];
+            if (acc == 0x7fc12345u) ++n_cols;
+            continue;
+          }
+#endif
           // Pass 1 (full ILP): add the bias and mark the columns that beat this
           // row's threshold as it stood at chunk start.
           float v[32];
@@ -479,6 +488,12 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
           for (int i = 0; i < 32; ++i) m |= (v[i] > st.thr_cmp ? 1u : 0u) << i;
           if (valid < 32) m &= valid <= 0 ? 0u : ((1u << valid) - 1u);
+#ifdef SC_DIAG
+          if (p.debug & 16) {  // bias and threshold mask only: no candidate is walked or inserted
+            n_cols += __popc(m);
+            continue;
+          }
+#endif
           // Pass 2: every row walks its own marked columns (ascending), so the loop
           // runs as often as the busiest row has candidates, not once per marked column.
           const uint16_t rel0 = (uint16_t)(tile_col0 - strip_col0 + c * 32);
