@@ -1096,6 +1096,16 @@ def run_kernel(a):
         ms = timed(lambda: ops.decode_residual(idx, vals, W, None, yb, want_e16=True))
         nbytes = N * k * D * 2 + N * k * 12 + N * D * (2 + 4 + 2)
         results.append(dict(kernel="decode_residual", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+    if which in ("decode", "all") and ops.decode_dots_supported(W, k):
+        yb = gout.bfloat16()
+        ms = timed(lambda: ops.decode_residual(idx, vals, W, None, yb, want_out=False, want_e16=True, want_dots=True))
+        nbytes = N * k * D * 2 + N * k * 16 + N * D * (2 + 2)
+        results.append(dict(kernel="decode_residual_dots", ms=ms, gbs=nbytes / ms / 1e6, frac=nbytes / ms / 1e6 / peaks["hbm"]))
+        ms = timed(lambda: ops.decode_residual(idx, vals, W, None, yb, want_out=False, want_e16=True))
+        results.append(dict(kernel="decode_residual (no out)", ms=ms))
+        e16 = ops.decode_residual(idx, vals, W, None, yb, want_out=False, want_e16=True)[2]
+        ms = timed(lambda: ops.embedding_bag_bwd_acts(idx, e16, W))
+        results.append(dict(kernel="embedding_bag_bwd_acts (bf16 gradient)", ms=ms))
     if which in ("bwd_acts", "all"):
         ms = timed(lambda: ops.embedding_bag_bwd_acts(idx, gout, W))
         nbytes = N * k * D * 2 + N * D * 4 + N * k * 12

@@ -165,6 +165,20 @@ int sc_decode_residual(const int64_t* idx, const float* acts, const void* W,
                        float* out, float* e_f32, void* e_bf16, float* sse,
                        void* ws, size_t ws_bytes, void* stream);
 
+/* sc_decode_residual that also returns dots[N,k] = dot(e[n,:], W[idx[n,j],:]) from the
+ * same pass over the gathered rows (each row of W is read once): with grad_out = s * e
+ * this is grad_acts / s of sc_embedding_bag_bwd_acts, so the backward of the decode
+ * needs no second gather. The dot uses e as stored: rounded to bf16 when e_bf16 is the
+ * only residual written. Ids outside [0, M) contribute nothing and get dot 0.
+ * W must be bf16, k <= 64, D % 4 == 0; SC_ERR_UNSUPPORTED
+ * otherwise (use the two separate calls).
+ * sparsify/sparse_coder.py:198-202,225,253 and sparsify/xformers.py:125-131. */
+int sc_decode_residual_dots(const int64_t* idx, const float* acts, const void* W,
+                            int w_dtype, const float* bias, const void* y,
+                            int y_dtype, int64_t N, int64_t D, int64_t M, int k,
+                            float* out, float* e_f32, void* e_bf16, float* sse,
+                            float* dots, void* ws, size_t ws_bytes, void* stream);
+
 /* Latent-major CSR of the [N,k] index matrix: row_ptr[M+1], entries[N*k]
  * (flat position n*k+j, ascending inside each latent, whatever its length).
  * ws: sc_csr_workspace_bytes(M) bytes.

@@ -53,6 +53,10 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [P, P, P, c_int, P, P, c_int, I64, I64, I64, c_int, P, P, P, P, P, c_size_t, P],
     ),
+    "sc_decode_residual_dots": (
+        c_int,
+        [P, P, P, c_int, P, P, c_int, I64, I64, I64, c_int, P, P, P, P, P, P, c_size_t, P],
+    ),
     "sc_csr_workspace_bytes": (c_size_t, [I64]),
     "sc_csr_build": (c_int, [P, I64, c_int, I64, P, P, P, c_size_t, P]),
     "sc_csr_build_noalloc": (c_int, [P, I64, c_int, I64, P, P, P]),

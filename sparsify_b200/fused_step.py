@@ -92,22 +92,31 @@ class FusedSaeStep(torch.autograd.Function):
         ctx.skip = None
         ctx.multi = None
         multi_fvu = None
+        dots = None
         if multi:
             # FVU on the leading k, Multi-TopK FVU on all 4k; the returned reconstruction, activations
             # and indices are the 4k ones, as in the reference
             lp = sae.precision == "bf16"
             idx_k, acts_k = idx[:, :k].contiguous(), acts[:, :k].contiguous()
-            _, ek32, ek16, sse_k = ops.decode_residual(idx_k, acts_k, w_dec_src, b_dec.detach(), target,
-                                                       want_out=False, want_e32=not lp, want_e16=lp)
+            with_dots = ops.decode_dots_supported(w_dec_src, k)
+            res_k = ops.decode_residual(idx_k, acts_k, w_dec_src, b_dec.detach(), target, want_out=False,
+                                        want_e32=not lp, want_e16=lp, want_dots=with_dots)
+            _, ek32, ek16, sse_k = res_k[:4]
+            dots = res_k[4] if with_dots else None
             out, e, e16, sse = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target,
                                                    want_e32=not lp, want_e16=lp)
             multi_fvu = sse / tv
             sse = sse_k
             ctx.multi = (ek16 if lp else ek32,)
         elif W_skip is None and D % 4 == 0:
-            # decode, residual and its squared sum in one pass
-            out, e, e16, sse = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target,
-                                                   want_e32=not e16_only, want_e16=sae.precision == "bf16")
+            # decode, residual and its squared sum in one pass - and, where the kernel exists, the
+            # residual's dot product with every gathered row, which is the activation gradient up
+            # to a scalar: the backward then has no second gather of the decoder rows to do
+            with_dots = ops.decode_dots_supported(w_dec_src, k)
+            res = ops.decode_residual(idx, acts, w_dec_src, b_dec.detach(), target, want_e32=not e16_only,
+                                      want_e16=sae.precision == "bf16", want_dots=with_dots)
+            out, e, e16, sse = res[:4]
+            dots = res[4] if with_dots else None
         else:
             out = ops.embedding_bag_fwd(idx, acts, w_dec_src, b_dec.detach())
             if W_skip is not None:
@@ -154,6 +163,7 @@ class FusedSaeStep(torch.autograd.Function):
 
         ctx.save_for_backward(xe, idx, acts, e if e is not None else e16, tv)
         ctx.e16 = e16
+        ctx.dots = dots  # e . W_dec[idx] of the residual as saved (None where it was not computed)
         ctx.w_enc_src, ctx.w_dec_src = w_enc_src, w_dec_src
         ctx.shape = (M, D, k)
         ctx.transcode = cfg.transcode
@@ -179,7 +189,10 @@ class FusedSaeStep(torch.autograd.Function):
         else:
             gout, scale = e, s
 
-        gacts = ops.embedding_bag_bwd_acts(idx, gout, ctx.w_dec_src) * scale
+        if g_out is None and ctx.dots is not None:
+            gacts = ctx.dots * scale  # the forward already dotted the residual with the gathered rows
+        else:
+            gacts = ops.embedding_bag_bwd_acts(idx, gout, ctx.w_dec_src) * scale
         if g_acts is not None:
             gacts = gacts + g_acts
         # ---- AuxK: dense gradient rows for the dead latents, and its share of b_dec ----
@@ -282,7 +295,10 @@ class FusedSaeStep(torch.autograd.Function):
         else:
             vec4, scale4 = e4, s4
         idx_k = idx[:, :k].contiguous()
-        gacts_k = ops.embedding_bag_bwd_acts(idx_k, ek, ctx.w_dec_src) * sk   # [N, k]
+        if ctx.dots is not None:
+            gacts_k = ctx.dots * sk                                               # [N, k], from the forward
+        else:
+            gacts_k = ops.embedding_bag_bwd_acts(idx_k, ek, ctx.w_dec_src) * sk
         u = (vec4.to(torch.float32) * scale4).add_(ek.to(torch.float32) * sk)
         u = u.to(torch.bfloat16) if lp else u
         pad_i = idx.new_full((N, 2 * k), -1)

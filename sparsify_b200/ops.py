@@ -269,9 +269,19 @@ def embedding_bag_bwd_acts(idx: Tensor, grad_out: Tensor, W: Tensor) -> Tensor:
     return gacts
 
 
+def decode_dots_supported(W: Tensor, k: int) -> bool:
+    """Whether `decode_residual(..., want_dots=True)` has a kernel for this case."""
+    D = W.shape[-1]
+    return W.dtype == torch.bfloat16 and k <= 64 and D % 4 == 0
+
+
 def decode_residual(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None, y: Tensor, *,
-                    want_out: bool = True, want_e32: bool = False, want_e16: bool = False):
-    """(out, e_f32, e_bf16, sse): decode, residual e = y - out and sum(e^2) in one pass."""
+                    want_out: bool = True, want_e32: bool = False, want_e16: bool = False,
+                    want_dots: bool = False):
+    """(out, e_f32, e_bf16, sse): decode, residual e = y - out and sum(e^2) in one pass.
+    want_dots=True (see `decode_dots_supported`) appends dots[N, k] = e . W[idx], computed from
+    the same gathered rows: the activation gradient of the decode up to the scalar that turns
+    e into the gradient of the output."""
     _check_cuda(idx, acts, W, bias, y)
     idx, acts = idx.contiguous(), _f32(acts)
     W, y = W.detach().contiguous(), y.detach().contiguous()
@@ -286,6 +296,13 @@ def decode_residual(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None, y
     sse = torch.empty((), dtype=torch.float32, device=dev)
     ws = _ws(_lib.lib().sc_decode_residual_workspace_bytes(N), dev)
     bias32 = _f32(bias)
+    if want_dots:
+        dots = torch.empty(N, k, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            call("sc_decode_residual_dots", ptr(idx), ptr(acts), ptr(W), dtype_code(W), ptr(bias32), ptr(y),
+                 dtype_code(y), N, D, M, int(k), ptr(out), ptr(e32), ptr(e16), ptr(sse), ptr(dots), ptr(ws),
+                 ws.numel(), _stream(W))
+        return out, e32, e16, sse, dots
     with torch.cuda.device(dev):
         call("sc_decode_residual", ptr(idx), ptr(acts), ptr(W), dtype_code(W), ptr(bias32), ptr(y),
              dtype_code(y), N, D, M, int(k), ptr(out), ptr(e32), ptr(e16), ptr(sse), ptr(ws), ws.numel(),

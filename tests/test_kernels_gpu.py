@@ -374,6 +374,45 @@ def test_decode_residual(cuda_lib, ydtype):
     assert rel_l2(gacts16, gacts_ref) < F32_TOL
 
 
+@pytest.mark.parametrize("N,D,M,k,ydtype,both", [
+    (300, 4096, 2048, 32, torch.bfloat16, False),   # the training step's case: bf16 residual only
+    (65, 520, 300, 7, torch.float32, True),         # ragged width, fp32 residual kept
+    (130, 1024, 512, 64, torch.bfloat16, False),    # k > 32: two columns per thread
+    (33, 260, 100, 40, torch.float32, True),        # k > 32, ragged width, fp32 residual kept
+])
+def test_decode_residual_dots(cuda_lib, N, D, M, k, ydtype, both):
+    """sc_decode_residual_dots: the decode / residual outputs equal sc_decode_residual's bit for bit,
+    and the dots equal sc_embedding_bag_bwd_acts on the stored residual (up to summation order) and
+    the fp64 dot products; entries with an id outside [0, M) contribute nothing and get dot 0."""
+    from sparsify_b200 import ops
+    g = torch.Generator().manual_seed(N + k)
+    W = bf16_round(torch.randn(M, D, generator=g))
+    b = torch.randn(D, generator=g)
+    acts = torch.rand(N, k, generator=g)
+    idx = torch.stack([torch.randperm(M, generator=g)[:k] for _ in range(N)])
+    idx[0, 0], idx[N - 1, k - 1] = -1, M          # invalid ids
+    y = torch.randn(N, D, generator=g)
+    if ydtype == torch.bfloat16:
+        y = bf16_round(y)
+    Wc, args = W.cuda().bfloat16(), (idx.cuda(), acts.cuda())
+    assert ops.decode_dots_supported(Wc, k)
+    kw = dict(want_out=both, want_e32=both, want_e16=True)
+    out, e32, e16, sse = ops.decode_residual(*args, Wc, b.cuda(), y.cuda().to(ydtype), **kw)
+    out2, e32b, e16b, sse2, dots = ops.decode_residual(*args, Wc, b.cuda(), y.cuda().to(ydtype), want_dots=True, **kw)
+    assert torch.equal(e16, e16b)
+    if both:
+        assert torch.equal(out, out2) and torch.equal(e32, e32b)
+    assert abs(float(sse) - float(sse2)) <= 1e-6 * float(sse)
+    stored = e32 if both else e16
+    sep = ops.embedding_bag_bwd_acts(args[0], stored, Wc)
+    assert rel_l2(dots, sep) < 1e-5
+    valid = (idx >= 0) & (idx < M)
+    rows = W.double()[idx.clamp(0, M - 1)]                       # [N, k, D]
+    ref = torch.einsum("nd,nkd->nk", stored.double().cpu(), rows) * valid
+    assert rel_l2(dots, ref.float()) < F32_TOL
+    assert float(dots[0, 0]) == 0.0 and float(dots[N - 1, k - 1]) == 0.0
+
+
 @pytest.mark.parametrize("n", [4096 * 3, 1001])
 def test_signum_schedulefree_kernel(cuda_lib, n):
     """sc_signum_schedulefree against the oracle's restatement, several steps, with the bf16 copy."""
