@@ -5,8 +5,36 @@
 
 namespace {
 
-constexpr int kSlices = 64;       // row slices for the column sums
-constexpr int kRedBlocks = 1024;  // partial sums of the flat reductions
+#ifndef SC_COLSUM_SLICES
+#define SC_COLSUM_SLICES 256
+#endif
+constexpr int kSlices = SC_COLSUM_SLICES;  // row slices for the column sums
+constexpr int kColsumUnroll = 4;           // rows in flight per thread
+constexpr int kRedBlocks = 1024;           // partial sums of the flat reductions
+
+// partial[s][d] = sum of w[n] * y[n][d] over the rows n of slice s (w == NULL: 1), D % 4 == 0.
+// A CTA owns 1024 consecutive columns (a thread four of them) and walks the rows of its
+// slice, so every row is read in 2 KB (bf16) / 4 KB contiguous pieces and a thread's sums
+// never leave its registers.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_wide_kernel(const T* __restrict__ y, const float* __restrict__ w, int64_t N, int64_t D,
+                   float* __restrict__ partial) {
+  const int64_t d = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+  if (d >= D) return;
+  const int64_t per = (N + kSlices - 1) / kSlices;
+  const int64_t r0 = (int64_t)blockIdx.y * per;
+  const int64_t r1 = r0 + per < N ? r0 + per : N;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll kColsumUnroll
+  for (int64_t r = r0; r < r1; ++r) {
+    const float wr = w != nullptr ? __ldg(w + r) : 1.f;
+    const float4 x = sc::load4<T>(y + r * D + d);
+    acc.x = fmaf(wr, x.x, acc.x); acc.y = fmaf(wr, x.y, acc.y);
+    acc.z = fmaf(wr, x.z, acc.z); acc.w = fmaf(wr, x.w, acc.w);
+  }
+  *reinterpret_cast<float4*>(partial + (int64_t)blockIdx.y * D + d) = acc;
+}
 
 // partial[s][d] = sum of w[n] * y[n][d] over the rows n of slice s (w == NULL: 1).
 // VEC = 4: each lane owns four consecutive columns (8/16-byte loads); VEC = 1
@@ -52,9 +80,9 @@ colsum_partial_kernel(const T* __restrict__ y, const float* __restrict__ w, int6
 
 template <typename T>
 void launch_colsum(const T* y, const float* w, int64_t N, int64_t D, float* partial, cudaStream_t st) {
-  if (D % 4 == 0 && sc::aligned(y, 16)) {
-    dim3 grid((unsigned)((D + 127) / 128), kSlices);
-    colsum_partial_kernel<T, 4><<<grid, 256, 0, st>>>(y, w, N, D, partial);
+  if (D % 4 == 0 && sc::aligned(y, 16) && sc::aligned(partial, 16)) {
+    dim3 grid((unsigned)((D + 1023) / 1024), kSlices);
+    colsum_wide_kernel<T><<<grid, 256, 0, st>>>(y, w, N, D, partial);
   } else {
     dim3 grid((unsigned)((D + 31) / 32), kSlices);
     colsum_partial_kernel<T, 1><<<grid, 256, 0, st>>>(y, w, N, D, partial);
