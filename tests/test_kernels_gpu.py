@@ -65,6 +65,9 @@ def test_decode_golden(cuda_lib, d_in):
     (300, 4096, 8192, 32, torch.bfloat16),
     (64, 1024, 2048, 64, torch.bfloat16),
     (5, 52, 96, 3, torch.float32),
+    (33, 520, 300, 7, torch.bfloat16),      # k below one register group, ragged width
+    (40, 1024, 4096, 100, torch.bfloat16),  # several register groups, the last one partial
+    (3, 256, 4096, 1100, torch.bfloat16),   # more entries than the register-staged kernel stages
 ])
 def test_decode_oracle(cuda_lib, N, D, M, k, wdtype):
     from sparsify_b200 import ops
