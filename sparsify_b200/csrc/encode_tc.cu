@@ -579,42 +579,85 @@ encode_topk_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 // One warp per row. Candidates with value < 0 are empty slots. Output is in
 // descending value (ties: ascending index), so it does not depend on the order
 // in which the lists were filled.
+//
+// Keys are 64-bit: value bits in the high word (values are >= 0), inverted index in the
+// low word, so a larger key is the better candidate, keys of real candidates are distinct
+// and non-zero, and 0 stands for an empty slot. Every strip's list becomes a chunk of
+// kp = 2^ceil(log2 k) keys in shared memory; each chunk is sorted (descending) by a bitonic
+// network, then chunks are merged pairwise keeping only the better kp of each pair:
+// max(A[i], B[kp-1-i]) is a bitonic sequence holding them, which log2(kp) compare-exchange
+// steps sort again. After log2(chunks) rounds chunk 0 is the row's top kp.
+__device__ __forceinline__ void cmp_swap_desc(unsigned long long* keys, int i, int j, bool desc) {
+  const unsigned long long x = keys[i], y = keys[j];
+  const bool swap = desc ? x < y : x > y;
+  keys[i] = swap ? y : x;
+  keys[j] = swap ? x : y;
+}
+
 __global__ void __launch_bounds__(128)
 topk_merge_kernel(const float* __restrict__ cand_vals, const int32_t* __restrict__ cand_idx, int64_t N,
-                  int ncand, int k, float* __restrict__ top_vals, int64_t* __restrict__ top_idx) {
-  const int lane = threadIdx.x & 31;
-  const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+                  int n_strips, int k, int kp, int chunks, float* __restrict__ top_vals,
+                  int64_t* __restrict__ top_idx) {
+  extern __shared__ unsigned long long s_keys[];  // [warps][chunks * kp]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
   if (n >= N) return;
-  const float* cv = cand_vals + n * ncand;
-  const int32_t* ci = cand_idx + n * ncand;
-  // 64-bit keys: value bits in the high word (values are >= 0), inverted index
-  // in the low word, so a larger key is the better candidate.
-  unsigned long long last = ~0ull;
-  for (int r = 0; r < k; ++r) {
-    unsigned long long best = 0ull;
-    for (int c = lane; c < ncand; c += 32) {
-      const float v = cv[c];
-      if (v >= 0.f) {
-        const unsigned long long key =
-            ((unsigned long long)__float_as_uint(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)ci[c]);
-        if (key < last && key > best) best = key;
+  const int P = chunks * kp;
+  unsigned long long* keys = s_keys + (size_t)warp * P;
+  const float* cv = cand_vals + n * (int64_t)n_strips * k;
+  const int32_t* ci = cand_idx + n * (int64_t)n_strips * k;
+  for (int t = lane; t < P; t += 32) {
+    const int c = t / kp, j = t - c * kp;
+    unsigned long long key = 0ull;
+    if (c < n_strips && j < k) {
+      const float v = cv[c * k + j];
+      if (v >= 0.f)
+        key = ((unsigned long long)__float_as_uint(v) << 32) |
+              (unsigned long long)(0xffffffffu - (uint32_t)ci[c * k + j]);
+    }
+    keys[t] = key;
+  }
+  __syncwarp();
+  // every chunk sorted descending
+  for (int size = 2; size <= kp; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = lane; t < (P >> 1); t += 32) {
+        const int i = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+        const bool desc = size == kp || (i & size) == 0;
+        cmp_swap_desc(keys, i, i + stride, desc);
       }
+      __syncwarp();
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-      best = other > best ? other : best;
+  }
+  // pairwise merges that keep the better kp keys of two chunks in the first of them
+  for (int step = 1; step < chunks; step <<= 1) {
+    const int pairs = chunks / (2 * step);
+    for (int t = lane; t < pairs * kp; t += 32) {
+      const int m = t / kp, i = t - m * kp;
+      unsigned long long* A = keys + (size_t)(2 * step * m) * kp;
+      const unsigned long long* B = A + (size_t)step * kp;
+      const unsigned long long x = A[i], y = B[kp - 1 - i];
+      A[i] = x > y ? x : y;
     }
-    if (lane == 0) {
-      if (best != 0ull) {
-        top_vals[n * k + r] = __uint_as_float((uint32_t)(best >> 32));
-        top_idx[n * k + r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
-      } else {  // fewer than k candidates: cannot happen when M >= k
-        top_vals[n * k + r] = 0.f;
-        top_idx[n * k + r] = 0;
+    __syncwarp();
+    for (int stride = kp >> 1; stride > 0; stride >>= 1) {
+      for (int t = lane; t < pairs * (kp >> 1); t += 32) {
+        const int m = t / (kp >> 1), u = t - m * (kp >> 1);
+        const int i = ((u & ~(stride - 1)) << 1) | (u & (stride - 1));
+        cmp_swap_desc(keys + (size_t)(2 * step * m) * kp, i, i + stride, true);
       }
+      __syncwarp();
     }
-    last = best;
+  }
+  for (int r = lane; r < k; r += 32) {
+    const unsigned long long best = keys[r];
+    if (best != 0ull) {
+      top_vals[n * k + r] = __uint_as_float((uint32_t)(best >> 32));
+      top_idx[n * k + r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
+    } else {  // fewer than k candidates: cannot happen when M >= k
+      top_vals[n * k + r] = 0.f;
+      top_idx[n * k + r] = 0;
+    }
   }
 }
 
@@ -772,8 +815,14 @@ extern "C" int sc_encode_topk(const void* x_bf16, const void* W_bf16, const floa
   SC_CHECK_LAUNCH("init_tau");
   rc = launch_encoder(pl, tmx, tmw, p, st, "encode_topk_tc");
   if (rc != SC_OK) return rc;
-  const int ncand = pl.n_strips * k;
-  topk_merge_kernel<<<(unsigned)((N + 3) / 4), 128, 0, st>>>(cand_vals, cand_idx, N, ncand, k, top_vals, top_idx);
+  int kp = 1, chunks = 1;
+  while (kp < k) kp <<= 1;
+  while (chunks < pl.n_strips) chunks <<= 1;
+  const size_t merge_smem = (size_t)4 * chunks * kp * sizeof(unsigned long long);
+  if (merge_smem > 48 * 1024)
+    SC_CUDA(cudaFuncSetAttribute(topk_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+  topk_merge_kernel<<<(unsigned)((N + 3) / 4), 128, merge_smem, st>>>(cand_vals, cand_idx, N, pl.n_strips, k, kp,
+                                                                      chunks, top_vals, top_idx);
   SC_CHECK_LAUNCH("topk_merge");
   return SC_OK;
 }
