@@ -480,7 +480,7 @@ class StepWorkload:
         self.opt.zero_grad(set_to_none=True)
         with torch.no_grad():
             fired = torch.zeros(M, dtype=torch.bool, device=self.dev)
-            fired[out.latent_indices.flatten()] = True
+            fired.index_fill_(0, out.latent_indices.flatten(), True)  # (indexed assignment would block the host)
             if world > 1:
                 f8 = fired.to(torch.uint8)
                 dist.all_reduce(f8, op=dist.ReduceOp.MAX)

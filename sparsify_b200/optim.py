@@ -175,7 +175,7 @@ class FusedAdam(torch.optim.Optimizer):
                 dist.all_reduce(extra_rows)  # dead sets are identical on every rank
                 extra_rows /= shard[1]
             rank_map = torch.full((W_dec.shape[0],), -1, dtype=torch.int32, device=W_dec.device)
-            rank_map[dead_idx] = torch.arange(dead_idx.numel(), dtype=torch.int32, device=W_dec.device)
+            rank_map.index_copy_(0, dead_idx, torch.arange(dead_idx.numel(), dtype=torch.int32, device=W_dec.device))
             kw.update(extraA=extra_rows, extra_rank=rank_map[rows].contiguous())
         if getattr(sae, "_overlap_decoder", False):
             # Encoder half now; decoder half on a side stream, where it can run under the

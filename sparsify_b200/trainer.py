@@ -347,7 +347,9 @@ class Trainer:
                                 self.num_tokens_since_fired[name] > self.cfg.dead_feature_threshold)
                                if may_be_dead else None),
                 )
-                did_fire[name][out.latent_indices.flatten()] = True
+                # index_fill_ is queued like any kernel; `mask[indices] = True` makes the host wait
+                # for everything queued before it
+                did_fire[name].index_fill_(0, out.latent_indices.flatten(), True)
                 self.maybe_all_reduce(did_fire[name], "max")
 
                 if e2e:
