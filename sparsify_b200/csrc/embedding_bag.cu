@@ -289,6 +289,12 @@ decode_residual_dots_kernel(const int64_t* __restrict__ idx, const float* __rest
   }
 }
 
+// Launch shape of decode_residual_dots_kernel for k <= 32: 64 threads, six CTAs per SM (about 170
+// registers each) measured fastest - 0.88 ms at 16384 x 32 rows of 8 KB, against 0.91 (128 x 3),
+// 1.00 (192 x 2) and 1.17 ms (256 x 2)
+constexpr int kDotsThreads = 64;
+constexpr int kDotsCtasPerSm = 6;
+
 // Decode (and residual) of bf16 rows with the gathered rows staged in registers: a thread owns
 // four columns out of every 4 * TPB and loads that column group of GROUP rows at once (GROUP
 // independent 8-byte loads), then accumulates them in ascending j order - the same sums, in the
@@ -358,20 +364,16 @@ decode_rows_kernel(const int64_t* __restrict__ idx, const float* __restrict__ ac
 // 16 rows at a time, 64 threads, 12 CTAs per SM measured fastest at 16384 x 32 rows of 8 KB (decode
 // 0.60 ms, decode + residual 0.64 ms; 32 rows at a time: 0.64 / 0.72 ms; 128 threads: 0.62 / 0.67 ms;
 // the kernels with 256 threads and four rows in flight that this replaced: 0.86 / 1.03 ms)
-#ifndef SC_ROWS_GROUP
-#define SC_ROWS_GROUP 16
-#define SC_ROWS_TPB 64
-#define SC_ROWS_MINB 12
-#endif
+constexpr int kRowsGroup = 16, kRowsThreads = 64, kRowsCtasPerSm = 12;
 constexpr int kRowsMaxK = 1024;  // entries of one token staged at once by decode_rows_kernel
 
 template <typename YT>
 void launch_decode_rows(const int64_t* idx, const float* acts, const __nv_bfloat16* W, const float* bias,
                         const YT* y, int64_t N, int64_t D, int64_t M, int k, float* out, float* e32,
                         __nv_bfloat16* e16, float* partial, cudaStream_t st) {
-  const int kpad = (k + SC_ROWS_GROUP - 1) / SC_ROWS_GROUP * SC_ROWS_GROUP;
-  decode_rows_kernel<SC_ROWS_GROUP, SC_ROWS_TPB, SC_ROWS_MINB, YT>
-      <<<(unsigned)N, SC_ROWS_TPB, (size_t)kpad * 12, st>>>(idx, acts, W, bias, y, D, M, k, out, e32, e16, partial);
+  const int kpad = (k + kRowsGroup - 1) / kRowsGroup * kRowsGroup;
+  decode_rows_kernel<kRowsGroup, kRowsThreads, kRowsCtasPerSm, YT>
+      <<<(unsigned)N, kRowsThreads, (size_t)kpad * 12, st>>>(idx, acts, W, bias, y, D, M, k, out, e32, e16, partial);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -580,19 +582,12 @@ extern "C" int sc_decode_residual_dots(const int64_t* idx, const float* acts, co
   using bf16 = __nv_bfloat16;
   bf16* e16 = static_cast<bf16*>(e_bf16);
   const bf16* w = static_cast<const bf16*>(W);
-  // k <= 32: 64 threads, six CTAs per SM (about 170 registers each) measured fastest - 0.88 ms at
-  // 16384 x 32 rows of 8 KB, against 0.91 (128 x 3), 1.00 (192 x 2) and 1.17 ms (256 x 2)
-#ifndef SC_DOTS_TPB
-#define SC_DOTS_TPB 64
-#define SC_DOTS_MINB 6
-#define SC_DOTS_VEC 4
-#endif
 #define SC_LAUNCH_DRD(KMAX, VEC, TPB, MINB, YT)                                                        \
   decode_residual_dots_kernel<KMAX, VEC, TPB, MINB, YT><<<grid, TPB, 0, st>>>(idx, acts, w, bias,       \
       static_cast<const YT*>(y), D, M, k, out, e_f32, e16, partial, dots)
   if (k <= 32) {
-    if (y_dtype == SC_F32) SC_LAUNCH_DRD(32, SC_DOTS_VEC, SC_DOTS_TPB, SC_DOTS_MINB, float);
-    else SC_LAUNCH_DRD(32, SC_DOTS_VEC, SC_DOTS_TPB, SC_DOTS_MINB, bf16);
+    if (y_dtype == SC_F32) SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, float);
+    else SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, bf16);
   } else {
     if (y_dtype == SC_F32) SC_LAUNCH_DRD(64, 2, 256, 1, float); else SC_LAUNCH_DRD(64, 2, 256, 1, bf16);
   }
