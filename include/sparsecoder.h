@@ -170,7 +170,7 @@ int sc_decode_residual(const int64_t* idx, const float* acts, const void* W,
  * this is grad_acts / s of sc_embedding_bag_bwd_acts, so the backward of the decode
  * needs no second gather. The dot uses e as stored: rounded to bf16 when e_bf16 is the
  * only residual written. Ids outside [0, M) contribute nothing and get dot 0.
- * W must be bf16, k <= 64, D % 4 == 0; SC_ERR_UNSUPPORTED
+ * W must be bf16, k <= 32, D % 4 == 0; SC_ERR_UNSUPPORTED
  * otherwise (use the two separate calls).
  * sparsify/sparse_coder.py:198-202,225,253 and sparsify/xformers.py:125-131. */
 int sc_decode_residual_dots(const int64_t* idx, const float* acts, const void* W,

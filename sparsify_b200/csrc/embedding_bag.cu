@@ -561,7 +561,9 @@ extern "C" int sc_decode_residual(const int64_t* idx, const float* acts, const v
 }
 
 // As sc_decode_residual, and also dots[N, k] = e . W[idx] per selected entry (see the kernel).
-// Covers what the training step uses: W in bf16, k <= 64, D a multiple of 4.
+// Covers what the training step uses: W in bf16, k <= 32, D a multiple of 4. (With 64 rows in
+// registers - two columns per thread - the pass took 2.6-2.9 ms at k = 64 against 1.16 + 1.35 ms
+// for the two separate kernels, so wider selections keep those.)
 extern "C" int sc_decode_residual_dots(const int64_t* idx, const float* acts, const void* W, int w_dtype,
                                        const float* bias, const void* y, int y_dtype, int64_t N, int64_t D,
                                        int64_t M, int k, float* out, float* e_f32, void* e_bf16, float* sse,
@@ -569,8 +571,8 @@ extern "C" int sc_decode_residual_dots(const int64_t* idx, const float* acts, co
   SC_REQUIRE(sc::valid_dtype(w_dtype) && sc::valid_dtype(y_dtype), "sc_decode_residual_dots: bad dtype");
   SC_REQUIRE(N > 0 && D > 0 && M > 0 && k > 0 && N <= 0x7fffffffLL, "sc_decode_residual_dots: bad shape");
   SC_REQUIRE(idx && acts && W && y && sse && ws && dots, "sc_decode_residual_dots: null pointer");
-  if (w_dtype != SC_BF16 || k > 64 || D % 4 != 0)
-    return sc::fail(SC_ERR_UNSUPPORTED, "sc_decode_residual_dots: needs bf16 W, k <= 64 and D %% 4 == 0");
+  if (w_dtype != SC_BF16 || k > 32 || D % 4 != 0)
+    return sc::fail(SC_ERR_UNSUPPORTED, "sc_decode_residual_dots: needs bf16 W, k <= 32 and D %% 4 == 0");
   const void* al[] = {W, y, out, e_f32, e_bf16, bias};
   for (const void* q : al) SC_REQUIRE(q == nullptr || sc::aligned(q, 16), "sc_decode_residual_dots: pointers must be 16-byte aligned");
   if (ws_bytes < sc_decode_residual_workspace_bytes(N))
@@ -585,12 +587,8 @@ extern "C" int sc_decode_residual_dots(const int64_t* idx, const float* acts, co
 #define SC_LAUNCH_DRD(KMAX, VEC, TPB, MINB, YT)                                                        \
   decode_residual_dots_kernel<KMAX, VEC, TPB, MINB, YT><<<grid, TPB, 0, st>>>(idx, acts, w, bias,       \
       static_cast<const YT*>(y), D, M, k, out, e_f32, e16, partial, dots)
-  if (k <= 32) {
-    if (y_dtype == SC_F32) SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, float);
-    else SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, bf16);
-  } else {
-    if (y_dtype == SC_F32) SC_LAUNCH_DRD(64, 2, 256, 1, float); else SC_LAUNCH_DRD(64, 2, 256, 1, bf16);
-  }
+  if (y_dtype == SC_F32) SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, float);
+  else SC_LAUNCH_DRD(32, 4, kDotsThreads, kDotsCtasPerSm, bf16);
 #undef SC_LAUNCH_DRD
   SC_CHECK_LAUNCH("sc_decode_residual_dots");
   sum_partials_kernel<<<1, 1024, 0, st>>>(partial, N, sse);

@@ -272,7 +272,7 @@ def embedding_bag_bwd_acts(idx: Tensor, grad_out: Tensor, W: Tensor) -> Tensor:
 def decode_dots_supported(W: Tensor, k: int) -> bool:
     """Whether `decode_residual(..., want_dots=True)` has a kernel for this case."""
     D = W.shape[-1]
-    return W.dtype == torch.bfloat16 and k <= 64 and D % 4 == 0
+    return W.dtype == torch.bfloat16 and k <= 32 and D % 4 == 0
 
 
 def decode_residual(idx: Tensor, acts: Tensor, W: Tensor, bias: Tensor | None, y: Tensor, *,

@@ -380,8 +380,8 @@ def test_decode_residual(cuda_lib, ydtype):
 @pytest.mark.parametrize("N,D,M,k,ydtype,both", [
     (300, 4096, 2048, 32, torch.bfloat16, False),   # the training step's case: bf16 residual only
     (65, 520, 300, 7, torch.float32, True),         # ragged width, fp32 residual kept
-    (130, 1024, 512, 64, torch.bfloat16, False),    # k > 32: two columns per thread
-    (33, 260, 100, 40, torch.float32, True),        # k > 32, ragged width, fp32 residual kept
+    (130, 1024, 512, 32, torch.bfloat16, False),    # every register slot in use
+    (33, 260, 100, 20, torch.float32, True),        # ragged width and k, fp32 residual kept
 ])
 def test_decode_residual_dots(cuda_lib, N, D, M, k, ydtype, both):
     """sc_decode_residual_dots: the decode / residual outputs equal sc_decode_residual's bit for bit,
@@ -414,6 +414,7 @@ def test_decode_residual_dots(cuda_lib, N, D, M, k, ydtype, both):
     ref = torch.einsum("nd,nkd->nk", stored.double().cpu(), rows) * valid
     assert rel_l2(dots, ref.float()) < F32_TOL
     assert float(dots[0, 0]) == 0.0 and float(dots[N - 1, k - 1]) == 0.0
+    assert not ops.decode_dots_supported(Wc, 33)      # wider selections keep the two separate kernels
 
 
 @pytest.mark.parametrize("n", [4096 * 3, 1001])
