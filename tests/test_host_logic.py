@@ -207,3 +207,19 @@ def test_sparse_update_is_refused_where_dead_sets_can_diverge():
     assert sparse_update_allowed(mk(exclude_tokens=[0], auxk_alpha=1 / 32, distribute_modules=True), 8)
     assert not sparse_update_allowed(mk(grad_acc_steps=2), 1)
     assert not sparse_update_allowed(mk(loss_fn="ce"), 1)
+
+
+def test_no_assignment_through_an_index_tensor_on_the_step_path():
+    """`t[index_tensor] = value` on a CUDA tensor makes the host wait for everything queued before
+    it (measured: the whole training step); `index_fill_` / `index_copy_` do not. The step path -
+    the package and the benchmark's step - must not reintroduce such an assignment."""
+    import pathlib
+    import re
+    root = pathlib.Path(__file__).resolve().parent.parent
+    pat = re.compile(r"\[[^\[\]\"']*\b\w*(?:idx|indices)\b[^\[\]\"']*\]\s*=(?!=)")
+    hits = []
+    for f in sorted((root / "sparsify_b200").glob("*.py")) + [root / "bench.py"]:
+        for no, line in enumerate(f.read_text().splitlines(), 1):
+            if pat.search(line.split("#")[0]):
+                hits.append(f"{f.name}:{no}: {line.strip()}")
+    assert not hits, hits
